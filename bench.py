@@ -1,0 +1,288 @@
+"""Benchmark of the Clef-Omni MoE block on B200: MoE-layer prefill tokens/s at T=4096.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the block (router -> top-8 -> permutation -> gate/up+SwiGLU -> down ->
+combine) over one packed batch.  Workload at N=1: BASELINE configuration 2 -- T=4096 as eight
+packed sequences (lengths uniform in [64,1024] rescaled to 4096), hidden 2048, 128 experts
+top-8, intermediate 768, BF16 weights N(0,0.02), BF16 activations N(0,1), seed 1.
+
+Prints ONE JSON line.  `value` is tokens/s with inputs resident in HBM; `e2e` is the same
+metric through the host-buffer C-ABI call with the copies inside the timed region; `roofline`
+is the gate/up expert product (the dominant kernel) against the measured BF16 peak;
+`cpu_baseline` is the PyTorch CPU block the reference's Python oracle runs, timed on a bounded
+sample of the same workload on this host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+T_TOKENS = 4096
+SEED = 1
+H, F, E, TOP = 2048, 768, 128, 8
+GATEUP_FLOP_PER_TOKEN = 2 * H * (2 * F) * TOP          # 50,331,648
+EXPERT_FLOP_PER_TOKEN = GATEUP_FLOP_PER_TOKEN + 2 * F * H * TOP   # 75,497,472
+WEIGHT_BYTES = (E * H + E * 2 * F * H + E * H * F) * 2
+KERNELS_PER_PASS = 9     # router, exact pass, histogram, scan, scatter, gather, gate/up, down, combine
+METRIC = "MoE-layer prefill tokens/sec at T=4096"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(bf16_tflops=float(d["bf16_tflops"]), hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(bf16_tflops=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None, reasons=reasons,
+                    samples=len(sm))
+
+
+def cpu_block(router, gate_up, down):
+    """The CPU block the reference's Python oracle executes per layer (ref/omni.py:125-128):
+    Hugging Face Qwen3OmniMoeThinkerTextSparseMoeBlock, eager experts, FP32 math on the
+    BF16-rounded weights.  Falls back to the FP32 port in oracle/ when transformers lacks it."""
+    import torch
+    try:
+        from transformers.models.qwen3_omni_moe import modeling_qwen3_omni_moe as m
+        from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeTextConfig
+        cfg = Qwen3OmniMoeTextConfig(hidden_size=H, moe_intermediate_size=F, num_experts=E, num_experts_per_tok=TOP,
+                                     norm_topk_prob=True)
+        cfg._experts_implementation = "eager"
+        blk = m.Qwen3OmniMoeThinkerTextSparseMoeBlock(cfg).eval()
+        with torch.no_grad():
+            blk.gate.weight.copy_(router.float())
+            blk.experts.gate_up_proj.copy_(gate_up.float())
+            blk.experts.down_proj.copy_(down.float())
+
+        def run(x):
+            with torch.inference_mode():
+                y = blk(x[None])
+                return y[0] if isinstance(y, tuple) else y
+        return run, "reference", "Hugging Face Qwen3OmniMoeThinkerTextSparseMoeBlock (the block ref/omni.py runs), FP32 on BF16-rounded weights"
+    except Exception:   # pragma: no cover - depends on the installed transformers
+        from oracle import omni_oracle as orc
+
+        def run(x):
+            with torch.inference_mode():
+                return orc.moe_block_f32(x, router, gate_up, down)[0]
+        return run, "port", "FP32 restatement of the block (oracle/omni_oracle.py: moe_block_f32)"
+
+
+def time_cpu(run, x, steps, warmup):
+    for _ in range(warmup):
+        run(x)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        run(x)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def reference_arm(args):
+    """The reference's own CPU implementation of the path on this host's cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from cleffa_b200 import workloads
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    router, gate_up, down = workloads.make_weights(SEED)
+    x = workloads.make_activations(SEED, T_TOKENS).float()
+    run, kind, what = cpu_block(router, gate_up, down)
+    probe = time_cpu(run, x[:512].contiguous(), 1, 1)[0]
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    sample_t = T_TOKENS if probe * (T_TOKENS / 512) <= budget else 512
+    xs = x[:sample_t].contiguous()
+    times = time_cpu(run, xs, args.steps, max(1, args.warmup))
+    total = sum(times)
+    value = sample_t * args.steps / total
+    sample = f"{what}; first {sample_t} of {T_TOKENS} tokens per step, {torch.get_num_threads()} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(1), "tokens": sample_t},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_name(n_gpus):
+    return (f"Clef-Omni MoE layer, T={T_TOKENS} packed varlen prefill (8 sequences), hidden 2048, 128 experts top-8, "
+            f"intermediate 768, bf16 weights N(0,0.02), bf16 activations N(0,1), seed {SEED}"
+            + ("" if n_gpus == 1 else f", per GPU (experts sharded {E // n_gpus} per GPU)"))
+
+
+def ours(args):
+    import torch
+    import torch.distributed as dist
+    from cleffa_b200 import OmniBackend, workloads
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    router, gate_up, down = workloads.make_weights(SEED)
+    x_host = workloads.make_activations(SEED + 1000 * rank, T_TOKENS).pin_memory()
+    bounds = workloads.varlen_bounds(SEED, T_TOKENS)
+    res_host = torch.zeros(T_TOKENS, H).pin_memory()
+
+    stream = torch.cuda.current_stream()
+    b = OmniBackend(local, stream=stream.cuda_stream)
+    b.reserve(T_TOKENS)
+    b.bind_layer(0, router, gate_up, down)
+    xn = x_host.cuda()
+    x = torch.zeros(T_TOKENS, H, device="cuda")
+
+    def step():
+        b.begin()
+        b.encode_moe(0, xn, x, bounds)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    b.complete()
+
+    # ---- device-resident timing (value) with per-stage marks for the roofline
+    b.set_option("profile", 1)
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record(stream)
+        for _ in range(args.steps):
+            step()
+        stop.record(stream)
+        barrier()
+    b.complete()
+    elapsed_ms = start.elapsed_time(stop)
+    stages = b.profile()
+    b.set_option("profile", 0)
+
+    # ---- end to end through the host-buffer call (copies inside the timed region)
+    for _ in range(2):
+        b.forward_host(0, x_host, res_host, bounds)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        b.forward_host(0, x_host, res_host, bounds)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_s = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        tokens = T_TOKENS * world
+        value = tokens * args.steps / (elapsed_ms * 1e-3)
+        gateup_ms = stages["gate_up"]
+        achieved = GATEUP_FLOP_PER_TOKEN * T_TOKENS / (gateup_ms * 1e-3) / 1e12 if gateup_ms > 0 else 0.0
+        both_ms = stages["gate_up"] + stages["down"]
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(world), "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
+                       "timing": "CUDA events on the launching stream, max over ranks"},
+            "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s",
+                    "h2d_bytes_per_step": T_TOKENS * H * 2 + T_TOKENS * H * 4, "d2h_bytes_per_step": T_TOKENS * H * 4},
+            "gpu_launches": KERNELS_PER_PASS * args.steps,
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": "expert_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                         "peak_source": peaks["source"], "traffic": None},
+            "stages_ms": stages,
+            "expert_gemms": {"tflops": EXPERT_FLOP_PER_TOKEN * T_TOKENS / (both_ms * 1e-3) / 1e12 if both_ms > 0 else 0.0,
+                             "frac_of_bf16_peak": (EXPERT_FLOP_PER_TOKEN * T_TOKENS / (both_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]) if both_ms > 0 else 0.0},
+            "hbm": {"weights_gbs_over_layer": WEIGHT_BYTES / (elapsed_ms / args.steps * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"]},
+        }
+        if world == 1 and not args.no_cpu:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            run, kind, what = cpu_block(router, gate_up, down)
+            xs = x_host[:512].float().contiguous()
+            times = time_cpu(run, xs, 3, 1)
+            line["cpu_baseline"] = {"value": 512 / min(times), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+                                    "sample": f"{what}; first 512 of {T_TOKENS} tokens, best of 3 after one warm-up"}
+        print(json.dumps(line))
+    b.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        ours(args)
+
+
+if __name__ == "__main__":
+    main()

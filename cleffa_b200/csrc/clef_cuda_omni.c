@@ -1,0 +1,668 @@
+/* CUDA backend for the Clef-Omni mixture-of-experts block: host side.
+ *
+ * Mirrors the Omni module of the reference's Metal backend (clef_metal_omni.m): a scratch
+ * arena with an atomic reserve, a device status word cleared by begin and checked by complete,
+ * per-chunk stage dispatch, optional route capture with a JSONL dump.  A command buffer
+ * becomes a CUDA stream; "encode" only enqueues work and errors surface at completion, as in
+ * the reference (clef_metal.m:1591-1597).
+ *
+ * There is no CPU fallback: every stage is a CUDA kernel (omni_kernels.cu, omni_sm100.cu).
+ */
+#define _GNU_SOURCE
+#include "clef_cuda_omni.h"
+#include "omni_internal.h"
+
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { MAX_LAYERS = 128, N_STAGE_EVENTS = 6, PROF_SLOTS = 64 };
+
+/* Route capture row, byte-compatible with omni_route_row (clef_metal_omni.m:15): 1088 bytes. */
+typedef struct { float logits[OMNI_E], low[OMNI_E]; int32_t ids[OMNI_TOP]; float weights[OMNI_TOP]; } omni_route_row;
+
+typedef struct {
+    void *router, *gate_up, *down;      /* device, BF16 */
+    float *bias;                        /* device, FP32 [128] or NULL */
+    bool owned, bound;
+    CUtensorMap tm_router, tm_gate_up, tm_down;
+} omni_layer;
+
+/* The scratch arena (clef_omni_gpu in the reference, clef_metal_omni.m:18-23). */
+typedef struct {
+    float *logits;                      /* [CHUNK][128] approximate router logits */
+    int32_t *ids; float *weights;       /* [CHUNK][8] */
+    int32_t *flag_rows, *n_flag;        /* rows handed to the exact pass */
+    uint32_t *status, *sink;
+    omni_sort_state sort;
+    void *xg, *h, *d;                   /* permuted rows: BF16 [ROWS][2048], [ROWS][768], [ROWS][2048] */
+    CUtensorMap tm_xg, tm_h;
+    size_t bytes;
+} omni_arena;
+
+struct clef_gpu {
+    int device, n_sm;
+    cudaStream_t stream;
+    bool own_stream;
+    omni_arena *omni;
+    omni_layer layer[MAX_LAYERS];
+    int n_layer;
+    /* route capture */
+    omni_route_row *trace;              /* device */
+    int trace_first, trace_rows, trace_layers;
+    bool trace_valid;
+    /* options */
+    bool debug_poison, router_exact, profile;
+    float router_eps;
+    int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
+    long alloc_fail_at, alloc_count;    /* host-side fault injection */
+    long launch_fail_at, launch_count;
+    /* pass state */
+    bool failed;                        /* a launch or copy of this pass failed (cb_failed, clef_metal_internal.h:52) */
+    char fail_msg[160];
+    int last_T;
+    cudaEvent_t ev[PROF_SLOTS][N_STAGE_EVENTS];   /* ring of per-pass stage marks, read by clef_omni_profile */
+    long prof_passes;
+    void *stage_x, *stage_res;          /* forward_host staging */
+    size_t stage_cap;
+    CUresult (*encode_tiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                             const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+};
+
+static void set_err(char *err, size_t errlen, const char *fmt, ...) {
+    if (!err || !errlen) return;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(err, errlen, fmt, ap);
+    va_end(ap);
+}
+
+static void note_failure(clef_gpu *g, const char *what, cudaError_t e) {
+    if (g->failed) return;
+    g->failed = true;
+    snprintf(g->fail_msg, sizeof g->fail_msg, "cuda: %s failed: %s", what, cudaGetErrorString(e));
+}
+
+/* Every stage launch goes through here so a test can make the Nth one fail on the host
+ * (the counterpart of CLEF_DEBUG_NIL_CMDBUF, clef_metal_internal.h:53). */
+static bool launched(clef_gpu *g, const char *what, cudaError_t e) {
+    if (g->launch_fail_at > 0 && ++g->launch_count == g->launch_fail_at) e = cudaErrorLaunchFailure;
+    if (e == cudaSuccess) return true;
+    note_failure(g, what, e);
+    return false;
+}
+
+/* ---------------------------------------------------------------- allocation */
+static void *dev_alloc(clef_gpu *g, size_t bytes) {
+    void *p = NULL;
+    if (g->alloc_fail_at > 0 && ++g->alloc_count == g->alloc_fail_at) return NULL;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return NULL; }
+    return p;
+}
+
+static bool make_map(clef_gpu *g, CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                     CUtensorMapL2promotion promo) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return g->encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)base, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+/* ---------------------------------------------------------------- lifecycle */
+bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, size_t errlen) {
+    if (!out) { set_err(err, errlen, "cuda: null context pointer"); return false; }
+    *out = NULL;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot select device %d: %s", device, cudaGetErrorString(e)); return false; }
+    struct cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot query device %d: %s", device, cudaGetErrorString(e)); return false; }
+    if (prop.major != 10) {
+        set_err(err, errlen, "cuda: device %d is sm_%d%d; this backend is built for sm_100a only", device, prop.major, prop.minor);
+        return false;
+    }
+    clef_gpu *g = calloc(1, sizeof *g);
+    if (!g) { set_err(err, errlen, "cuda: cannot allocate backend state"); return false; }
+    g->device = device;
+    g->n_sm = prop.multiProcessorCount;
+    g->router_eps = 5e-4f;
+    void *fn = NULL;
+    enum cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess) {
+        set_err(err, errlen, "cuda: driver lacks cuTensorMapEncodeTiled");
+        free(g);
+        return false;
+    }
+    *(void **)&g->encode_tiled = fn;
+    if (stream) g->stream = (cudaStream_t)stream;
+    else {
+        e = cudaStreamCreateWithFlags(&g->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot create stream: %s", cudaGetErrorString(e)); free(g); return false; }
+        g->own_stream = true;
+    }
+    e = omni_sm100_configure();
+    if (e != cudaSuccess) {
+        set_err(err, errlen, "cuda: cannot configure sm_100a kernels: %s", cudaGetErrorString(e));
+        if (g->own_stream) cudaStreamDestroy(g->stream);
+        free(g);
+        return false;
+    }
+    for (int p = 0; p < PROF_SLOTS; p++) for (int i = 0; i < N_STAGE_EVENTS; i++) cudaEventCreate(&g->ev[p][i]);
+    const char *v;
+    if ((v = getenv("CLEF_DEBUG_POISON")) && *v == '1') g->debug_poison = true;
+    if ((v = getenv("CLEF_PROFILE")) && *v == '1') g->profile = true;
+    if ((v = getenv("CLEF_OMNI_ROUTER_EXACT")) && *v == '1') g->router_exact = true;
+    if ((v = getenv("CLEF_OMNI_ROUTER_EPS"))) { float f = strtof(v, NULL); if (f > 0 && isfinite(f)) g->router_eps = f; }
+    if ((v = getenv("CLEF_DEBUG_OMNI_ALLOC_FAIL"))) g->alloc_fail_at = strtol(v, NULL, 10);
+    if ((v = getenv("CLEF_DEBUG_OMNI_LAUNCH_FAIL"))) g->launch_fail_at = strtol(v, NULL, 10);
+    *out = g;
+    return true;
+}
+
+static void free_layer(omni_layer *L) {
+    if (L->owned) { cudaFree(L->router); cudaFree(L->gate_up); cudaFree(L->down); cudaFree(L->bias); }
+    memset(L, 0, sizeof *L);
+}
+
+static void free_arena(omni_arena *s) {
+    if (!s) return;
+    void *all[] = {s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status, s->sink, s->sort.counts,
+                   s->sort.offsets, s->sort.rowmap, s->sort.slots, s->sort.segcount, s->sort.ttiles, s->sort.n_ttiles,
+                   s->xg, s->h, s->d};
+    for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
+    free(s);
+}
+
+void clef_omni_free(clef_gpu *g) {
+    if (!g) return;
+    free_arena(g->omni);
+    g->omni = NULL;
+}
+
+void clef_cuda_omni_close(clef_gpu *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    cudaStreamSynchronize(g->stream);
+    clef_omni_free(g);
+    for (int l = 0; l < MAX_LAYERS; l++) free_layer(&g->layer[l]);
+    if (g->trace) cudaFree(g->trace);
+    if (g->stage_x) cudaFree(g->stage_x);
+    if (g->stage_res) cudaFree(g->stage_res);
+    for (int p = 0; p < PROF_SLOTS; p++) for (int i = 0; i < N_STAGE_EVENTS; i++) if (g->ev[p][i]) cudaEventDestroy(g->ev[p][i]);
+    if (g->own_stream) cudaStreamDestroy(g->stream);
+    free(g);
+}
+
+bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err, size_t errlen) {
+    if (!g || !c || T <= 0 || c->H != OMNI_H || c->ffn != OMNI_F || c->n_expert != OMNI_E || c->n_expert_used != OMNI_TOP ||
+        c->n_layer <= 0 || c->n_layer > MAX_LAYERS) {
+        set_err(err, errlen, "cuda: invalid Omni scratch dimensions");
+        return false;
+    }
+    if (g->omni) { if (c->n_layer > g->n_layer) g->n_layer = c->n_layer; return true; }
+    cudaSetDevice(g->device);
+    omni_arena *s = calloc(1, sizeof *s);
+    if (!s) { set_err(err, errlen, "cuda: cannot allocate Omni state"); return false; }
+    struct { void **p; size_t bytes; } want[] = {
+        {(void **)&s->logits, (size_t)OMNI_CHUNK * OMNI_E * 4},
+        {(void **)&s->ids, (size_t)OMNI_CHUNK * OMNI_TOP * 4},
+        {(void **)&s->weights, (size_t)OMNI_CHUNK * OMNI_TOP * 4},
+        {(void **)&s->flag_rows, (size_t)OMNI_CHUNK * 4},
+        {(void **)&s->n_flag, 256},
+        {(void **)&s->status, 256},
+        {(void **)&s->sink, 256},
+        {(void **)&s->sort.counts, (size_t)OMNI_E * 4},
+        {(void **)&s->sort.offsets, (size_t)(OMNI_E + 1) * 4},
+        {(void **)&s->sort.rowmap, (size_t)OMNI_ROWS * 4},
+        {(void **)&s->sort.slots, (size_t)OMNI_ROWS * 4},
+        {(void **)&s->sort.segcount, (size_t)OMNI_MAX_SEGS * OMNI_E * 4},
+        {(void **)&s->sort.ttiles, (size_t)OMNI_MAX_TTILES * sizeof(omni_ttile)},
+        {(void **)&s->sort.n_ttiles, 256},
+        {&s->xg, (size_t)OMNI_ROWS * OMNI_H * 2},
+        {&s->h, (size_t)OMNI_ROWS * OMNI_F * 2},
+        {&s->d, (size_t)OMNI_ROWS * OMNI_H * 2},
+    };
+    bool ok = true;
+    for (size_t i = 0; i < sizeof want / sizeof want[0] && ok; i++) {
+        *want[i].p = dev_alloc(g, want[i].bytes);
+        if (!*want[i].p) ok = false;
+        else s->bytes += want[i].bytes;
+    }
+    s->sort.status = s->status;
+    if (ok) ok = make_map(g, &s->tm_xg, s->xg, OMNI_ROWS, OMNI_H, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
+                 make_map(g, &s->tm_h, s->h, OMNI_ROWS, OMNI_F, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (ok) ok = cudaMemsetAsync(s->status, 0, 256, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(s->sink, 0, 256, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(s->n_flag, 0, 256, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(s->sort.n_ttiles, 0, 256, g->stream) == cudaSuccess &&
+                 cudaStreamSynchronize(g->stream) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        free_arena(s);
+        set_err(err, errlen, "cuda: cannot allocate Omni expert arena (previous buffers kept)");
+        return false;
+    }
+    g->omni = s;
+    g->n_layer = c->n_layer;
+    return true;
+}
+
+size_t clef_omni_arena_bytes(const clef_gpu *g) { return g && g->omni ? g->omni->bytes : 0; }
+
+static void poison(clef_gpu *g, void *p, size_t bytes, uint32_t pattern) {
+    launched(g, "poison fill", omni_launch_fill_u32(p, pattern, bytes / 4, g->stream));
+}
+
+void clef_omni_begin(clef_gpu *g) {
+    if (!g || !g->omni) return;
+    omni_arena *s = g->omni;
+    cudaSetDevice(g->device);
+    g->failed = false;
+    g->fail_msg[0] = 0;
+    g->trace_valid = false;
+    if (cudaMemsetAsync(s->status, 0, 4, g->stream) != cudaSuccess) note_failure(g, "status clear", cudaGetLastError());
+    if (g->debug_poison) {
+        /* clef_metal_omni.m:152-158: every float scratch buffer starts as NaN */
+        poison(g, s->logits, (size_t)OMNI_CHUNK * OMNI_E * 4, 0x7fc00000u);
+        poison(g, s->weights, (size_t)OMNI_CHUNK * OMNI_TOP * 4, 0x7fc00000u);
+        poison(g, s->xg, (size_t)OMNI_ROWS * OMNI_H * 2, 0x7fc07fc0u);
+        poison(g, s->h, (size_t)OMNI_ROWS * OMNI_F * 2, 0x7fc07fc0u);
+        poison(g, s->d, (size_t)OMNI_ROWS * OMNI_H * 2, 0x7fc07fc0u);
+        if (g->trace) poison(g, g->trace, (size_t)g->trace_layers * g->trace_rows * sizeof(omni_route_row), 0x7fc00000u);
+    }
+}
+
+bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen) {
+    if (!g || !g->omni) { set_err(err, errlen, "cuda: Omni arena not reserved"); return false; }
+    cudaSetDevice(g->device);
+    uint32_t status = 0;
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e == cudaSuccess) e = cudaMemcpy(&status, g->omni->status, 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni pass failed: %s", cudaGetErrorString(e)); return false; }
+    if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    if (status & OMNI_ST_TIMEOUT) { set_err(err, errlen, "cuda: a bounded device wait ran out in an Omni expert kernel"); return false; }
+    if (status & OMNI_ST_BAD_ID) { set_err(err, errlen, "cuda: expert id outside [0,128) reached the Omni permutation"); return false; }
+    if (status) { set_err(err, errlen, "cuda: nonfinite Omni attention or router values"); return false; }
+    g->trace_valid = g->trace != NULL;
+    return true;
+}
+
+void clef_omni_keepalive(clef_gpu *g) {
+    if (!g || !g->omni) return;
+    omni_arena *s = g->omni;
+    cudaSetDevice(g->device);
+    const void *buffers[] = {s->logits, s->ids, s->weights, s->status, s->sort.counts, s->sort.offsets, s->sort.rowmap,
+                             s->sort.slots, s->xg, s->h, s->d, g->trace};
+    for (size_t i = 0; i < sizeof buffers / sizeof buffers[0]; i++)
+        if (buffers[i]) omni_launch_touch(buffers[i], NULL, g->stream);
+}
+
+/* ---------------------------------------------------------------- route capture */
+bool clef_omni_trace_reserve(clef_gpu *g, int T, int layers, int rows, bool enabled, char *err, size_t errlen) {
+    if (!g || !g->omni) { set_err(err, errlen, "cuda: Omni arena not reserved"); return false; }
+    cudaSetDevice(g->device);
+    if (!enabled) {
+        cudaStreamSynchronize(g->stream);
+        if (g->trace) cudaFree(g->trace);
+        g->trace = NULL;
+        g->trace_rows = g->trace_layers = 0;
+        g->trace_valid = false;
+        return true;
+    }
+    if (T <= 0 || layers <= 0 || layers > MAX_LAYERS || rows < 0) {
+        set_err(err, errlen, "cuda: invalid Omni trace dimensions");
+        return false;
+    }
+    const int R = rows > 0 && rows < T ? rows : T;
+    omni_route_row *next = dev_alloc(g, (size_t)layers * R * sizeof(omni_route_row));
+    if (!next) {
+        set_err(err, errlen, "cuda: cannot allocate Omni route capture (previous buffers kept)");
+        return false;
+    }
+    cudaStreamSynchronize(g->stream);
+    if (g->trace) cudaFree(g->trace);
+    g->trace = next;
+    g->trace_first = T - R; g->trace_rows = R; g->trace_layers = layers;
+    g->trace_valid = false;
+    return true;
+}
+
+bool clef_gpu_dump_routes(clef_gpu *g, const char *path, char *err, size_t errlen) {
+    if (!g || !g->omni || !g->trace || !g->trace_rows || !g->trace_valid) {
+        set_err(err, errlen, "no captured Omni routes");
+        return false;
+    }
+    cudaSetDevice(g->device);
+    const size_t n = (size_t)g->trace_layers * g->trace_rows;
+    omni_route_row *rows = malloc(n * sizeof *rows);
+    if (!rows) { set_err(err, errlen, "cannot allocate Omni route dump"); return false; }
+    if (cudaMemcpy(rows, g->trace, n * sizeof *rows, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        free(rows);
+        set_err(err, errlen, "cannot read captured Omni routes");
+        return false;
+    }
+    /* Validate before creating output (clef_metal_omni.m:105-113). */
+    for (size_t i = 0; i < n; i++) {
+        for (int j = 0; j < OMNI_E; j++) if (!isfinite(rows[i].logits[j]) || !isfinite(rows[i].low[j])) {
+            free(rows); set_err(err, errlen, "nonfinite captured Omni router logits"); return false;
+        }
+        for (int j = 0; j < OMNI_TOP; j++) if (rows[i].ids[j] < 0 || rows[i].ids[j] >= OMNI_E || !isfinite(rows[i].weights[j])) {
+            free(rows); set_err(err, errlen, "invalid captured Omni routes"); return false;
+        }
+    }
+    FILE *f = fopen(path, "w");
+    if (!f) { free(rows); set_err(err, errlen, "cannot open Omni route dump: %s", path); return false; }
+    for (int l = 0; l < g->trace_layers; l++) for (int t = 0; t < g->trace_rows; t++) {
+        const omni_route_row *r = rows + (size_t)l * g->trace_rows + t;
+        double top[OMNI_TOP + 1];
+        for (int j = 0; j <= OMNI_TOP; j++) top[j] = -INFINITY;
+        for (int e = 0; e < OMNI_E; e++) {
+            double v = (double)r->logits[e] + r->low[e];
+            for (int j = 0; j <= OMNI_TOP; j++) if (v > top[j]) { double old = top[j]; top[j] = v; v = old; }
+        }
+        fprintf(f, "{\"layer\":%d,\"token\":%d,\"logits\":[", l, g->trace_first + t);
+        for (int j = 0; j < OMNI_E; j++) fprintf(f, "%s%.17g", j ? "," : "", (double)r->logits[j] + r->low[j]);
+        fputs("],\"ids\":[", f);
+        for (int j = 0; j < OMNI_TOP; j++) fprintf(f, "%s%d", j ? "," : "", r->ids[j]);
+        fputs("],\"weights\":[", f);
+        for (int j = 0; j < OMNI_TOP; j++) fprintf(f, "%s%.9g", j ? "," : "", r->weights[j]);
+        fprintf(f, "],\"margin\":%.17g}\n", top[OMNI_TOP - 1] - top[OMNI_TOP]);
+    }
+    bool ok = !ferror(f);
+    if (fclose(f)) ok = false;
+    free(rows);
+    if (!ok) set_err(err, errlen, "cannot write Omni route dump: %s", path);
+    return ok;
+}
+
+/* ---------------------------------------------------------------- weights */
+bool clef_omni_bind_layer(clef_gpu *g, int layer, const void *router, const void *gate_up, const void *down,
+                          const float *router_bias, int where, char *err, size_t errlen) {
+    if (!g || layer < 0 || layer >= MAX_LAYERS || !router || !gate_up || !down ||
+        (where != CLEF_OMNI_HOST && where != CLEF_OMNI_DEVICE)) {
+        set_err(err, errlen, "cuda: invalid Omni expert tensor binding");
+        return false;
+    }
+    cudaSetDevice(g->device);
+    const size_t nr = (size_t)OMNI_E * OMNI_H * 2, ng = (size_t)OMNI_E * 2 * OMNI_F * OMNI_H * 2, nd = (size_t)OMNI_E * OMNI_H * OMNI_F * 2;
+    omni_layer next;
+    memset(&next, 0, sizeof next);
+    if (where == CLEF_OMNI_DEVICE) {
+        if (((uintptr_t)router | (uintptr_t)gate_up | (uintptr_t)down) & 255) {
+            set_err(err, errlen, "cuda: Omni expert tensors must be 256-byte aligned");
+            return false;
+        }
+        next.router = (void *)router; next.gate_up = (void *)gate_up; next.down = (void *)down; next.bias = (float *)router_bias;
+    } else {
+        next.owned = true;
+        next.router = dev_alloc(g, nr); next.gate_up = dev_alloc(g, ng); next.down = dev_alloc(g, nd);
+        if (router_bias) next.bias = dev_alloc(g, OMNI_E * 4);
+        bool ok = next.router && next.gate_up && next.down && (!router_bias || next.bias);
+        if (ok) ok = cudaMemcpyAsync(next.router, router, nr, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
+                     cudaMemcpyAsync(next.gate_up, gate_up, ng, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
+                     cudaMemcpyAsync(next.down, down, nd, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
+                     (!router_bias || cudaMemcpyAsync(next.bias, router_bias, OMNI_E * 4, cudaMemcpyHostToDevice, g->stream) == cudaSuccess) &&
+                     cudaStreamSynchronize(g->stream) == cudaSuccess;
+        if (!ok) {
+            cudaGetLastError();
+            free_layer(&next);
+            set_err(err, errlen, "cuda: cannot upload Omni expert tensors of layer %d (previous binding kept)", layer);
+            return false;
+        }
+    }
+    if (!make_map(g, &next.tm_router, next.router, OMNI_E, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
+        !make_map(g, &next.tm_gate_up, next.gate_up, (uint64_t)OMNI_E * 2 * OMNI_F, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
+        !make_map(g, &next.tm_down, next.down, (uint64_t)OMNI_E * OMNI_H, OMNI_F, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+        free_layer(&next);
+        set_err(err, errlen, "cuda: cannot describe Omni expert tensors of layer %d", layer);
+        return false;
+    }
+    next.bound = true;
+    cudaStreamSynchronize(g->stream);
+    free_layer(&g->layer[layer]);
+    g->layer[layer] = next;
+    return true;
+}
+
+/* ---------------------------------------------------------------- stages */
+static bool check_pass(clef_gpu *g, int layer, bool need_weights, char *err, size_t errlen) {
+    if (!g || !g->omni) { set_err(err, errlen, "cuda: Omni arena not reserved"); return false; }
+    if (need_weights && (layer < 0 || layer >= MAX_LAYERS || !g->layer[layer].bound)) {
+        set_err(err, errlen, "cuda: invalid Omni layer dispatch");
+        return false;
+    }
+    cudaSetDevice(g->device);
+    return true;
+}
+
+/* Stage marks are only recorded here; nothing waits on them inside a pass. */
+static void stage_mark(clef_gpu *g, int i) { if (g->profile) cudaEventRecord(g->ev[g->prof_passes % PROF_SLOTS][i], g->stream); }
+
+/* router + exact pass for one chunk; fills arena ids/weights/logits */
+static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int rows) {
+    omni_arena *s = g->omni;
+    if (!launched(g, "flag reset", cudaMemsetAsync(s->n_flag, 0, 4, g->stream))) return false;
+    if (g->router_impl == 0) {
+        CUtensorMap tm_x;
+        if (!make_map(g, &tm_x, xn, (uint64_t)rows, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
+            note_failure(g, "router activation descriptor", cudaErrorInvalidValue);
+            return false;
+        }
+        if (!launched(g, "router", omni_launch_router_sm100(&tm_x, &L->tm_router, L->bias, rows, g->router_eps, g->router_exact,
+                                                            s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status,
+                                                            g->stream))) return false;
+    } else {
+        if (!launched(g, "router (check kernel)", omni_launch_router_simple(xn, L->router, L->bias, rows, s->logits, g->stream))) return false;
+        if (!launched(g, "route", omni_launch_select(s->logits, rows, g->router_eps, g->router_exact, s->ids, s->weights,
+                                                     s->flag_rows, s->n_flag, s->status, g->stream))) return false;
+    }
+    return launched(g, "router exact pass", omni_launch_recheck(xn, L->router, L->bias, s->logits, s->flag_rows, s->n_flag, rows,
+                                                                g->router_eps, s->ids, s->weights, s->status, g->stream));
+}
+
+/* permutation + expert products + combine for one chunk, routing taken from ids/weights */
+static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const int32_t *ids, const float *weights,
+                        float *x, int rows) {
+    omni_arena *s = g->omni;
+    const int rows8 = rows * OMNI_TOP;
+    if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
+    if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
+    stage_mark(g, 2);
+    if (g->gemm_impl == 0) {
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, &s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
+        stage_mark(g, 3);
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, &s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
+    } else {
+        if (!launched(g, "gate/up experts (check kernel)", omni_launch_gateup_simple(s->xg, L->gate_up, s->sort.offsets, rows8, s->h, g->stream))) return false;
+        stage_mark(g, 3);
+        if (!launched(g, "down experts (check kernel)", omni_launch_down_simple(s->h, L->down, s->sort.offsets, rows8, s->d, g->stream))) return false;
+    }
+    stage_mark(g, 4);
+    if (!launched(g, "combine", omni_launch_combine(s->d, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
+    stage_mark(g, 5);
+    return true;
+}
+
+static void book_profile(clef_gpu *g) { if (g->profile) g->prof_passes++; }
+
+bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int T, int n_seq,
+                          const int32_t *seq_bounds, char *err, size_t errlen) {
+    if (!check_pass(g, layer, true, err, errlen)) return false;
+    if (!xn || !x || T <= 0 || n_seq < 1 || ((uintptr_t)xn & 15) || ((uintptr_t)x & 15)) {
+        set_err(err, errlen, "cuda: invalid Omni layer dispatch");
+        return false;
+    }
+    if (seq_bounds) {
+        bool ok = seq_bounds[0] == 0 && seq_bounds[n_seq] == T;
+        for (int i = 0; i < n_seq && ok; i++) ok = seq_bounds[i] < seq_bounds[i + 1];
+        if (!ok) { set_err(err, errlen, "cuda: invalid Omni sequence bounds"); return false; }
+    } else if (n_seq != 1) {
+        set_err(err, errlen, "cuda: invalid Omni sequence bounds");
+        return false;
+    }
+    if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    const omni_layer *L = &g->layer[layer];
+    omni_arena *s = g->omni;
+    /* Tokens are independent, so the packed batch is processed in arena-sized chunks
+     * regardless of record boundaries; a token's arithmetic never depends on its chunk. */
+    for (int start = 0; start < T; start += OMNI_CHUNK) {
+        const int rows = T - start < OMNI_CHUNK ? T - start : OMNI_CHUNK;
+        const char *xn_c = (const char *)xn + (size_t)start * OMNI_H * 2;
+        stage_mark(g, 0);
+        bool ok = run_router(g, L, xn_c, rows);
+        if (ok && g->trace && layer < g->trace_layers && start + rows > g->trace_first)
+            ok = launched(g, "route capture", omni_launch_trace(s->logits, s->ids, s->weights, rows, start, g->trace_first,
+                                                                g->trace_rows, layer, g->trace, g->stream));
+        stage_mark(g, 1);
+        if (ok) ok = run_experts(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows);
+        if (!ok) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+        book_profile(g);
+        g->last_T = rows;
+    }
+    return true;
+}
+
+bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
+                            const int32_t *seq_bounds, char *err, size_t errlen) {
+    if (!check_pass(g, layer, true, err, errlen)) return false;
+    if (!xn_host || !x_host || T <= 0) { set_err(err, errlen, "cuda: invalid Omni layer dispatch"); return false; }
+    if ((size_t)T > g->stage_cap) {
+        void *nx = dev_alloc(g, (size_t)T * OMNI_H * 2), *nr = dev_alloc(g, (size_t)T * OMNI_H * 4);
+        if (!nx || !nr) {
+            if (nx) cudaFree(nx);
+            if (nr) cudaFree(nr);
+            set_err(err, errlen, "cuda: cannot allocate Omni activation staging (previous buffers kept)");
+            return false;
+        }
+        cudaStreamSynchronize(g->stream);
+        if (g->stage_x) cudaFree(g->stage_x);
+        if (g->stage_res) cudaFree(g->stage_res);
+        g->stage_x = nx; g->stage_res = nr; g->stage_cap = (size_t)T;
+    }
+    clef_omni_begin(g);
+    cudaError_t e = cudaMemcpyAsync(g->stage_x, xn_host, (size_t)T * OMNI_H * 2, cudaMemcpyHostToDevice, g->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(g->stage_res, x_host, (size_t)T * OMNI_H * 4, cudaMemcpyHostToDevice, g->stream);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot upload Omni activations: %s", cudaGetErrorString(e)); return false; }
+    if (!clef_omni_encode_moe(g, layer, g->stage_x, g->stage_res, T, n_seq, seq_bounds, err, errlen)) {
+        cudaStreamSynchronize(g->stream);
+        return false;
+    }
+    e = cudaMemcpyAsync(x_host, g->stage_res, (size_t)T * OMNI_H * 4, cudaMemcpyDeviceToHost, g->stream);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot download Omni residual: %s", cudaGetErrorString(e)); return false; }
+    return clef_omni_complete(g, err, errlen);
+}
+
+bool clef_omni_stage_router(clef_gpu *g, int layer, const void *xn, int T, double *logits, char *err, size_t errlen) {
+    if (!check_pass(g, layer, true, err, errlen)) return false;
+    if (!xn || !logits || T <= 0) { set_err(err, errlen, "cuda: invalid Omni router dispatch"); return false; }
+    const omni_layer *L = &g->layer[layer];
+    if (!launched(g, "router (exact)", omni_launch_router_exact(xn, L->router, L->bias, T, logits, g->stream))) {
+        set_err(err, errlen, "%s", g->fail_msg);
+        return false;
+    }
+    return true;
+}
+
+bool clef_omni_stage_route(clef_gpu *g, const float *hi, const float *lo, int rows, int32_t *ids, float *weights,
+                           char *err, size_t errlen) {
+    if (!check_pass(g, 0, false, err, errlen)) return false;
+    if (!hi || !ids || !weights || rows <= 0) { set_err(err, errlen, "cuda: invalid Omni route dispatch"); return false; }
+    if (!launched(g, "route", omni_launch_route_pairs(hi, lo, rows, ids, weights, g->omni->status, g->stream))) {
+        set_err(err, errlen, "%s", g->fail_msg);
+        return false;
+    }
+    return true;
+}
+
+bool clef_omni_stage_assign(clef_gpu *g, const int32_t *ids, int rows, int32_t *counts, int32_t *offsets,
+                            int32_t *rowmap, int32_t *slots, char *err, size_t errlen) {
+    if (!check_pass(g, 0, false, err, errlen)) return false;
+    if (!ids || rows <= 0 || rows > OMNI_CHUNK || !counts || !offsets || !rowmap || !slots) {
+        set_err(err, errlen, "cuda: invalid Omni assignment dispatch");
+        return false;
+    }
+    omni_sort_state st = g->omni->sort;
+    st.counts = counts; st.offsets = offsets; st.rowmap = rowmap; st.slots = slots;
+    if (!launched(g, "assign", omni_launch_assign(ids, rows, st, g->stream))) {
+        set_err(err, errlen, "%s", g->fail_msg);
+        return false;
+    }
+    return true;
+}
+
+bool clef_omni_stage_experts(clef_gpu *g, int layer, const void *xn, const int32_t *ids, const float *weights,
+                             float *x, int T, char *err, size_t errlen) {
+    if (!check_pass(g, layer, true, err, errlen)) return false;
+    if (!xn || !ids || !weights || !x || T <= 0 || T > OMNI_CHUNK) {
+        set_err(err, errlen, "cuda: invalid Omni expert dispatch");
+        return false;
+    }
+    stage_mark(g, 0); stage_mark(g, 1);
+    if (!run_experts(g, &g->layer[layer], xn, ids, weights, x, T)) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    book_profile(g);
+    g->last_T = T;
+    return true;
+}
+
+/* ---------------------------------------------------------------- introspection */
+bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char *err, size_t errlen) {
+    if (!check_pass(g, 0, false, err, errlen)) return false;
+    omni_arena *s = g->omni;
+    const size_t T = (size_t)g->last_T;
+    const void *src = NULL;
+    size_t have = 0;
+    if (!strcmp(what, "ids")) { src = s->ids; have = T * OMNI_TOP * 4; }
+    else if (!strcmp(what, "weights")) { src = s->weights; have = T * OMNI_TOP * 4; }
+    else if (!strcmp(what, "logits")) { src = s->logits; have = T * OMNI_E * 4; }
+    else if (!strcmp(what, "counts")) { src = s->sort.counts; have = OMNI_E * 4; }
+    else if (!strcmp(what, "offsets")) { src = s->sort.offsets; have = (OMNI_E + 1) * 4; }
+    else if (!strcmp(what, "rowmap")) { src = s->sort.rowmap; have = T * OMNI_TOP * 4; }
+    else if (!strcmp(what, "slots")) { src = s->sort.slots; have = T * OMNI_TOP * 4; }
+    else if (!strcmp(what, "status")) { src = s->status; have = 4; }
+    else if (!strcmp(what, "rechecked")) { src = s->n_flag; have = 4; }
+    else if (!strcmp(what, "n_ttiles")) { src = s->sort.n_ttiles; have = 4; }
+    if (!src || !dst || bytes > have || !bytes) { set_err(err, errlen, "cuda: unknown or oversized Omni read: %s", what); return false; }
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e == cudaSuccess) e = cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni read failed: %s", cudaGetErrorString(e)); return false; }
+    return true;
+}
+
+bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
+    if (!g || !name) return false;
+    if (!strcmp(name, "debug_poison")) g->debug_poison = value != 0;
+    else if (!strcmp(name, "router_exact")) g->router_exact = value != 0;
+    else if (!strcmp(name, "router_eps")) { if (value <= 0) return false; g->router_eps = (float)((double)value * 1e-9); }
+    else if (!strcmp(name, "gemm")) { if (value < 0 || value > 1) return false; g->gemm_impl = (int)value; }
+    else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
+    else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
+    else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
+    else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }
+    else return false;
+    return true;
+}
+
+bool clef_omni_profile(clef_gpu *g, float ms[6]) {
+    if (!g || !g->profile || !ms) return false;
+    cudaSetDevice(g->device);
+    for (int i = 0; i < 6; i++) ms[i] = 0;
+    const long n = g->prof_passes < PROF_SLOTS ? g->prof_passes : PROF_SLOTS;
+    g->prof_passes = 0;
+    if (n <= 0 || cudaStreamSynchronize(g->stream) != cudaSuccess) { cudaGetLastError(); return n <= 0; }
+    for (long p = 0; p < n; p++) {
+        float t = 0;
+        for (int i = 0; i < 5; i++)
+            if (cudaEventElapsedTime(&t, g->ev[p][i], g->ev[p][i + 1]) == cudaSuccess) ms[i] += t / (float)n;
+        if (cudaEventElapsedTime(&t, g->ev[p][0], g->ev[p][5]) == cudaSuccess) ms[5] += t / (float)n;
+    }
+    cudaGetLastError();
+    return true;
+}

@@ -1,0 +1,80 @@
+/* Shared between the C host (clef_cuda_omni.c) and the CUDA translation units.
+ * Plain C declarations only: launchers take raw pointers and a cudaStream_t. */
+#ifndef OMNI_INTERNAL_H
+#define OMNI_INTERNAL_H
+
+#include <stdint.h>
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    OMNI_H = 2048, OMNI_F = 768, OMNI_E = 128, OMNI_TOP = 8,
+    OMNI_CHUNK = 16384,                    /* tokens per arena pass */
+    OMNI_ROWS = OMNI_CHUNK * OMNI_TOP,     /* permuted rows per pass */
+    OMNI_SEG = 256,                        /* assignments per sort segment (one warp) */
+    OMNI_MAX_SEGS = OMNI_ROWS / OMNI_SEG,
+    OMNI_TILE_N = 256,                     /* token rows per expert-GEMM tile */
+    OMNI_MAX_TTILES = OMNI_ROWS / OMNI_TILE_N + OMNI_E,
+};
+
+/* status word bits (clef_omni_complete) */
+enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_RECHECK_OVERFLOW = 32u };
+
+/* One token tile of one expert: rows [row0, row0+len) of the permuted buffers. */
+typedef struct { int32_t expert, row0, len, pad; } omni_ttile;
+
+/* Device-resident sort/tile state produced by the assignment kernels. */
+typedef struct {
+    int32_t *counts;       /* [E]                                     */
+    int32_t *offsets;      /* [E+1] exclusive prefix sum of counts    */
+    int32_t *rowmap;       /* [rows*8] token of each permuted row     */
+    int32_t *slots;        /* [rows*8] permuted row of assignment i   */
+    int32_t *segcount;     /* [MAX_SEGS][E] per-segment histograms, then exclusive bases */
+    omni_ttile *ttiles;    /* [MAX_TTILES] full tiles first, remainders after            */
+    int32_t *n_ttiles;     /* [1]                                     */
+    uint32_t *status;      /* [1]                                     */
+} omni_sort_state;
+
+/* ---- plain kernels (omni_kernels.cu) ---- */
+cudaError_t omni_launch_router_simple(const void *xn, const void *router, const float *bias, int T,
+                                      float *logits, cudaStream_t s);
+cudaError_t omni_launch_select(const float *logits, int T, float eps, int exact_all, int32_t *ids, float *weights,
+                               int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s);
+cudaError_t omni_launch_recheck(const void *xn, const void *router, const float *bias, const float *logits,
+                                const int32_t *flag_rows, const int32_t *n_flag, int T, float eps,
+                                int32_t *ids, float *weights, uint32_t *status, cudaStream_t s);
+cudaError_t omni_launch_router_exact(const void *xn, const void *router, const float *bias, int T,
+                                     double *logits, cudaStream_t s);
+cudaError_t omni_launch_route_pairs(const float *hi, const float *lo, int rows, int32_t *ids, float *weights,
+                                    uint32_t *status, cudaStream_t s);
+cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st, cudaStream_t s);
+cudaError_t omni_launch_gather(const void *xn, const int32_t *rowmap, int rows8, void *xg, cudaStream_t s);
+cudaError_t omni_launch_combine(const void *d, const int32_t *ids, const float *weights, const int32_t *slots,
+                                float *x, int T, cudaStream_t s);
+cudaError_t omni_launch_gateup_simple(const void *xg, const void *gate_up, const int32_t *offsets, int rows8, void *h,
+                                      cudaStream_t s);
+cudaError_t omni_launch_down_simple(const void *h, const void *down, const int32_t *offsets, int rows8, void *d,
+                                    cudaStream_t s);
+cudaError_t omni_launch_fill_u32(void *p, uint32_t v, size_t words, cudaStream_t s);
+cudaError_t omni_launch_touch(const void *p, uint32_t *sink, cudaStream_t s);
+cudaError_t omni_launch_trace(const float *logits, const int32_t *ids, const float *weights, int rows, int start,
+                              int first, int captured, int layer, void *trace, cudaStream_t s);
+
+/* ---- tcgen05 kernels (omni_sm100.cu) ---- */
+cudaError_t omni_sm100_configure(void);   /* opt-in shared-memory sizes; call once per device */
+cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
+                                     float eps, int exact_all, float *logits, int32_t *ids, float *weights,
+                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s);
+cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x, const omni_sort_state st,
+                                     void *h, int n_sm, cudaStream_t s);
+cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h, const omni_sort_state st,
+                                   void *d, int n_sm, cudaStream_t s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

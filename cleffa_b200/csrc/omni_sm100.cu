@@ -1,0 +1,528 @@
+// Tensor-core stages of the Clef-Omni MoE block, written for sm_100a only:
+//   * router_sm100_kernel   x[T][2048] . W_r[128][2048]^T on tcgen05 with the FP32 accumulator in
+//                           TMEM, fused with bias, nonfinite check, top-8 selection, renormalised
+//                           weights and the near-tie flagging that feeds the exact pass
+//                           (reference: metal/clef.metal:2330-2394, omni_router + omni_route)
+//   * expert_gemm_kernel<GATEUP>  per expert: h = silu(Xe Wg^T) * (Xe Wu^T), SwiGLU in the epilogue
+//                           (reference: metal/clef.metal:2455-2492, omni_expert_gemm + omni_swiglu)
+//   * expert_gemm_kernel<DOWN>    per expert: d = He Wd^T            (clef.metal:2455-2482)
+//
+// Orientation of the expert products: the WEIGHT rows are the MMA M dimension (always a full
+// 128), the expert's TOKEN rows are the N dimension (16..256 in steps of 16).  A ragged expert
+// therefore costs its real row count rounded up to 16, not to a 128-row tile, and every
+// weight tile is streamed from HBM by exactly one CTA when the expert has <= 256 rows.
+//
+// Operands reach shared memory through per-CTA TMA loads (cp.async.bulk.tensor, 128-byte
+// swizzle); no cluster multicast is used anywhere.  Every wait on an mbarrier is bounded: when
+// it runs out the CTA raises OMNI_ST_TIMEOUT in the status word, drains what it issued, frees
+// its TMEM and returns.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "omni_internal.h"
+
+namespace {
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s: far beyond any legitimate wait here
+
+// Bounded wait.  Returns false when the limit ran out or another thread of the CTA gave up.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *status) {
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 256; i++) if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            atomicOr(status, OMNI_ST_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *status) {
+    for (int i = 0; i < 64; i++) if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem]^T, BF16 inputs, FP32 accumulate, one CTA.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The mbarrier gets one arrival when every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp reads TMEM lane (base+i).
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ------------------------------------------------------------------ descriptors
+// Shared-memory matrix descriptor for a K-major BF16 tile whose rows are 128 bytes (64
+// elements) written by TMA with 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO);
+// the leading offset is unused for swizzled K-major layouts.  Bits: [0,14) address>>4,
+// [16,30) LBO>>4, [32,46) SBO>>4, [46,48) version = 1, [61,64) layout = 2 (128B swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: FP32 accumulator (bits [4,6) = 1), BF16 A and B
+// ([7,10) = [10,13) = 1), both K-major, N>>3 at [17,23), M>>4 at [24,29).
+__device__ __forceinline__ uint32_t idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+constexpr int BK = 64;                       // K elements per pipeline stage (one 128-byte swizzle row)
+constexpr int A_TILE_BYTES = 128 * BK * 2;   // 16 KiB: 128 weight rows
+constexpr int TOK_BOX_ROWS = 32;             // token rows per TMA box
+constexpr int TOK_BOX_BYTES = TOK_BOX_ROWS * BK * 2;
+
+struct PipeState {
+    int stage = 0; uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int stages) { if (++stage == stages) { stage = 0; phase ^= 1; } }
+};
+
+// ====================================================================== grouped expert products
+enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
+
+template <int MODE> struct GemmCfg;
+template <> struct GemmCfg<MODE_GATEUP> {
+    static constexpr int KTOT = OMNI_H, NACC = 2, NBUF = 1, STAGES = 3, MTILES = OMNI_F / 128;
+    static constexpr int W_ROWS_PER_EXPERT = 2 * OMNI_F, OUT_COLS = OMNI_F;
+};
+template <> struct GemmCfg<MODE_DOWN> {
+    static constexpr int KTOT = OMNI_F, NACC = 1, NBUF = 2, STAGES = 4, MTILES = OMNI_H / 128;
+    static constexpr int W_ROWS_PER_EXPERT = OMNI_H, OUT_COLS = OMNI_H;
+};
+
+constexpr int GEMM_THREADS = 384;            // warp 0 TMA, 1 MMA, 2 TMEM, 3 spare, 4..11 epilogue
+constexpr int EPI_WARPS = 8;
+
+template <int MODE> struct GemmSmem {
+    static constexpr int STAGE_BYTES = GemmCfg<MODE>::NACC * A_TILE_BYTES + OMNI_TILE_N * BK * 2;
+    static constexpr int TOTAL_BYTES = GemmCfg<MODE>::STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_tok,
+                   const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
+                   __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
+    using C = GemmCfg<MODE>;
+    constexpr int KSTAGES = C::KTOT / BK;
+    constexpr int STAGE_BYTES = GemmSmem<MODE>::STAGE_BYTES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + C::STAGES * STAGE_BYTES;   // 8-byte aligned
+    // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2], drain
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 4);
+    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * (2 * C::STAGES + 5);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
+    volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);   // [STAGES] parity armed by the producer, -1 none
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_work = *n_ttiles * C::MTILES;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); armed[s] = -1; }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EPI_WARPS); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tm_w);
+        prefetch_tmap(&tm_tok);
+    }
+    if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- TMA producer
+        PipeState p;
+        for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+            const omni_ttile tt = ttiles[w / C::MTILES];
+            const int m = w % C::MTILES;
+            const int nbox = (tt.len + TOK_BOX_ROWS - 1) / TOK_BOX_ROWS;
+            const uint32_t bytes = C::NACC * A_TILE_BYTES + nbox * TOK_BOX_BYTES;
+            const int wrow = tt.expert * C::W_ROWS_PER_EXPERT + m * 128;
+            bool ok = true;
+            for (int ks = 0; ks < KSTAGES && ok; ks++) {
+                ok = mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
+                if (!ok) break;
+                const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
+                armed[p.stage] = (int)p.phase;
+                mbar_expect_tx(full_bar(p.stage), bytes);
+                tma_load_2d(sa, &tm_w, ks * BK, wrow, full_bar(p.stage));
+                if (C::NACC == 2) tma_load_2d(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, full_bar(p.stage));
+                const uint32_t sb = sa + C::NACC * A_TILE_BYTES;
+                for (int b = 0; b < nbox; b++)
+                    tma_load_2d(sb + b * TOK_BOX_BYTES, &tm_tok, ks * BK, tt.row0 + b * TOK_BOX_ROWS, full_bar(p.stage));
+                p.advance(C::STAGES);
+            }
+            if (!ok) break;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------------------------------------------------- MMA issuer
+        PipeState p;
+        int it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, it++) {
+            const omni_ttile tt = ttiles[w / C::MTILES];
+            const int n_mma = (tt.len + 15) & ~15;
+            const uint32_t idesc = idesc_bf16(128, n_mma);
+            const int buf = it % C::NBUF;
+            const uint32_t use = (uint32_t)(it / C::NBUF);
+            ok = mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u, abort_flag, status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d0 = tmem_base + (C::NBUF == 2 ? buf * 256 : 0);
+            for (int ks = 0; ks < KSTAGES; ks++) {
+                ok = mbar_wait(full_bar(p.stage), p.phase, abort_flag, status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
+                const uint64_t da0 = smem_desc_sw128(sa);
+                const uint64_t db = smem_desc_sw128(sa + C::NACC * A_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++) {
+                    const uint32_t acc = (ks | k) ? 1u : 0u;
+                    umma_bf16(d0, da0 + 2u * k, db + 2u * k, idesc, acc);
+                    if (C::NACC == 2)
+                        umma_bf16(d0 + 256, smem_desc_sw128(sa + A_TILE_BYTES) + 2u * k, db + 2u * k, idesc, acc);
+                }
+                umma_commit(empty_bar(p.stage));     // frees the stage when these MMAs have read it
+                p.advance(C::STAGES);
+            }
+            if (!ok) break;
+            umma_commit(tfull_bar(buf));             // accumulator complete
+        }
+        // Whatever happened, wait (bounded) until every MMA issued by this thread retired
+        // before TMEM is released.
+        umma_commit(drain_bar);
+        {
+            const uint64_t t0 = globaltimer_ns();
+            while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+        }
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------- epilogue: TMEM -> registers -> HBM
+        const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+        const int half = (warp - 4) >> 2;             // two warps per quadrant split the column chunks
+        int it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, it++) {
+            const omni_ttile tt = ttiles[w / C::MTILES];
+            const int m = w % C::MTILES;
+            const int buf = it % C::NBUF;
+            const uint32_t use = (uint32_t)(it / C::NBUF);
+            ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (C::NBUF == 2 ? buf * 256 : 0);
+            const int nchunk = (tt.len + 31) >> 5;
+            const int col_out = m * 128 + q * 32 + lane;            // output column owned by this thread
+            __nv_bfloat16 *orow = out + (long)tt.row0 * C::OUT_COLS + col_out;
+            for (int c = half; c < nchunk; c += 2) {
+                uint32_t g[32];
+                tmem_ld32(t0 + c * 32, g);
+                if (MODE == MODE_GATEUP) {
+                    uint32_t u[32];
+                    tmem_ld32(t0 + 256 + c * 32, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int col = c * 32 + j;
+                        if (col < tt.len)
+                            orow[(long)col * C::OUT_COLS] =
+                                __float2bfloat16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])));
+                    }
+                } else {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int col = c * 32 + j;
+                        if (col < tt.len) orow[(long)col * C::OUT_COLS] = __float2bfloat16(__uint_as_float(g[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // a wait ran out: give copies already in flight a bounded chance to land
+        for (int s = 0; s < C::STAGES; s++) {
+            const int par = armed[s];
+            if (par < 0) continue;
+            const uint64_t t0 = globaltimer_ns();
+            while (!mbar_try_wait(full_bar(s), (uint32_t)par) && globaltimer_ns() - t0 < 50000000ull) {}
+        }
+    }
+    __syncthreads();
+    if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ====================================================================== router
+constexpr int RT_STAGES = 6;
+constexpr int RT_STAGE_BYTES = 2 * A_TILE_BYTES;        // 128 token rows + 128 expert rows, 64 K each
+constexpr int RT_THREADS = 256;                         // warp 0 TMA, 1 MMA, 2 TMEM, 3 spare, 4..7 epilogue
+constexpr int RT_SMEM_BYTES = RT_STAGES * RT_STAGE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(RT_THREADS, 1)
+router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                    const float *__restrict__ bias, int T, float eps, int exact_all, float *__restrict__ logits,
+                    int32_t *__restrict__ ids, float *__restrict__ weights, int32_t *__restrict__ flag_rows,
+                    int32_t *__restrict__ n_flag, uint32_t *__restrict__ status) {
+    constexpr int KSTAGES = OMNI_H / BK;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + RT_STAGES * RT_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (RT_STAGES + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * RT_STAGES);
+    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * (2 * RT_STAGES + 1);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
+    volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * 128;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RT_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); armed[s] = -1; }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tm_x);
+        prefetch_tmap(&tm_w);
+    }
+    if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 128); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        PipeState p;
+        for (int ks = 0; ks < KSTAGES; ks++) {
+            if (!mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status)) break;
+            const uint32_t sa = smem_base + p.stage * RT_STAGE_BYTES;
+            armed[p.stage] = (int)p.phase;
+            mbar_expect_tx(full_bar(p.stage), RT_STAGE_BYTES);
+            tma_load_2d(sa, &tm_x, ks * BK, row0, full_bar(p.stage));             // rows past T read as zero
+            tma_load_2d(sa + A_TILE_BYTES, &tm_w, ks * BK, 0, full_bar(p.stage));
+            p.advance(RT_STAGES);
+        }
+    } else if (warp == 1 && lane == 0) {
+        PipeState p;
+        const uint32_t idesc = idesc_bf16(128, OMNI_E);
+        bool ok = true;
+        for (int ks = 0; ks < KSTAGES; ks++) {
+            ok = mbar_wait(full_bar(p.stage), p.phase, abort_flag, status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_base + p.stage * RT_STAGE_BYTES;
+            const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / 16; k++) umma_bf16(tmem_base, da + 2u * k, db + 2u * k, idesc, (ks | k) ? 1u : 0u);
+            umma_commit(empty_bar(p.stage));
+            p.advance(RT_STAGES);
+        }
+        umma_commit(tfull_bar);
+    } else if (warp >= 4) {
+        // One thread per token: its 128 logits sit in one TMEM lane.
+        const int q = warp & 3;
+        const long row = row0 + q * 32 + lane;
+        if (mbar_wait(tfull_bar, 0, abort_flag, status)) {
+            tc_fence_after();
+            float v[OMNI_E];
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t r[32];
+                tmem_ld32(t0 + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[c * 32 + j] = __uint_as_float(r[j]);
+            }
+            if (bias) {
+#pragma unroll
+                for (int i = 0; i < OMNI_E; i++) v[i] += __ldg(bias + i);
+            }
+            if (row < T) {
+                float4 *lp = reinterpret_cast<float4 *>(logits + row * OMNI_E);
+                bool bad = false;
+#pragma unroll
+                for (int i = 0; i < OMNI_E / 4; i++) {
+                    lp[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    bad |= !(fabsf(v[4 * i]) < CUDART_INF_F) || !(fabsf(v[4 * i + 1]) < CUDART_INF_F) ||
+                           !(fabsf(v[4 * i + 2]) < CUDART_INF_F) || !(fabsf(v[4 * i + 3]) < CUDART_INF_F);
+                }
+                int4 *ip = reinterpret_cast<int4 *>(ids + row * 8);
+                float4 *wp = reinterpret_cast<float4 *>(weights + row * 8);
+                if (bad) {
+                    atomicOr(status, OMNI_ST_NONFINITE);     // clef.metal:2362-2367
+                    ip[0] = make_int4(0, 1, 2, 3); ip[1] = make_int4(4, 5, 6, 7);
+                    wp[0] = make_float4(0.f, 0.f, 0.f, 0.f); wp[1] = wp[0];
+                } else {
+                    // nine rounds of arg-max in registers; strict '>' keeps the lowest id on ties
+                    float tv[9]; int ti[9];
+#pragma unroll
+                    for (int r = 0; r < 9; r++) {
+                        float bv = v[0]; int bi = 0;
+#pragma unroll
+                        for (int i = 1; i < OMNI_E; i++) if (v[i] > bv) { bv = v[i]; bi = i; }
+                        tv[r] = bv; ti[r] = bi;
+#pragma unroll
+                        for (int i = 0; i < OMNI_E; i++) if (i == bi) v[i] = -CUDART_INF_F;
+                    }
+                    bool close = exact_all != 0;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) close |= (tv[k] - tv[k + 1]) < 2.f * eps;
+                    float p[8], sum = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) { p[k] = expf(tv[k] - tv[0]); sum += p[k]; }
+                    const float inv = 1.f / sum;
+                    ip[0] = make_int4(ti[0], ti[1], ti[2], ti[3]); ip[1] = make_int4(ti[4], ti[5], ti[6], ti[7]);
+                    wp[0] = make_float4(p[0] * inv, p[1] * inv, p[2] * inv, p[3] * inv);
+                    wp[1] = make_float4(p[4] * inv, p[5] * inv, p[6] * inv, p[7] * inv);
+                    if (close) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        for (int s = 0; s < RT_STAGES; s++) {
+            const int par = armed[s];
+            if (par < 0) continue;
+            const uint64_t t0 = globaltimer_ns();
+            while (!mbar_try_wait(full_bar(s), (uint32_t)par) && globaltimer_ns() - t0 < 50000000ull) {}
+        }
+        // and the MMAs that may still be reading them
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(tfull_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {}
+    }
+    __syncthreads();
+    if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
+}
+
+}  // namespace
+
+// ====================================================================== launchers
+extern "C" {
+
+cudaError_t omni_sm100_configure(void) {
+    cudaError_t e;
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmSmem<MODE_GATEUP>::TOTAL_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmSmem<MODE_DOWN>::TOTAL_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(router_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);
+}
+
+cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
+                                     float eps, int exact_all, float *logits, int32_t *ids, float *weights,
+                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s) {
+    router_sm100_kernel<<<(T + 127) / 128, RT_THREADS, RT_SMEM_BYTES, s>>>(*tm_x, *tm_w, bias, T, eps, exact_all, logits,
+                                                                          ids, weights, flag_rows, n_flag, status);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x, const omni_sort_state st,
+                                     void *h, int n_sm, cudaStream_t s) {
+    expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
+        *tm_w, *tm_x, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)h, st.status);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h, const omni_sort_state st,
+                                   void *d, int n_sm, cudaStream_t s) {
+    expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
+        *tm_w, *tm_h, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)d, st.status);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

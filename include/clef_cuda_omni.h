@@ -1,0 +1,149 @@
+/* C-ABI of the CUDA (sm_100a) backend for the Clef-Omni mixture-of-experts block.
+ *
+ * This header is the drop-in boundary: it mirrors the entry points that the reference's
+ * shared Metal backend calls on its Omni module (clef_metal_internal.h:65-81, implemented in
+ * clef_metal_omni.m) for the MoE half of a decoder layer.  Objective-C handles
+ * (id<MTLCommandBuffer>, id<MTLComputeCommandEncoder>) become a CUDA stream owned by the
+ * context; everything else keeps the reference's names, argument meaning and error style:
+ * every fallible call returns bool and writes a NUL-terminated message into err[errlen].
+ *
+ * Threading: like the reference (clef_engine.h:152-155) a context is driven by one thread.
+ * All device pointers passed in must belong to the context's device.
+ */
+#ifndef CLEF_CUDA_OMNI_H
+#define CLEF_CUDA_OMNI_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque backend state: the CUDA counterpart of `struct clef_gpu`
+ * (clef_metal_internal.h:12-57) restricted to what the MoE path needs. */
+typedef struct clef_gpu clef_gpu;
+
+/* The fields of clef_config (clef_engine.h:18-33) this path reads. */
+typedef struct {
+    int n_layer;        /* decoder layers whose expert weights may be bound (<= 128) */
+    int H;              /* hidden width: 2048 */
+    int ffn;            /* expert intermediate width: 768 */
+    int n_expert;       /* 128 */
+    int n_expert_used;  /* 8 */
+} clef_omni_config;
+
+enum { CLEF_OMNI_HOST = 0, CLEF_OMNI_DEVICE = 1 };
+
+/* Geometry the kernels are compiled for (clef.c:83-93 pins the same numbers). */
+enum { CLEF_OMNI_H = 2048, CLEF_OMNI_F = 768, CLEF_OMNI_E = 128, CLEF_OMNI_TOP = 8,
+       CLEF_OMNI_CHUNK = 16384 /* tokens per arena pass; longer calls are split */ };
+
+/* ---- lifecycle -------------------------------------------------------------------- */
+
+/* Counterpart of clef_gpu_open (clef_engine.h:165; clef_metal.m:113) for this path: selects
+ * `device`, adopts `stream` (a cudaStream_t; NULL creates a private non-blocking stream)
+ * and reads the CLEF_* debug environment. */
+bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, size_t errlen);
+/* Counterpart of clef_gpu_close (clef_metal.m:241-247): frees arena, trace and owned weights. */
+void clef_cuda_omni_close(clef_gpu *g);
+
+/* clef_omni_reserve (clef_metal_omni.m:40-69): rejects T <= 0 and any geometry other than
+ * (2048, 768, 128, 8); idempotent once allocated; atomic -- a failed allocation frees what it
+ * made and leaves the previous state ("... (previous buffers kept)").  The arena size does
+ * not depend on T. */
+bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err, size_t errlen);
+/* clef_omni_free (clef_metal_omni.m:71-74). */
+void clef_omni_free(clef_gpu *g);
+/* clef_omni_begin (clef_metal_omni.m:149-159): clears the status word; with debug poison on,
+ * fills every float scratch buffer with NaN. */
+void clef_omni_begin(clef_gpu *g);
+/* clef_omni_complete (clef_metal_omni.m:161-167): waits for the stream, then reports a
+ * nonzero status word as an error.  Bit 0: nonfinite router values (clef.metal:2364).
+ * Bit 3: an expert id outside [0,128) reached the permutation.  Bit 4: a bounded device-side
+ * wait ran out.  A failed launch or stream error is reported here too. */
+bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen);
+/* clef_omni_keepalive (clef_metal_omni.m:138-147): read-only touch of every arena buffer. */
+void clef_omni_keepalive(clef_gpu *g);
+
+/* clef_omni_trace_reserve (clef_metal_omni.m:76-96): enabled=false drops the capture; a
+ * failed allocation keeps the previous capture.  Captures the last `rows` rows (0 = all T)
+ * of every layer. */
+bool clef_omni_trace_reserve(clef_gpu *g, int T, int layers, int rows, bool enabled, char *err, size_t errlen);
+/* clef_gpu_dump_routes (clef_metal_omni.m:98-136): validates, then writes one JSON line per
+ * (layer, token): logits[128] (%.17g), ids[8], weights[8] (%.9g), margin = 8th - 9th logit. */
+bool clef_gpu_dump_routes(clef_gpu *g, const char *path, char *err, size_t errlen);
+
+/* ---- weights ---------------------------------------------------------------------- */
+
+/* Binds one layer's tensors in the converted layout that bind_experts checks
+ * (clef.c:194-203, 239-246; tools/convert_omni.py:135-139), all BF16, K contiguous:
+ *   router  [128][2048]          (blk.N.ffn_router.weight)
+ *   gate_up [128][1536][2048]    (blk.N.ffn_gate_up_exps.weight; gate rows, then up rows)
+ *   down    [128][2048][768]     (blk.N.ffn_down_exps.weight)
+ * where == CLEF_OMNI_HOST: pointers into host memory (e.g. the mmap'd GGUF); the backend
+ * uploads and owns a device copy.  where == CLEF_OMNI_DEVICE: device pointers, borrowed
+ * (256-byte aligned).  router_bias (FP32 [128], same location, may be NULL) is an additive
+ * logit term; the reference has none. */
+bool clef_omni_bind_layer(clef_gpu *g, int layer, const void *router, const void *gate_up, const void *down,
+                          const float *router_bias, int where, char *err, size_t errlen);
+
+/* ---- the hot path ----------------------------------------------------------------- */
+
+/* MoE half of clef_omni_encode_layer (clef_metal_omni.m:256-329): reads the normed hidden
+ * state `xn` (device, BF16 [T][2048]), adds the routed-expert output into the FP32 residual
+ * `x` (device, [T][2048]).  Asynchronous on the context's stream: it only enqueues; errors
+ * surface at clef_omni_complete.  seq_bounds (host, n_seq+1 ascending offsets ending at T)
+ * is validated; results do not depend on how tokens are grouped into records. */
+bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int T, int n_seq,
+                          const int32_t *seq_bounds, char *err, size_t errlen);
+
+/* One synchronous pass with HOST buffers: begin, copy xn (BF16) and x (FP32) to the device,
+ * encode_moe, copy x back, complete.  This is the call a host engine makes when its
+ * activations live in host memory. */
+bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
+                            const int32_t *seq_bounds, char *err, size_t errlen);
+
+/* ---- stage entry points (model-free tests, mirroring tests/test_omni_*.m) ---------- */
+
+/* omni_router (clef.metal:2330-2345): logits[t][e] as FP64 sums of exact BF16 products. */
+bool clef_omni_stage_router(clef_gpu *g, int layer, const void *xn, int T, double *logits, char *err, size_t errlen);
+/* omni_route (clef.metal:2347-2394) on given hi/lo logit pairs (lo may be NULL): ids
+ * descending by hi+lo, ties to the lowest id; weights renormalised over the selected. */
+bool clef_omni_stage_route(clef_gpu *g, const float *hi, const float *lo, int rows, int32_t *ids, float *weights,
+                           char *err, size_t errlen);
+/* omni_assign_count/offsets/scatter (clef.metal:2396-2443) in canonical form: counts[128],
+ * offsets[129] = exclusive prefix sum of counts, rowmap[rows*8] = token of each permuted
+ * row, slots[rows*8] = permuted row of assignment t*8+k.  Stable. */
+bool clef_omni_stage_assign(clef_gpu *g, const int32_t *ids, int rows, int32_t *counts, int32_t *offsets,
+                            int32_t *rowmap, int32_t *slots, char *err, size_t errlen);
+/* gather + expert products + combine (clef.metal:2445-2523) with routing supplied by the
+ * caller: x[t] += sum_k weights[t][k] * expert_{ids[t][k]}(xn[t]). */
+bool clef_omni_stage_experts(clef_gpu *g, int layer, const void *xn, const int32_t *ids, const float *weights,
+                             float *x, int T, char *err, size_t errlen);
+
+/* ---- introspection, options, profiling -------------------------------------------- */
+
+/* Copies an arena buffer of the last pass to host memory after waiting for the stream:
+ * "ids" int32[T][8], "weights" f32[T][8], "logits" f32[T][128], "counts" int32[128],
+ * "offsets" int32[129], "rowmap" int32[T*8], "slots" int32[T*8], "status" u32,
+ * "rechecked" int32 (rows whose order was decided by the exact pass). */
+bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char *err, size_t errlen);
+/* Options: "debug_poison" 0/1 (CLEF_DEBUG_POISON), "router_exact" 0/1 (decide every row with
+ * FP64 logits), "router_eps" (bound on the tensor-core logit error, x1e-9), "gemm" 0 =
+ * tcgen05 kernels, 1 = plain CUDA-core check kernels, "router" likewise, "profile" 0/1,
+ * "alloc_fail_at" N / "launch_fail_at" N (host-side fault injection, 0 = off). */
+bool clef_omni_set_option(clef_gpu *g, const char *name, long value);
+/* With "profile" on every pass records stage marks on the stream without waiting.  This call
+ * waits for the stream and returns the mean device milliseconds per pass over the passes
+ * recorded since the previous call (at most the last 64), in the order router, permute
+ * (histogram + sort + gather), gate_up, down, combine, total; then restarts the count. */
+bool clef_omni_profile(clef_gpu *g, float ms[6]);
+/* Arena bytes currently reserved (0 when not reserved). */
+size_t clef_omni_arena_bytes(const clef_gpu *g);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
