@@ -28,7 +28,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-T_TOKENS = 4096
+T_TOKENS = 4096          # overridden by --tokens for small profiling captures
 SEED = 1
 H, F, E, TOP = 2048, 768, 128, 8
 GATEUP_FLOP_PER_TOKEN = 2 * H * (2 * F) * TOP          # 50,331,648
@@ -181,7 +181,10 @@ def ours(args):
     bounds = workloads.varlen_bounds(SEED, T_TOKENS)
     res_host = torch.zeros(T_TOKENS, H).pin_memory()
 
-    stream = torch.cuda.current_stream()
+    # A dedicated stream: the library launches on it and the timing events are recorded on it
+    # (the legacy default stream has handle 0, which the C-ABI reads as "create your own").
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     b = OmniBackend(local, stream=stream.cuda_stream)
     b.reserve(T_TOKENS)
     b.bind_layer(0, router, gate_up, down)
@@ -271,13 +274,16 @@ def ours(args):
 
 
 def main():
+    global T_TOKENS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU (default: the headline 4096)")
     args = ap.parse_args()
+    T_TOKENS = args.tokens
     if args.impl == "reference":
         reference_arm(args)
     else:

@@ -10,7 +10,7 @@ from oracle import omni_oracle as orc
 from test_oracle import SIZES, pattern_ids
 
 pytestmark = pytest.mark.gpu
-POISON = 0x5A5AC3C3 - (1 << 32)
+POISON = 0x5A5AC3C3            # tests/test_omni_assign.m:11
 GUARD = 16
 
 
