@@ -38,7 +38,7 @@ typedef struct {
     uint32_t *status, *sink;
     omni_sort_state sort;
     void *xg, *h, *d;                   /* permuted rows: BF16 [ROWS][2048], [ROWS][768], [ROWS][2048] */
-    CUtensorMap tm_xg, tm_h;
+    CUtensorMap tm_xg[4], tm_h[4];      /* box heights 32, 64, 128, 256 rows */
     size_t bytes;
 } omni_arena;
 
@@ -236,8 +236,9 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         else s->bytes += want[i].bytes;
     }
     s->sort.status = s->status;
-    if (ok) ok = make_map(g, &s->tm_xg, s->xg, OMNI_ROWS, OMNI_H, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
-                 make_map(g, &s->tm_h, s->h, OMNI_ROWS, OMNI_F, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    for (int i = 0; i < 4 && ok; i++)
+        ok = make_map(g, &s->tm_xg[i], s->xg, OMNI_ROWS, OMNI_H, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
+             make_map(g, &s->tm_h[i], s->h, OMNI_ROWS, OMNI_F, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (ok) ok = cudaMemsetAsync(s->status, 0, 256, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(s->sink, 0, 256, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(s->n_flag, 0, 256, g->stream) == cudaSuccess &&
@@ -477,9 +478,9 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
     if (g->gemm_impl == 0) {
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, &s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, &s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
     } else {
         if (!launched(g, "gate/up experts (check kernel)", omni_launch_gateup_simple(s->xg, L->gate_up, s->sort.offsets, rows8, s->h, g->stream))) return false;
         stage_mark(g, 3);

@@ -34,7 +34,7 @@ typedef struct {
     int32_t *rowmap;       /* [rows*8] token of each permuted row     */
     int32_t *slots;        /* [rows*8] permuted row of assignment i   */
     int32_t *segcount;     /* [MAX_SEGS][E] per-segment histograms, then exclusive bases */
-    omni_ttile *ttiles;    /* [MAX_TTILES] full tiles first, remainders after            */
+    omni_ttile *ttiles;    /* [MAX_TTILES] full tiles, then remainders by descending length */
     int32_t *n_ttiles;     /* [1]                                     */
     uint32_t *status;      /* [1]                                     */
 } omni_sort_state;
@@ -69,9 +69,10 @@ cudaError_t omni_sm100_configure(void);   /* opt-in shared-memory sizes; call on
 cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
                                      int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s);
-cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x, const omni_sort_state st,
+/* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
+cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, int n_sm, cudaStream_t s);
-cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h, const omni_sort_state st,
+cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                    void *d, int n_sm, cudaStream_t s);
 
 #ifdef __cplusplus

@@ -318,7 +318,16 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         const int total_full = scan_b[OMNI_E - 1];
         int at = scan_b[e] - nfull;
         for (int j = 0; j < nfull; j++) st.ttiles[at + j] = omni_ttile{e, off + j * OMNI_TILE_N, OMNI_TILE_N, 0};
-        if (rem) st.ttiles[total_full + scan_c[e] - 1] = omni_ttile{e, off + nfull * OMNI_TILE_N, rem, 0};
+        if (rem) {
+            // remainder tiles in descending length (ties by expert id): round-robin over CTAs
+            // then hands out the long ones first and the short ones last
+            int rank = 0;
+            for (int o = 0; o < OMNI_E; o++) {
+                const int ro = cnt[o] % OMNI_TILE_N;
+                rank += (ro > rem) || (ro == rem && o < e);
+            }
+            st.ttiles[total_full + rank] = omni_ttile{e, off + nfull * OMNI_TILE_N, rem, 0};
+        }
         if (e == 0) *st.n_ttiles = total_full + scan_c[OMNI_E - 1];
     }
 }

@@ -78,6 +78,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// L2 eviction policies: expert weights are read once per pass (evict first); token rows are
+// re-read by every CTA that shares the token tile (evict last).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -138,8 +155,11 @@ __device__ __forceinline__ uint32_t idesc_bf16(int m, int n) {
 
 constexpr int BK = 64;                       // K elements per pipeline stage (one 128-byte swizzle row)
 constexpr int A_TILE_BYTES = 128 * BK * 2;   // 16 KiB: 128 weight rows
-constexpr int TOK_BOX_ROWS = 32;             // token rows per TMA box
-constexpr int TOK_BOX_BYTES = TOK_BOX_ROWS * BK * 2;
+// Token rows arrive in ONE TMA box per stage; four box heights (32, 64, 128, 256 rows) keep the
+// over-read of a ragged tile below 2x.  Rows past the tile belong to the next expert (or are
+// zero-filled past the buffer): they only feed accumulator columns that are never stored.
+struct TokMaps { CUtensorMap m[4]; };
+__device__ __forceinline__ int tok_box_index(int len) { return len <= 32 ? 0 : len <= 64 ? 1 : len <= 128 ? 2 : 3; }
 
 struct PipeState {
     int stage = 0; uint32_t phase = 0;
@@ -171,7 +191,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(
 
 template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_tok,
+expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ TokMaps tm_tok,
                    const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
                    __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
     using C = GemmCfg<MODE>;
@@ -202,7 +222,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_w);
-        prefetch_tmap(&tm_tok);
+        for (int i = 0; i < 4; i++) prefetch_tmap(&tm_tok.m[i]);
     }
     if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 512); tmem_relinquish(); }
     tc_fence_before();
@@ -213,11 +233,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- TMA producer
         PipeState p;
+        const uint64_t pol_w = l2_policy_evict_first(), pol_t = l2_policy_evict_last();
         for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
             const omni_ttile tt = ttiles[w / C::MTILES];
             const int m = w % C::MTILES;
-            const int nbox = (tt.len + TOK_BOX_ROWS - 1) / TOK_BOX_ROWS;
-            const uint32_t bytes = C::NACC * A_TILE_BYTES + nbox * TOK_BOX_BYTES;
+            const int bi = tok_box_index(tt.len);
+            const uint32_t bytes = C::NACC * A_TILE_BYTES + (32u << bi) * (BK * 2);
             const int wrow = tt.expert * C::W_ROWS_PER_EXPERT + m * 128;
             bool ok = true;
             for (int ks = 0; ks < KSTAGES && ok; ks++) {
@@ -226,11 +247,9 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
                 armed[p.stage] = (int)p.phase;
                 mbar_expect_tx(full_bar(p.stage), bytes);
-                tma_load_2d(sa, &tm_w, ks * BK, wrow, full_bar(p.stage));
-                if (C::NACC == 2) tma_load_2d(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, full_bar(p.stage));
-                const uint32_t sb = sa + C::NACC * A_TILE_BYTES;
-                for (int b = 0; b < nbox; b++)
-                    tma_load_2d(sb + b * TOK_BOX_BYTES, &tm_tok, ks * BK, tt.row0 + b * TOK_BOX_ROWS, full_bar(p.stage));
+                tma_load_2d_hint(sa, &tm_w, ks * BK, wrow, full_bar(p.stage), pol_w);
+                if (C::NACC == 2) tma_load_2d_hint(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, full_bar(p.stage), pol_w);
+                tma_load_2d_hint(sa + C::NACC * A_TILE_BYTES, &tm_tok.m[bi], ks * BK, tt.row0, full_bar(p.stage), pol_t);
                 p.advance(C::STAGES);
             }
             if (!ok) break;
@@ -295,21 +314,47 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const int nchunk = (tt.len + 31) >> 5;
             const int col_out = m * 128 + q * 32 + lane;            // output column owned by this thread
             __nv_bfloat16 *orow = out + (long)tt.row0 * C::OUT_COLS + col_out;
-            for (int c = half; c < nchunk; c += 2) {
-                uint32_t g[32];
-                tmem_ld32(t0 + c * 32, g);
-                if (MODE == MODE_GATEUP) {
-                    uint32_t u[32];
-                    tmem_ld32(t0 + 256 + c * 32, u);
-                    tmem_ld_wait();
+            if (MODE == MODE_GATEUP) {
+                // SwiGLU into registers first, so that TMEM is handed back to the MMA warp
+                // before the (slow, strided) stores to HBM start.
+                uint32_t hp[4][16];
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int col = c * 32 + j;
-                        if (col < tt.len)
-                            orow[(long)col * C::OUT_COLS] =
-                                __float2bfloat16(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])));
+                for (int ci = 0; ci < 4; ci++) {
+                    const int c = half + 2 * ci;
+                    if (c < nchunk) {
+                        uint32_t g[32], u[32];
+                        tmem_ld32(t0 + c * 32, g);
+                        tmem_ld32(t0 + 256 + c * 32, u);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(
+                                silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j])),
+                                silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1])));
+                            hp[ci][j] = *reinterpret_cast<const uint32_t *>(&v);
+                        }
                     }
-                } else {
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));
+                unsigned short *o16 = reinterpret_cast<unsigned short *>(orow);
+#pragma unroll
+                for (int ci = 0; ci < 4; ci++) {
+                    const int c = half + 2 * ci;
+                    if (c < nchunk) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int col = c * 32 + 2 * j;
+                            if (col < tt.len) o16[(long)col * C::OUT_COLS] = (unsigned short)(hp[ci][j] & 0xffffu);
+                            if (col + 1 < tt.len) o16[(long)(col + 1) * C::OUT_COLS] = (unsigned short)(hp[ci][j] >> 16);
+                        }
+                    }
+                }
+            } else {
+                for (int c = half; c < nchunk; c += 2) {
+                    uint32_t g[32];
+                    tmem_ld32(t0 + c * 32, g);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -317,10 +362,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                         if (col < tt.len) orow[(long)col * C::OUT_COLS] = __float2bfloat16(__uint_as_float(g[j]));
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
     }
 
@@ -511,17 +556,21 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x, const omni_sort_state st,
+cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, int n_sm, cudaStream_t s) {
+    TokMaps tok;
+    for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
     expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, *tm_x, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)h, st.status);
+        *tm_w, tok, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)h, st.status);
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h, const omni_sort_state st,
+cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                    void *d, int n_sm, cudaStream_t s) {
+    TokMaps tok;
+    for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
     expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
-        *tm_w, *tm_h, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)d, st.status);
+        *tm_w, tok, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)d, st.status);
     return cudaGetLastError();
 }
 
