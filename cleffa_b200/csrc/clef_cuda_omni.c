@@ -36,6 +36,7 @@ typedef struct {
     int32_t *ids; float *weights;       /* [CHUNK][8] */
     int32_t *flag_rows, *n_flag;        /* rows handed to the exact pass */
     uint32_t *status, *sink;
+    unsigned long long *stamps;         /* [CHUNK/128][8] optional router timestamps */
     omni_sort_state sort;
     void *xg, *h, *d;                   /* permuted rows: BF16 [ROWS][2048], [ROWS][768], [ROWS][2048] */
     CUtensorMap tm_xg[4], tm_h[4];      /* box heights 32, 64, 128, 256 rows */
@@ -54,7 +55,7 @@ struct clef_gpu {
     int trace_first, trace_rows, trace_layers;
     bool trace_valid;
     /* options */
-    bool debug_poison, router_exact, profile;
+    bool debug_poison, router_exact, profile, debug_stamps;
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
@@ -174,8 +175,8 @@ static void free_layer(omni_layer *L) {
 static void free_arena(omni_arena *s) {
     if (!s) return;
     void *all[] = {s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status, s->sink, s->sort.counts,
-                   s->sort.offsets, s->sort.rowmap, s->sort.slots, s->sort.segcount, s->sort.ttiles, s->sort.n_ttiles,
-                   s->xg, s->h, s->d};
+                   s->sort.offsets, s->sort.rowmap, s->sort.slots, s->sort.segcount, s->sort.ttiles, s->sort.n_ttiles, s->sort.sched,
+                   s->xg, s->h, s->d, s->stamps};
     for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
     free(s);
 }
@@ -218,6 +219,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         {(void **)&s->n_flag, 256},
         {(void **)&s->status, 256},
         {(void **)&s->sink, 256},
+        {(void **)&s->stamps, (size_t)(OMNI_CHUNK / 128) * 8 * 8},
         {(void **)&s->sort.counts, (size_t)OMNI_E * 4},
         {(void **)&s->sort.offsets, (size_t)(OMNI_E + 1) * 4},
         {(void **)&s->sort.rowmap, (size_t)OMNI_ROWS * 4},
@@ -225,6 +227,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         {(void **)&s->sort.segcount, (size_t)OMNI_MAX_SEGS * OMNI_E * 4},
         {(void **)&s->sort.ttiles, (size_t)OMNI_MAX_TTILES * sizeof(omni_ttile)},
         {(void **)&s->sort.n_ttiles, 256},
+        {(void **)&s->sort.sched, 256},
         {&s->xg, (size_t)OMNI_ROWS * OMNI_H * 2},
         {&s->h, (size_t)OMNI_ROWS * OMNI_F * 2},
         {&s->d, (size_t)OMNI_ROWS * OMNI_H * 2},
@@ -459,7 +462,7 @@ static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int row
         }
         if (!launched(g, "router", omni_launch_router_sm100(&tm_x, &L->tm_router, L->bias, rows, g->router_eps, g->router_exact,
                                                             s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status,
-                                                            g->stream))) return false;
+                                                            g->debug_stamps ? s->stamps : NULL, g->stream))) return false;
     } else {
         if (!launched(g, "router (check kernel)", omni_launch_router_simple(xn, L->router, L->bias, rows, s->logits, g->stream))) return false;
         if (!launched(g, "route", omni_launch_select(s->logits, rows, g->router_eps, g->router_exact, s->ids, s->weights,
@@ -630,6 +633,7 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
     else if (!strcmp(what, "status")) { src = s->status; have = 4; }
     else if (!strcmp(what, "rechecked")) { src = s->n_flag; have = 4; }
     else if (!strcmp(what, "n_ttiles")) { src = s->sort.n_ttiles; have = 4; }
+    else if (!strcmp(what, "router_stamps")) { src = s->stamps; have = (size_t)(OMNI_CHUNK / 128) * 64; }
     if (!src || !dst || bytes > have || !bytes) { set_err(err, errlen, "cuda: unknown or oversized Omni read: %s", what); return false; }
     cudaError_t e = cudaStreamSynchronize(g->stream);
     if (e == cudaSuccess) e = cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost);
@@ -645,6 +649,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "gemm")) { if (value < 0 || value > 1) return false; g->gemm_impl = (int)value; }
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
+    else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }
     else return false;

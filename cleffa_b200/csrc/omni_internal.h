@@ -25,7 +25,8 @@ enum {
 enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_RECHECK_OVERFLOW = 32u };
 
 /* One token tile of one expert: rows [row0, row0+len) of the permuted buffers. */
-typedef struct { int32_t expert, row0, len, pad; } omni_ttile;
+/* group = index of the expert's first tile | (its tile count << 16) */
+typedef struct { int32_t expert, row0, len, group; } omni_ttile;
 
 /* Device-resident sort/tile state produced by the assignment kernels. */
 typedef struct {
@@ -34,8 +35,9 @@ typedef struct {
     int32_t *rowmap;       /* [rows*8] token of each permuted row     */
     int32_t *slots;        /* [rows*8] permuted row of assignment i   */
     int32_t *segcount;     /* [MAX_SEGS][E] per-segment histograms, then exclusive bases */
-    omni_ttile *ttiles;    /* [MAX_TTILES] full tiles, then remainders by descending length */
+    omni_ttile *ttiles;    /* [MAX_TTILES] expert-major: an expert's full tiles, then its remainder */
     int32_t *n_ttiles;     /* [1]                                     */
+    int32_t *sched;        /* [2] work counters of the two expert-product kernels, zeroed by the scan */
     uint32_t *status;      /* [1]                                     */
 } omni_sort_state;
 
@@ -68,7 +70,8 @@ cudaError_t omni_launch_trace(const float *logits, const int32_t *ids, const flo
 cudaError_t omni_sm100_configure(void);   /* opt-in shared-memory sizes; call once per device */
 cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
-                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s);
+                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
+                                     cudaStream_t s);
 /* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, int n_sm, cudaStream_t s);

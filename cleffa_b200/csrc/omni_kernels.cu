@@ -296,8 +296,8 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         for (int gq = 0; gq < 8; gq++) total += part[gq][e];
         cnt[e] = total;
         scan_a[e] = total;                          // rows
-        scan_b[e] = total / OMNI_TILE_N;            // full tiles
-        scan_c[e] = (total % OMNI_TILE_N) ? 1 : 0;  // remainder tiles
+        scan_b[e] = (total + OMNI_TILE_N - 1) / OMNI_TILE_N;   // token tiles
+        scan_c[e] = 0;
     }
     __syncthreads();
     // inclusive Hillis-Steele scans over the 128 experts
@@ -314,21 +314,14 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         st.counts[e] = n;
         st.offsets[e] = off;
         if (e == OMNI_E - 1) st.offsets[OMNI_E] = scan_a[e];
-        const int nfull = n / OMNI_TILE_N, rem = n % OMNI_TILE_N;
-        const int total_full = scan_b[OMNI_E - 1];
-        int at = scan_b[e] - nfull;
-        for (int j = 0; j < nfull; j++) st.ttiles[at + j] = omni_ttile{e, off + j * OMNI_TILE_N, OMNI_TILE_N, 0};
-        if (rem) {
-            // remainder tiles in descending length (ties by expert id): round-robin over CTAs
-            // then hands out the long ones first and the short ones last
-            int rank = 0;
-            for (int o = 0; o < OMNI_E; o++) {
-                const int ro = cnt[o] % OMNI_TILE_N;
-                rank += (ro > rem) || (ro == rem && o < e);
-            }
-            st.ttiles[total_full + rank] = omni_ttile{e, off + nfull * OMNI_TILE_N, rem, 0};
+        // expert-major tile list: the expert's full tiles, then its remainder
+        const int nt = (n + OMNI_TILE_N - 1) / OMNI_TILE_N;
+        const int first = scan_b[e] - nt;
+        for (int j = 0; j < nt; j++) {
+            const int len = min(OMNI_TILE_N, n - j * OMNI_TILE_N);
+            st.ttiles[first + j] = omni_ttile{e, off + j * OMNI_TILE_N, len, first | (nt << 16)};
         }
-        if (e == 0) *st.n_ttiles = total_full + scan_c[OMNI_E - 1];
+        if (e == 0) { *st.n_ttiles = scan_b[OMNI_E - 1]; st.sched[0] = 0; st.sched[1] = 0; }
     }
 }
 

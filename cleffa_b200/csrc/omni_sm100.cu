@@ -184,16 +184,25 @@ constexpr int EPI_WARPS = 8;
 
 template <int MODE> struct GemmSmem {
     static constexpr int STAGE_BYTES = GemmCfg<MODE>::NACC * A_TILE_BYTES + OMNI_TILE_N * BK * 2;
-    static constexpr int TOTAL_BYTES = GemmCfg<MODE>::STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int TOTAL_BYTES = GemmCfg<MODE>::STAGES * STAGE_BYTES + 1024 + 512;
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
+// Work distribution.  The work list is expert-major: for one expert, every (weight tile m,
+// token tile j) pair is consecutive, so CTAs that run at the same time share either the token
+// rows or the weight rows through L2 and each weight byte leaves HBM once even when an expert
+// has a second (remainder) token tile.  Items differ in cost, so CTAs claim them one at a time
+// from a device counter; warp 0 claims and hands the decoded item to the MMA thread and the
+// epilogue warps through a small shared-memory ring.
+struct WorkSlot { int expert, row0, len, m; };
+constexpr int RING = 4;
 
 template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ TokMaps tm_tok,
                    const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
-                   __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
+                   int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
     constexpr int STAGE_BYTES = GemmSmem<MODE>::STAGE_BYTES;
@@ -201,16 +210,19 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + C::STAGES * STAGE_BYTES;   // 8-byte aligned
-    // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2], drain
+    // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2], drain, work_full[RING], work_empty[RING]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
     const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 4);
-    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * (2 * C::STAGES + 5);
+    auto wfull_bar = [&](int r) { return bar_base + 8u * (2 * C::STAGES + 5 + r); };
+    auto wempty_bar = [&](int r) { return bar_base + 8u * (2 * C::STAGES + 5 + RING + r); };
+    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * (2 * C::STAGES + 5 + 2 * RING);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
     volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);   // [STAGES] parity armed by the producer, -1 none
+    volatile WorkSlot *ring = reinterpret_cast<volatile WorkSlot *>(misc + 32);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_work = *n_ttiles * C::MTILES;
@@ -219,6 +231,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); armed[s] = -1; }
         for (int b = 0; b < 2; b++) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EPI_WARPS); }
         mbar_init(drain_bar, 1);
+        for (int r = 0; r < RING; r++) { mbar_init(wfull_bar(r), 1); mbar_init(wempty_bar(r), 1 + EPI_WARPS); }
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_w);
@@ -231,17 +244,33 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0 && lane == 0) {
-        // ---------------------------------------------------------- TMA producer
-        PipeState p;
+        // ---------------------------------------------------------- scheduler + TMA producer
+        PipeState p, wr;
         const uint64_t pol_w = l2_policy_evict_first(), pol_t = l2_policy_evict_last();
-        for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
-            const omni_ttile tt = ttiles[w / C::MTILES];
-            const int m = w % C::MTILES;
+        int cur = atomicAdd(work_counter, 1);
+        for (;;) {
+            if (!mbar_wait(wempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) break;
+            if (cur >= n_work) {
+                ring[wr.stage].len = -1;                      // tells the consumers to stop
+                mbar_arrive(wfull_bar(wr.stage));
+                break;
+            }
+            // item -> (expert group, weight tile m, token tile j): see assign_scan_kernel
+            const omni_ttile t0 = ttiles[cur / C::MTILES];
+            const int first = t0.group & 0xffff, cnt = t0.group >> 16;
+            const int local = cur - first * C::MTILES;
+            const int m = local / cnt;
+            const omni_ttile tt = ttiles[first + local % cnt];
+            ring[wr.stage].expert = tt.expert; ring[wr.stage].row0 = tt.row0;
+            ring[wr.stage].len = tt.len; ring[wr.stage].m = m;
+            mbar_arrive(wfull_bar(wr.stage));
+            wr.advance(RING);
+            const int next = atomicAdd(work_counter, 1);      // claimed early: its latency hides behind the loads below
             const int bi = tok_box_index(tt.len);
             const uint32_t bytes = C::NACC * A_TILE_BYTES + (32u << bi) * (BK * 2);
             const int wrow = tt.expert * C::W_ROWS_PER_EXPERT + m * 128;
             bool ok = true;
-            for (int ks = 0; ks < KSTAGES && ok; ks++) {
+            for (int ks = 0; ks < KSTAGES; ks++) {
                 ok = mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
                 if (!ok) break;
                 const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
@@ -253,15 +282,20 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 p.advance(C::STAGES);
             }
             if (!ok) break;
+            cur = next;
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------- MMA issuer
-        PipeState p;
-        int it = 0;
+        PipeState p, wr;
         bool ok = true;
-        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, it++) {
-            const omni_ttile tt = ttiles[w / C::MTILES];
-            const int n_mma = (tt.len + 15) & ~15;
+        for (int it = 0; ok; it++) {
+            ok = mbar_wait(wfull_bar(wr.stage), wr.phase, abort_flag, status);
+            if (!ok) break;
+            const int len = ring[wr.stage].len;
+            mbar_arrive(wempty_bar(wr.stage));
+            wr.advance(RING);
+            if (len < 0) break;
+            const int n_mma = (len + 15) & ~15;
             const uint32_t idesc = idesc_bf16(128, n_mma);
             const int buf = it % C::NBUF;
             const uint32_t use = (uint32_t)(it / C::NBUF);
@@ -300,20 +334,25 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // ---------------------------------------------------------- epilogue: TMEM -> registers -> HBM
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
         const int half = (warp - 4) >> 2;             // two warps per quadrant split the column chunks
-        int it = 0;
+        PipeState wr;
         bool ok = true;
-        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, it++) {
-            const omni_ttile tt = ttiles[w / C::MTILES];
-            const int m = w % C::MTILES;
+        for (int it = 0; ok; it++) {
+            ok = mbar_wait(wfull_bar(wr.stage), wr.phase, abort_flag, status);
+            if (!ok) break;
+            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, m = ring[wr.stage].m;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(wempty_bar(wr.stage));
+            wr.advance(RING);
+            if (len < 0) break;
             const int buf = it % C::NBUF;
             const uint32_t use = (uint32_t)(it / C::NBUF);
             ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, status);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (C::NBUF == 2 ? buf * 256 : 0);
-            const int nchunk = (tt.len + 31) >> 5;
+            const int nchunk = (len + 31) >> 5;
             const int col_out = m * 128 + q * 32 + lane;            // output column owned by this thread
-            __nv_bfloat16 *orow = out + (long)tt.row0 * C::OUT_COLS + col_out;
+            __nv_bfloat16 *orow = out + (long)row0 * C::OUT_COLS + col_out;
             if (MODE == MODE_GATEUP) {
                 // SwiGLU into registers first, so that TMEM is handed back to the MMA warp
                 // before the (slow, strided) stores to HBM start.
@@ -346,8 +385,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             const int col = c * 32 + 2 * j;
-                            if (col < tt.len) o16[(long)col * C::OUT_COLS] = (unsigned short)(hp[ci][j] & 0xffffu);
-                            if (col + 1 < tt.len) o16[(long)(col + 1) * C::OUT_COLS] = (unsigned short)(hp[ci][j] >> 16);
+                            if (col < len) o16[(long)col * C::OUT_COLS] = (unsigned short)(hp[ci][j] & 0xffffu);
+                            if (col + 1 < len) o16[(long)(col + 1) * C::OUT_COLS] = (unsigned short)(hp[ci][j] >> 16);
                         }
                     }
                 }
@@ -359,7 +398,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int col = c * 32 + j;
-                        if (col < tt.len) orow[(long)col * C::OUT_COLS] = __float2bfloat16(__uint_as_float(g[j]));
+                        if (col < len) orow[(long)col * C::OUT_COLS] = __float2bfloat16(__uint_as_float(g[j]));
                     }
                 }
                 tc_fence_before();
@@ -395,8 +434,11 @@ __global__ void __launch_bounds__(RT_THREADS, 1)
 router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                     const float *__restrict__ bias, int T, float eps, int exact_all, float *__restrict__ logits,
                     int32_t *__restrict__ ids, float *__restrict__ weights, int32_t *__restrict__ flag_rows,
-                    int32_t *__restrict__ n_flag, uint32_t *__restrict__ status) {
+                    int32_t *__restrict__ n_flag, uint32_t *__restrict__ status, unsigned long long *__restrict__ dbg) {
     constexpr int KSTAGES = OMNI_H / BK;
+    // optional per-CTA timestamps (ns): 0 start, 1 loads issued, 2 MMAs issued, 3 accumulator
+    // ready, 4 logits stored, 5 selection stored
+    auto stamp = [&](int i) { if (dbg) dbg[blockIdx.x * 8 + i] = globaltimer_ns(); };
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + RT_STAGES * RT_STAGE_BYTES;
@@ -427,6 +469,7 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 
     if (warp == 0 && lane == 0) {
         PipeState p;
+        stamp(0);
         for (int ks = 0; ks < KSTAGES; ks++) {
             if (!mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status)) break;
             const uint32_t sa = smem_base + p.stage * RT_STAGE_BYTES;
@@ -436,6 +479,7 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             tma_load_2d(sa + A_TILE_BYTES, &tm_w, ks * BK, 0, full_bar(p.stage));
             p.advance(RT_STAGES);
         }
+        stamp(1);
     } else if (warp == 1 && lane == 0) {
         PipeState p;
         const uint32_t idesc = idesc_bf16(128, OMNI_E);
@@ -452,12 +496,14 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             p.advance(RT_STAGES);
         }
         umma_commit(tfull_bar);
+        stamp(2);
     } else if (warp >= 4) {
         // One thread per token: its 128 logits sit in one TMEM lane.
         const int q = warp & 3;
         const long row = row0 + q * 32 + lane;
         if (mbar_wait(tfull_bar, 0, abort_flag, status)) {
             tc_fence_after();
+            if (threadIdx.x == 128) stamp(3);
             float v[OMNI_E];
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
@@ -481,6 +527,7 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     bad |= !(fabsf(v[4 * i]) < CUDART_INF_F) || !(fabsf(v[4 * i + 1]) < CUDART_INF_F) ||
                            !(fabsf(v[4 * i + 2]) < CUDART_INF_F) || !(fabsf(v[4 * i + 3]) < CUDART_INF_F);
                 }
+                if (threadIdx.x == 128) stamp(4);
                 int4 *ip = reinterpret_cast<int4 *>(ids + row * 8);
                 float4 *wp = reinterpret_cast<float4 *>(weights + row * 8);
                 if (bad) {
@@ -511,6 +558,7 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     wp[1] = make_float4(p[4] * inv, p[5] * inv, p[6] * inv, p[7] * inv);
                     if (close) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
                 }
+                if (threadIdx.x == 128) stamp(5);
             }
         }
     }
@@ -550,9 +598,10 @@ cudaError_t omni_sm100_configure(void) {
 
 cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
-                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s) {
+                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
+                                     cudaStream_t s) {
     router_sm100_kernel<<<(T + 127) / 128, RT_THREADS, RT_SMEM_BYTES, s>>>(*tm_x, *tm_w, bias, T, eps, exact_all, logits,
-                                                                          ids, weights, flag_rows, n_flag, status);
+                                                                          ids, weights, flag_rows, n_flag, status, dbg);
     return cudaGetLastError();
 }
 
@@ -561,7 +610,7 @@ cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap 
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
     expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)h, st.status);
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status);
     return cudaGetLastError();
 }
 
@@ -570,7 +619,7 @@ cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *t
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
     expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, (__nv_bfloat16 *)d, st.status);
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1, (__nv_bfloat16 *)d, st.status);
     return cudaGetLastError();
 }
 
