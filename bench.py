@@ -35,6 +35,7 @@ GATEUP_FLOP_PER_TOKEN = 2 * H * (2 * F) * TOP          # 50,331,648
 EXPERT_FLOP_PER_TOKEN = GATEUP_FLOP_PER_TOKEN + 2 * F * H * TOP   # 75,497,472
 WEIGHT_BYTES = (E * H + E * 2 * F * H + E * H * F) * 2
 KERNELS_PER_PASS = 9     # router, exact pass, histogram, scan, scatter, gather, gate/up, down, combine
+KERNELS_PER_PASS_EP = 13 # ... with plan, dispatch, return and two barriers instead of gather
 METRIC = "MoE-layer prefill tokens/sec at T=4096"
 
 
@@ -187,6 +188,11 @@ def ours(args):
     torch.cuda.set_stream(stream)
     b = OmniBackend(local, stream=stream.cuda_stream)
     b.reserve(T_TOKENS)
+    if world > 1:
+        # expert parallel: 128/world experts per GPU; every rank maps every rank's exchange buffers
+        handles = [None] * world
+        dist.all_gather_object(handles, b.ep_export())
+        b.ep_connect(rank, world, b"".join(handles))
     b.bind_layer(0, router, gate_up, down)
     xn = x_host.cuda()
     x = torch.zeros(T_TOKENS, H, device="cuda")
@@ -245,11 +251,11 @@ def ours(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(world), "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
+            "config": {"workload": workload_name(world), "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world}, tokens data-parallel, peer-store dispatch/return over NVLink", "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s",
                     "h2d_bytes_per_step": T_TOKENS * H * 2 + T_TOKENS * H * 4, "d2h_bytes_per_step": T_TOKENS * H * 4},
-            "gpu_launches": KERNELS_PER_PASS * args.steps,
+            "gpu_launches": (KERNELS_PER_PASS if world == 1 else KERNELS_PER_PASS_EP) * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": "expert_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
@@ -268,6 +274,10 @@ def ours(args):
             line["cpu_baseline"] = {"value": 512 / min(times), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
                                     "sample": f"{what}; first 512 of {T_TOKENS} tokens, best of 3 after one warm-up"}
         print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        b.ep_disconnect()
+        dist.barrier()
     b.close()
     if world > 1:
         dist.destroy_process_group()

@@ -55,7 +55,7 @@ struct clef_gpu {
     int trace_first, trace_rows, trace_layers;
     bool trace_valid;
     /* options */
-    bool debug_poison, router_exact, profile, debug_stamps;
+    bool debug_poison, router_exact, profile, debug_stamps, fuse_gather;
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
@@ -68,6 +68,15 @@ struct clef_gpu {
     long prof_passes;
     void *stage_x, *stage_res;          /* forward_host staging */
     size_t stage_cap;
+    /* expert parallelism (omni_ep.cu); world <= 1 means off */
+    struct {
+        int rank, world;
+        bool ipc;                        /* peers opened through CUDA IPC (else direct pointers) */
+        omni_ep_peers peers;
+        uint32_t epoch;
+        void *dret; int32_t *rowinfo, *counts, *send_base, *n_local_rows; uint32_t *flags;
+        void *opened[OMNI_EP_MAX][OMNI_EP_BUFFERS];
+    } ep;
     CUresult (*encode_tiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -167,6 +176,8 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     return true;
 }
 
+void clef_omni_ep_disconnect(clef_gpu *g);
+
 static void free_layer(omni_layer *L) {
     if (L->owned) { cudaFree(L->router); cudaFree(L->gate_up); cudaFree(L->down); cudaFree(L->bias); }
     memset(L, 0, sizeof *L);
@@ -183,6 +194,7 @@ static void free_arena(omni_arena *s) {
 
 void clef_omni_free(clef_gpu *g) {
     if (!g) return;
+    clef_omni_ep_disconnect(g);          /* the exchange buffers include the arena's */
     free_arena(g->omni);
     g->omni = NULL;
 }
@@ -191,6 +203,7 @@ void clef_cuda_omni_close(clef_gpu *g) {
     if (!g) return;
     cudaSetDevice(g->device);
     cudaStreamSynchronize(g->stream);
+    clef_omni_ep_disconnect(g);
     clef_omni_free(g);
     for (int l = 0; l < MAX_LAYERS; l++) free_layer(&g->layer[l]);
     if (g->trace) cudaFree(g->trace);
@@ -292,6 +305,7 @@ bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen) {
     if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni pass failed: %s", cudaGetErrorString(e)); return false; }
     if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
     if (status & OMNI_ST_TIMEOUT) { set_err(err, errlen, "cuda: a bounded device wait ran out in an Omni expert kernel"); return false; }
+    if (status & OMNI_ST_EP_OVERFLOW) { set_err(err, errlen, "cuda: more expert rows were routed to this rank than its Omni arena holds"); return false; }
     if (status & OMNI_ST_BAD_ID) { set_err(err, errlen, "cuda: expert id outside [0,128) reached the Omni permutation"); return false; }
     if (status) { set_err(err, errlen, "cuda: nonfinite Omni attention or router values"); return false; }
     g->trace_valid = g->trace != NULL;
@@ -396,7 +410,11 @@ bool clef_omni_bind_layer(clef_gpu *g, int layer, const void *router, const void
         return false;
     }
     cudaSetDevice(g->device);
-    const size_t nr = (size_t)OMNI_E * OMNI_H * 2, ng = (size_t)OMNI_E * 2 * OMNI_F * OMNI_H * 2, nd = (size_t)OMNI_E * OMNI_H * OMNI_F * 2;
+    /* with expert parallelism on, only this rank's contiguous expert range lives here */
+    const int world = g->ep.world > 1 ? g->ep.world : 1, EL = OMNI_E / world;
+    const size_t per_gu = (size_t)2 * OMNI_F * OMNI_H * 2, per_dn = (size_t)OMNI_H * OMNI_F * 2;
+    const size_t nr = (size_t)OMNI_E * OMNI_H * 2, ng = (size_t)EL * per_gu, nd = (size_t)EL * per_dn;
+    const size_t first = world > 1 ? (size_t)g->ep.rank * EL : 0;
     omni_layer next;
     memset(&next, 0, sizeof next);
     if (where == CLEF_OMNI_DEVICE) {
@@ -411,8 +429,8 @@ bool clef_omni_bind_layer(clef_gpu *g, int layer, const void *router, const void
         if (router_bias) next.bias = dev_alloc(g, OMNI_E * 4);
         bool ok = next.router && next.gate_up && next.down && (!router_bias || next.bias);
         if (ok) ok = cudaMemcpyAsync(next.router, router, nr, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
-                     cudaMemcpyAsync(next.gate_up, gate_up, ng, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
-                     cudaMemcpyAsync(next.down, down, nd, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
+                     cudaMemcpyAsync(next.gate_up, (const char *)gate_up + first * per_gu, ng, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
+                     cudaMemcpyAsync(next.down, (const char *)down + first * per_dn, nd, cudaMemcpyHostToDevice, g->stream) == cudaSuccess &&
                      (!router_bias || cudaMemcpyAsync(next.bias, router_bias, OMNI_E * 4, cudaMemcpyHostToDevice, g->stream) == cudaSuccess) &&
                      cudaStreamSynchronize(g->stream) == cudaSuccess;
         if (!ok) {
@@ -423,8 +441,8 @@ bool clef_omni_bind_layer(clef_gpu *g, int layer, const void *router, const void
         }
     }
     if (!make_map(g, &next.tm_router, next.router, OMNI_E, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
-        !make_map(g, &next.tm_gate_up, next.gate_up, (uint64_t)OMNI_E * 2 * OMNI_F, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
-        !make_map(g, &next.tm_down, next.down, (uint64_t)OMNI_E * OMNI_H, OMNI_F, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+        !make_map(g, &next.tm_gate_up, next.gate_up, (uint64_t)EL * 2 * OMNI_F, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
+        !make_map(g, &next.tm_down, next.down, (uint64_t)EL * OMNI_H, OMNI_F, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
         free_layer(&next);
         set_err(err, errlen, "cuda: cannot describe Omni expert tensors of layer %d", layer);
         return false;
@@ -478,9 +496,20 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
-    if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
+    const bool fused = g->gemm_impl == 0 && g->fuse_gather;
+    if (!fused && !launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
-    if (g->gemm_impl == 0) {
+    if (fused) {
+        /* gate/up fetches its token rows from xn itself (TMA gather4): no permuted copy */
+        CUtensorMap tm_xrow;
+        if (!make_map(g, &tm_xrow, xn, (uint64_t)rows, OMNI_H, 1, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
+            note_failure(g, "activation row descriptor", cudaErrorInvalidValue);
+            return false;
+        }
+        if (!launched(g, "gate/up experts", omni_launch_gateup_gather_sm100(&L->tm_gate_up, &tm_xrow, s->sort, s->h, g->n_sm, g->stream))) return false;
+        stage_mark(g, 3);
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
+    } else if (g->gemm_impl == 0) {
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
         stage_mark(g, 3);
         if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
@@ -491,6 +520,29 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     }
     stage_mark(g, 4);
     if (!launched(g, "combine", omni_launch_combine(s->d, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
+    stage_mark(g, 5);
+    return true;
+}
+
+/* Expert-parallel variant of run_experts: rows travel to the ranks that own their experts and
+ * back by peer stores; three flag barriers order the phases (omni_ep.cu). */
+static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, const int32_t *ids, const float *weights,
+                           float *x, int rows) {
+    omni_arena *s = g->omni;
+    const int rows8 = rows * OMNI_TOP;
+    const omni_ep_peers *pe = &g->ep.peers;
+    if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
+    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->stream))) return false;
+    if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, g->stream))) return false;
+    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
+    stage_mark(g, 2);
+    if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
+    stage_mark(g, 3);
+    if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
+    stage_mark(g, 4);
+    if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, g->ep.n_local_rows, g->stream))) return false;
+    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
+    if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
     return true;
 }
@@ -513,6 +565,10 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
         return false;
     }
     if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    if (g->ep.world > 1 && T > OMNI_CHUNK) {
+        set_err(err, errlen, "cuda: expert-parallel Omni passes take at most %d tokens per rank", OMNI_CHUNK);
+        return false;
+    }
     const omni_layer *L = &g->layer[layer];
     omni_arena *s = g->omni;
     /* Tokens are independent, so the packed batch is processed in arena-sized chunks
@@ -526,7 +582,8 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
             ok = launched(g, "route capture", omni_launch_trace(s->logits, s->ids, s->weights, rows, start, g->trace_first,
                                                                 g->trace_rows, layer, g->trace, g->stream));
         stage_mark(g, 1);
-        if (ok) ok = run_experts(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows);
+        if (ok) ok = g->ep.world > 1 ? run_experts_ep(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows)
+                                     : run_experts(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows);
         if (!ok) { set_err(err, errlen, "%s", g->fail_msg); return false; }
         book_profile(g);
         g->last_T = rows;
@@ -650,6 +707,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
+    else if (!strcmp(name, "fuse_gather")) g->fuse_gather = value != 0;
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }
     else return false;
@@ -671,4 +729,141 @@ bool clef_omni_profile(clef_gpu *g, float ms[6]) {
     }
     cudaGetLastError();
     return true;
+}
+
+/* ---------------------------------------------------------------- expert parallelism */
+static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
+    if (g->ep.dret) return true;
+    void *dret = dev_alloc(g, (size_t)OMNI_ROWS * OMNI_H * 2);
+    int32_t *rowinfo = dev_alloc(g, (size_t)OMNI_ROWS * 4);
+    int32_t *counts = dev_alloc(g, (size_t)OMNI_EP_MAX * OMNI_E * 4);
+    uint32_t *flags = dev_alloc(g, 256);
+    int32_t *send_base = dev_alloc(g, (size_t)OMNI_E * 4);
+    int32_t *n_local = dev_alloc(g, 256);
+    bool ok = dret && rowinfo && counts && flags && send_base && n_local;
+    if (ok) ok = cudaMemsetAsync(flags, 0, 256, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(counts, 0, (size_t)OMNI_EP_MAX * OMNI_E * 4, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(n_local, 0, 256, g->stream) == cudaSuccess &&
+                 cudaStreamSynchronize(g->stream) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local};
+        for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
+        set_err(err, errlen, "cuda: cannot allocate Omni expert-parallel buffers (previous buffers kept)");
+        return false;
+    }
+    g->ep.dret = dret; g->ep.rowinfo = rowinfo; g->ep.counts = counts; g->ep.flags = flags;
+    g->ep.send_base = send_base; g->ep.n_local_rows = n_local;
+    return true;
+}
+
+static void ep_local_buffers(clef_gpu *g, void *out[OMNI_EP_BUFFERS]) {
+    out[0] = g->omni->xg; out[1] = g->ep.dret; out[2] = g->ep.rowinfo; out[3] = g->ep.counts; out[4] = g->ep.flags;
+}
+
+static void ep_set_peer(omni_ep_peers *pe, int r, void *const buf[OMNI_EP_BUFFERS]) {
+    pe->xg[r] = buf[0]; pe->dret[r] = buf[1]; pe->rowinfo[r] = buf[2]; pe->counts[r] = buf[3]; pe->flags[r] = buf[4];
+}
+
+bool clef_omni_ep_export(clef_gpu *g, clef_omni_ipc_handle out[CLEF_OMNI_EP_HANDLES], char *err, size_t errlen) {
+    if (!g || !g->omni || !out) { set_err(err, errlen, "cuda: Omni arena not reserved"); return false; }
+    cudaSetDevice(g->device);
+    if (!ep_alloc(g, err, errlen)) return false;
+    void *buf[OMNI_EP_BUFFERS];
+    ep_local_buffers(g, buf);
+    for (int i = 0; i < OMNI_EP_BUFFERS; i++) {
+        cudaIpcMemHandle_t h;
+        cudaError_t e = cudaIpcGetMemHandle(&h, buf[i]);
+        if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot export Omni exchange buffer %d: %s", i, cudaGetErrorString(e)); return false; }
+        memcpy(out[i].reserved, &h, sizeof h);
+    }
+    return true;
+}
+
+static bool ep_check(clef_gpu *g, int rank, int world, char *err, size_t errlen) {
+    if (!g || !g->omni) { set_err(err, errlen, "cuda: Omni arena not reserved"); return false; }
+    if (world < 2 || world > OMNI_EP_MAX || (OMNI_E % world) || rank < 0 || rank >= world) {
+        set_err(err, errlen, "cuda: invalid Omni expert-parallel geometry (rank %d of %d)", rank, world);
+        return false;
+    }
+    if (g->ep.world > 1) { set_err(err, errlen, "cuda: Omni expert parallelism already connected"); return false; }
+    for (int l = 0; l < MAX_LAYERS; l++) if (g->layer[l].bound) {
+        set_err(err, errlen, "cuda: connect Omni expert parallelism before binding layer weights");
+        return false;
+    }
+    return true;
+}
+
+bool clef_omni_ep_connect(clef_gpu *g, int rank, int world, const clef_omni_ipc_handle *all, char *err, size_t errlen) {
+    if (!ep_check(g, rank, world, err, errlen)) return false;
+    if (!all) { set_err(err, errlen, "cuda: missing Omni exchange handles"); return false; }
+    cudaSetDevice(g->device);
+    if (!ep_alloc(g, err, errlen)) return false;
+    omni_ep_peers pe;
+    memset(&pe, 0, sizeof pe);
+    pe.rank = rank; pe.world = world;
+    memset(g->ep.opened, 0, sizeof g->ep.opened);
+    for (int r = 0; r < world; r++) {
+        void *buf[OMNI_EP_BUFFERS];
+        if (r == rank) ep_local_buffers(g, buf);
+        else for (int i = 0; i < OMNI_EP_BUFFERS; i++) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, all[r * OMNI_EP_BUFFERS + i].reserved, sizeof h);
+            cudaError_t e = cudaIpcOpenMemHandle(&buf[i], h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                for (int rr = 0; rr <= r; rr++) for (int ii = 0; ii < OMNI_EP_BUFFERS; ii++)
+                    if (g->ep.opened[rr][ii]) { cudaIpcCloseMemHandle(g->ep.opened[rr][ii]); g->ep.opened[rr][ii] = NULL; }
+                set_err(err, errlen, "cuda: cannot map rank %d's Omni exchange buffer %d: %s", r, i, cudaGetErrorString(e));
+                return false;
+            }
+            g->ep.opened[r][i] = buf[i];
+        }
+        ep_set_peer(&pe, r, buf);
+    }
+    g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = true; g->ep.epoch = 0;
+    return true;
+}
+
+bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *const *peers, char *err, size_t errlen) {
+    if (!ep_check(g, rank, world, err, errlen)) return false;
+    if (!peers || peers[rank] != g) { set_err(err, errlen, "cuda: invalid Omni peer list"); return false; }
+    omni_ep_peers pe;
+    memset(&pe, 0, sizeof pe);
+    pe.rank = rank; pe.world = world;
+    for (int r = 0; r < world; r++) {
+        clef_gpu *p = peers[r];
+        if (!p || !p->omni) { set_err(err, errlen, "cuda: Omni peer %d has no arena", r); return false; }
+        cudaSetDevice(p->device);
+        if (!ep_alloc(p, err, errlen)) return false;
+        if (p != g) {
+            cudaSetDevice(g->device);
+            cudaError_t e = cudaDeviceEnablePeerAccess(p->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+                cudaGetLastError();
+                set_err(err, errlen, "cuda: no peer access from device %d to device %d: %s", g->device, p->device, cudaGetErrorString(e));
+                return false;
+            }
+            cudaGetLastError();
+        }
+        void *buf[OMNI_EP_BUFFERS];
+        ep_local_buffers(p, buf);
+        ep_set_peer(&pe, r, buf);
+    }
+    cudaSetDevice(g->device);
+    g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = false; g->ep.epoch = 0;
+    return true;
+}
+
+void clef_omni_ep_disconnect(clef_gpu *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    cudaStreamSynchronize(g->stream);
+    if (g->ep.ipc)
+        for (int r = 0; r < OMNI_EP_MAX; r++) for (int i = 0; i < OMNI_EP_BUFFERS; i++)
+            if (g->ep.opened[r][i]) { cudaIpcCloseMemHandle(g->ep.opened[r][i]); g->ep.opened[r][i] = NULL; }
+    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows};
+    for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
+    memset(&g->ep, 0, sizeof g->ep);
+    cudaGetLastError();
 }

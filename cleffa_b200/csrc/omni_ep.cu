@@ -1,0 +1,198 @@
+// Expert parallelism for the Clef-Omni MoE block over the GPUs of one NVLink/NVSwitch node.
+//
+// The reference is single-device; this stage has no counterpart there.  Experts are sharded in
+// contiguous id ranges (E/G per GPU), tokens are data-parallel.  Instead of a library
+// all-to-all, rows move by plain peer stores into buffers that every rank has mapped from every
+// other rank, so the permutation and the transfer are one kernel each way:
+//
+//   counts   every rank writes its 128 per-expert counts into every peer's count table, then a
+//            flag barrier; from the table each rank derives, with no further communication,
+//            where its rows land on the owners (source-rank-major inside each expert = the
+//            canonical global assignment order) and the owner derives its local tile list.
+//   dispatch one warp per permuted row copies the token's 4 KiB activation row straight into
+//            the owner's expert-major buffer and records (source rank, source row) beside it.
+//   return   after the expert products the owner copies each result row back to the source
+//            rank's buffer at the source's own permuted position, so the unchanged combine
+//            kernel finds it through `slots`.
+//
+// Cross-GPU ordering uses one monotonically increasing epoch per barrier and system-scope
+// release/acquire on flag words; every spin is bounded (1 s) and reports OMNI_ST_TIMEOUT
+// through the status word instead of hanging.  No TMA or multicast touches peer memory: remote
+// rows land in local HBM first and the GEMM kernels read them from there.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "omni_internal.h"
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+constexpr uint64_t SPIN_LIMIT_NS = 1000000000ull;
+
+__device__ __forceinline__ uint64_t now_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One block.  Every rank tells every peer "I reached epoch E", then waits until all peers
+// said so.  Writes made by earlier kernels of this stream are ordered before the flag by the
+// system-scope fence.
+__device__ void flag_barrier(const omni_ep_peers &pe, uint32_t epoch, uint32_t *status) {
+    __threadfence_system();
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t < pe.world) st_release_sys(pe.flags[t] + pe.rank, epoch);
+    if (t < pe.world) {
+        const uint32_t *mine = pe.flags[pe.rank] + t;
+        const uint64_t t0 = now_ns();
+        // epochs only grow; '>=' in wrap-safe form
+        while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+            if (now_ns() - t0 > SPIN_LIMIT_NS) { atomicOr(status, OMNI_ST_TIMEOUT); break; }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(128) ep_barrier_kernel(omni_ep_peers pe, uint32_t epoch, uint32_t *status) {
+    flag_barrier(pe, epoch, status);
+}
+
+// Publish my counts, barrier, then plan.  One block of 128 threads, thread e = expert e.
+__global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint32_t epoch, omni_sort_state st,
+                                                         int32_t *send_base, int32_t *n_local_rows) {
+    __shared__ int tot[OMNI_E], scan[OMNI_E], tiles[OMNI_E];
+    const int e = threadIdx.x;
+    const int G = pe.world, EL = OMNI_E / G;
+    const int mine = st.counts[e];
+    for (int p = 0; p < G; p++) pe.counts[p][pe.rank * OMNI_E + e] = mine;
+    flag_barrier(pe, epoch, st.status);
+    // table[s][e] = rows rank s routes to expert e
+    const int32_t *table = pe.counts[pe.rank];
+    int total = 0, before_me = 0;
+    for (int s = 0; s < G; s++) {
+        const int c = __ldcv(table + s * OMNI_E + e);     // written by peers: bypass L1
+        if (s < pe.rank) before_me += c;
+        total += c;
+    }
+    tot[e] = total;
+    __syncthreads();
+    // base of expert e inside its owner's buffer: totals of the owner's earlier experts
+    const int owner = e / EL, first = owner * EL;
+    int base = 0;
+    for (int o = first; o < e; o++) base += tot[o];
+    send_base[e] = base + before_me;
+    // the owner's view: local experts first..first+EL-1 of THIS rank
+    const int le = e;                       // threads 0..EL-1 act for local expert le
+    int n = 0, nt = 0;
+    if (le < EL) { n = tot[pe.rank * EL + le]; nt = (n + OMNI_TILE_N - 1) / OMNI_TILE_N; }
+    scan[e] = n; tiles[e] = nt;
+    __syncthreads();
+    if (e == 0) {                           // EL <= 128: a serial scan over the local experts is short
+        int rows = 0, t = 0;
+        for (int l = 0; l < EL; l++) { const int c = scan[l], k = tiles[l]; scan[l] = rows; tiles[l] = t; rows += c; t += k; }
+        *n_local_rows = rows;
+        *st.n_ttiles = rows <= OMNI_ROWS ? t : 0;
+        st.sched[0] = 0; st.sched[1] = 0;
+        if (rows > OMNI_ROWS) atomicOr(st.status, OMNI_ST_EP_OVERFLOW);
+    }
+    __syncthreads();
+    if (le < EL && *n_local_rows <= OMNI_ROWS) {
+        const int off = scan[le], firstt = tiles[le];
+        for (int j = 0; j < nt; j++) {
+            const int len = min(OMNI_TILE_N, n - j * OMNI_TILE_N);
+            st.ttiles[firstt + j] = omni_ttile{le, off + j * OMNI_TILE_N, len, firstt | (nt << 16)};
+        }
+    }
+}
+
+__device__ __forceinline__ int expert_of_row(const int32_t *offsets, int row) {
+    int lo = 0, hi = OMNI_E;
+    while (lo + 1 < hi) { const int mid = (lo + hi) >> 1; if (offsets[mid] <= row) lo = mid; else hi = mid; }
+    return lo;
+}
+
+// One warp per permuted row of this rank: 4 KiB to the owner's buffer + its origin tag.
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(omni_ep_peers pe, const uint4 *__restrict__ xn,
+                                                          const int32_t *__restrict__ rowmap,
+                                                          const int32_t *__restrict__ offsets,
+                                                          const int32_t *__restrict__ send_base, int rows8) {
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * 8;
+    const int EL = OMNI_E / pe.world;
+    for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < rows8; r += warps) {
+        const int e = expert_of_row(offsets, r);
+        const int owner = e / EL;
+        const long dst = (long)send_base[e] + (r - offsets[e]);
+        if (dst >= OMNI_ROWS) continue;                     // owner overflow: flagged by its plan kernel
+        const uint4 *src = xn + (long)rowmap[r] * (OMNI_H / 8);
+        uint4 *out = reinterpret_cast<uint4 *>(pe.xg[owner]) + dst * (OMNI_H / 8);
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __ldg(src + lane + 32 * i);
+#pragma unroll
+        for (int i = 0; i < 8; i++) out[lane + 32 * i] = v[i];
+        if (lane == 0) pe.rowinfo[owner][dst] = (pe.rank << 20) | r;
+    }
+}
+
+// One warp per local expert-major row: result row back to the source rank's permuted position.
+__global__ void __launch_bounds__(256) ep_return_kernel(omni_ep_peers pe, const uint4 *__restrict__ d,
+                                                        const int32_t *__restrict__ rowinfo,
+                                                        const int32_t *__restrict__ n_local_rows) {
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * 8;
+    int n = *n_local_rows;
+    if (n > OMNI_ROWS) n = 0;
+    for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < n; r += warps) {
+        const int info = rowinfo[r];
+        const int src_rank = info >> 20, src_row = info & 0xfffff;
+        const uint4 *src = d + (long)r * (OMNI_H / 8);
+        uint4 *out = reinterpret_cast<uint4 *>(pe.dret[src_rank]) + (long)src_row * (OMNI_H / 8);
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = src[lane + 32 * i];
+#pragma unroll
+        for (int i = 0; i < 8; i++) out[lane + 32 * i] = v[i];
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
+                                int32_t *n_local_rows, cudaStream_t s) {
+    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, cudaStream_t s) {
+    ep_barrier_kernel<<<1, 128, 0, s>>>(*pe, epoch, status);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
+                                    const int32_t *send_base, int rows8, cudaStream_t s) {
+    int blocks = (rows8 + 7) / 8;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    ep_dispatch_kernel<<<blocks, 256, 0, s>>>(*pe, (const uint4 *)xn, rowmap, offsets, send_base, rows8);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
+                                  const int32_t *n_local_rows, cudaStream_t s) {
+    ep_return_kernel<<<148 * 8, 256, 0, s>>>(*pe, (const uint4 *)d, rowinfo, n_local_rows);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

@@ -22,7 +22,7 @@ enum {
 };
 
 /* status word bits (clef_omni_complete) */
-enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_RECHECK_OVERFLOW = 32u };
+enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_EP_OVERFLOW = 32u };
 
 /* One token tile of one expert: rows [row0, row0+len) of the permuted buffers. */
 /* group = index of the expert's first tile | (its tile count << 16) */
@@ -40,6 +40,17 @@ typedef struct {
     int32_t *sched;        /* [2] work counters of the two expert-product kernels, zeroed by the scan */
     uint32_t *status;      /* [1]                                     */
 } omni_sort_state;
+
+/* Expert parallelism: every rank's view of every rank's exchange buffers (index = rank). */
+enum { OMNI_EP_MAX = 8, OMNI_EP_BUFFERS = 5 };
+typedef struct {
+    int32_t rank, world;
+    void *xg[OMNI_EP_MAX];          /* [ROWS][2048] bf16: token rows received, expert-major      */
+    void *dret[OMNI_EP_MAX];        /* [ROWS][2048] bf16: expert outputs returned, source order  */
+    int32_t *rowinfo[OMNI_EP_MAX];  /* [ROWS] (source rank << 20) | source permuted row          */
+    int32_t *counts[OMNI_EP_MAX];   /* [EP_MAX][128] per-expert counts of every rank             */
+    uint32_t *flags[OMNI_EP_MAX];   /* [EP_MAX] barrier epochs, written by the peers             */
+} omni_ep_peers;
 
 /* ---- plain kernels (omni_kernels.cu) ---- */
 cudaError_t omni_launch_router_simple(const void *xn, const void *router, const float *bias, int T,
@@ -75,8 +86,20 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
 /* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, int n_sm, cudaStream_t s);
+/* tm_xrow: the activation matrix [T][2048] with box {64, 1} for TMA gather4; st.rowmap gives the rows */
+cudaError_t omni_launch_gateup_gather_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_xrow, const omni_sort_state st,
+                                            void *h, int n_sm, cudaStream_t s);
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                    void *d, int n_sm, cudaStream_t s);
+
+/* ---- expert parallel (omni_ep.cu) ---- */
+cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
+                                int32_t *n_local_rows, cudaStream_t s);
+cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, cudaStream_t s);
+cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
+                                    const int32_t *send_base, int rows8, cudaStream_t s);
+cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
+                                  const int32_t *n_local_rows, cudaStream_t s);
 
 #ifdef __cplusplus
 }

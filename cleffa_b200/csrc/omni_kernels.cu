@@ -151,61 +151,74 @@ __device__ __forceinline__ XRow load_xrow(const __nv_bfloat16 *xn, long row, int
 // accurate to ~1e-13, far inside the 1e-9 bound of tests/test_omni_router.m:44.
 __device__ __forceinline__ double exact_dot(const XRow &x, const __nv_bfloat16 *wrow, int lane) {
     const uint4 *p = reinterpret_cast<const uint4 *>(wrow);
-    double acc = 0.0;
+    uint4 w[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = __ldg(p + lane + 32 * i);
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};      // four chains: the FP64 adds overlap instead of serialising
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const uint4 w = __ldg(p + lane + 32 * i);
         const uint32_t xu[4] = {x.q[i].x, x.q[i].y, x.q[i].z, x.q[i].w};
-        const uint32_t wu[4] = {w.x, w.y, w.z, w.w};
+        const uint32_t wu[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            acc += (double)(bf16_bits_to_float(xu[j] & 0xffffu) * bf16_bits_to_float(wu[j] & 0xffffu));
-            acc += (double)(bf16_bits_to_float(xu[j] >> 16) * bf16_bits_to_float(wu[j] >> 16));
+            acc[j] += (double)(bf16_bits_to_float(xu[j] & 0xffffu) * bf16_bits_to_float(wu[j] & 0xffffu));
+            acc[j] += (double)(bf16_bits_to_float(xu[j] >> 16) * bf16_bits_to_float(wu[j] >> 16));
         }
     }
+    double sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(FULL, acc, s);
-    return acc;
+    for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(FULL, sum, s);
+    return sum;
 }
 
-// One warp per flagged row: exact logits for every expert that can still reach the top
-// eight (approximate logit within 2*eps of the approximate 8th), then the final order.
+// One block (four warps) per flagged row: exact logits for every expert that can still reach
+// the top eight (approximate logit within 2*eps of the approximate 8th), spread over the
+// warps, then the final order by warp 0.
 __global__ void __launch_bounds__(128) recheck_kernel(const __nv_bfloat16 *__restrict__ xn,
                                                       const __nv_bfloat16 *__restrict__ w,
                                                       const float *__restrict__ bias, const float *__restrict__ logits,
                                                       const int32_t *__restrict__ flag_rows,
                                                       const int32_t *__restrict__ n_flag, int T, float eps,
                                                       int32_t *__restrict__ ids, float *__restrict__ weights) {
-    const int lane = threadIdx.x & 31;
-    const int warps = gridDim.x * 4;
+    __shared__ double exact_s[OMNI_E];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int n = *n_flag;
     if (n > T) n = T;
-    for (int f = blockIdx.x * 4 + (threadIdx.x >> 5); f < n; f += warps) {
+    for (int f = blockIdx.x; f < n; f += gridDim.x) {
         const long row = flag_rows[f];
+        exact_s[threadIdx.x] = -CUDART_INF;
         double val[4], approx[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) approx[j] = val[j] = (double)logits[row * OMNI_E + lane + 32 * j];
         double top_v[8]; int top_id[8];
-        warp_topn<8>(val, lane, top_v, top_id);
+        warp_topn<8>(val, lane, top_v, top_id);               // every warp finds the same threshold
         const double floor_v = top_v[7] - 2.0 * (double)eps;
         const XRow x = load_xrow(xn, row, lane);
-        double exact[4];
+        __syncthreads();
+        int c = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            exact[j] = -CUDART_INF;
             unsigned m = __ballot_sync(FULL, approx[j] >= floor_v);
             while (m) {
                 const int src = __ffs(m) - 1;
                 m &= m - 1;
+                if ((c++ & 3) != warp) continue;              // candidates round-robin over the warps
                 const int e = src + 32 * j;
                 double v = exact_dot(x, w + (long)e * OMNI_H, lane);
                 if (bias) v += (double)bias[e];
-                if (lane == src) exact[j] = v;
+                if (lane == 0) exact_s[e] = v;
             }
         }
-        double fin_v[9]; int fin_id[9];
-        warp_topn<9>(exact, lane, fin_v, fin_id);   // the 9th is unused here
-        write_selection(fin_v, fin_id, lane, ids, weights, row);
+        __syncthreads();
+        if (warp == 0) {
+            double exact[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) exact[j] = exact_s[lane + 32 * j];
+            double fin_v[9]; int fin_id[9];
+            warp_topn<9>(exact, lane, fin_v, fin_id);         // the 9th is unused here
+            write_selection(fin_v, fin_id, lane, ids, weights, row);
+        }
+        __syncthreads();
     }
 }
 
@@ -521,8 +534,7 @@ cudaError_t omni_launch_recheck(const void *xn, const void *router, const float 
                                 const int32_t *flag_rows, const int32_t *n_flag, int T, float eps, int32_t *ids,
                                 float *weights, uint32_t *status, cudaStream_t s) {
     (void)status;
-    int blocks = (T + 3) / 4;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    int blocks = T < 148 * 8 ? T : 148 * 8;
     recheck_kernel<<<blocks, 128, 0, s>>>((const __nv_bfloat16 *)xn, (const __nv_bfloat16 *)router, bias, logits,
                                           flag_rows, n_flag, T, eps, ids, weights);
     return cudaGetLastError();

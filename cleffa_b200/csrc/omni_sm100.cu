@@ -95,6 +95,15 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
 }
+// Four rows picked by index from a 2-D tensor (box {64, 1}), written as four consecutive
+// 128-byte rows of the swizzled tile.
+__device__ __forceinline__ void tma_gather4_hint(uint32_t dst, const CUtensorMap *map, int x, int r0, int r1, int r2, int r3,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -198,11 +207,18 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(
 struct WorkSlot { int expert, row0, len, m; };
 constexpr int RING = 4;
 
-template <int MODE>
+//
+// GATHER (gate/up only): the token rows are not read from a permuted copy but fetched from the
+// activation matrix itself with TMA gather4, four rows per instruction, by the 32 lanes of the
+// producer warp (row indices come from the row map of the counting sort).  This removes the
+// permuted copy from HBM altogether; the activations (16.8 MB at T=4096) stay in L2.
+template <int MODE, bool GATHER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ TokMaps tm_tok,
                    const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
-                   int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
+                   int32_t *__restrict__ work_counter, const int32_t *__restrict__ rowmap,
+                   __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
+    static_assert(!GATHER || MODE == MODE_GATEUP, "only the gate/up product gathers its token rows");
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
     constexpr int STAGE_BYTES = GemmSmem<MODE>::STAGE_BYTES;
@@ -243,42 +259,84 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
+    if (warp == 0 && (GATHER || lane == 0)) {
         // ---------------------------------------------------------- scheduler + TMA producer
+        // Lane 0 claims work and issues the tiled loads; with GATHER all 32 lanes stay in the
+        // loop and each issues its share of the gather4 loads.
         PipeState p, wr;
-        const uint64_t pol_w = l2_policy_evict_first(), pol_t = l2_policy_evict_last();
-        int cur = atomicAdd(work_counter, 1);
+        const uint64_t pol_w1 = l2_policy_evict_first(), pol_t = l2_policy_evict_last();
+        int cur = 0;
+        if (lane == 0) cur = atomicAdd(work_counter, 1);
         for (;;) {
-            if (!mbar_wait(wempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) break;
-            if (cur >= n_work) {
-                ring[wr.stage].len = -1;                      // tells the consumers to stop
-                mbar_arrive(wfull_bar(wr.stage));
-                break;
+            int expert = 0, row0 = 0, len = -2, m = 0, cnt = 1, next = 0;
+            if (lane == 0) {
+                if (mbar_wait(wempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) {
+                    if (cur >= n_work) {
+                        ring[wr.stage].len = -1;              // tells the consumers to stop
+                        mbar_arrive(wfull_bar(wr.stage));
+                        len = -1;
+                    } else {
+                        // item -> (expert group, weight tile m, token tile j): see assign_scan_kernel
+                        const omni_ttile t0 = ttiles[cur / C::MTILES];
+                        const int first = t0.group & 0xffff;
+                        cnt = t0.group >> 16;
+                        const int local = cur - first * C::MTILES;
+                        m = local / cnt;
+                        const omni_ttile tt = ttiles[first + local % cnt];
+                        expert = tt.expert; row0 = tt.row0; len = tt.len;
+                        ring[wr.stage].expert = expert; ring[wr.stage].row0 = row0;
+                        ring[wr.stage].len = len; ring[wr.stage].m = m;
+                        mbar_arrive(wfull_bar(wr.stage));
+                        wr.advance(RING);
+                        next = atomicAdd(work_counter, 1);    // claimed early: its latency hides behind the loads below
+                    }
+                }
             }
-            // item -> (expert group, weight tile m, token tile j): see assign_scan_kernel
-            const omni_ttile t0 = ttiles[cur / C::MTILES];
-            const int first = t0.group & 0xffff, cnt = t0.group >> 16;
-            const int local = cur - first * C::MTILES;
-            const int m = local / cnt;
-            const omni_ttile tt = ttiles[first + local % cnt];
-            ring[wr.stage].expert = tt.expert; ring[wr.stage].row0 = tt.row0;
-            ring[wr.stage].len = tt.len; ring[wr.stage].m = m;
-            mbar_arrive(wfull_bar(wr.stage));
-            wr.advance(RING);
-            const int next = atomicAdd(work_counter, 1);      // claimed early: its latency hides behind the loads below
-            const int bi = tok_box_index(tt.len);
-            const uint32_t bytes = C::NACC * A_TILE_BYTES + (32u << bi) * (BK * 2);
-            const int wrow = tt.expert * C::W_ROWS_PER_EXPERT + m * 128;
+            if (GATHER) {
+                row0 = __shfl_sync(0xffffffffu, row0, 0);
+                len = __shfl_sync(0xffffffffu, len, 0);
+            }
+            if (len < 0) break;                               // -1: no more work, -2: a wait ran out
+            const int bi = tok_box_index(len);
+            const int ngather = (len + 3) >> 2;               // gather4 instructions per stage
+            const uint32_t bytes = C::NACC * A_TILE_BYTES + (GATHER ? ngather * 512u : (32u << bi) * (BK * 2));
+            const int wrow = expert * C::W_ROWS_PER_EXPERT + m * 128;
+            // a weight tile is read once per token tile of its expert: keep it in L2 while
+            // the expert's other token tiles (claimed by neighbouring CTAs) still need it
+            const uint64_t pol_w = cnt > 1 ? pol_t : pol_w1;
+            int tok[2][4];                                     // this lane's source rows: groups lane and lane+32
+            if (GATHER) {
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int r = 4 * (lane + 32 * h) + i;
+                        tok[h][i] = rowmap[row0 + (r < len ? r : len - 1)];
+                    }
+            }
             bool ok = true;
             for (int ks = 0; ks < KSTAGES; ks++) {
-                ok = mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
+                if (lane == 0) ok = mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
+                if (GATHER) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                 if (!ok) break;
                 const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
-                armed[p.stage] = (int)p.phase;
-                mbar_expect_tx(full_bar(p.stage), bytes);
-                tma_load_2d_hint(sa, &tm_w, ks * BK, wrow, full_bar(p.stage), pol_w);
-                if (C::NACC == 2) tma_load_2d_hint(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, full_bar(p.stage), pol_w);
-                tma_load_2d_hint(sa + C::NACC * A_TILE_BYTES, &tm_tok.m[bi], ks * BK, tt.row0, full_bar(p.stage), pol_t);
+                if (lane == 0) {
+                    armed[p.stage] = (int)p.phase;
+                    mbar_expect_tx(full_bar(p.stage), bytes);
+                    tma_load_2d_hint(sa, &tm_w, ks * BK, wrow, full_bar(p.stage), pol_w);
+                    if (C::NACC == 2) tma_load_2d_hint(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, full_bar(p.stage), pol_w);
+                    if (!GATHER) tma_load_2d_hint(sa + C::NACC * A_TILE_BYTES, &tm_tok.m[bi], ks * BK, row0, full_bar(p.stage), pol_t);
+                }
+                if (GATHER) {
+                    const uint32_t sb = sa + C::NACC * A_TILE_BYTES;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int gidx = lane + 32 * h;
+                        if (gidx < ngather)
+                            tma_gather4_hint(sb + gidx * 512, &tm_tok.m[0], ks * BK, tok[h][0], tok[h][1], tok[h][2], tok[h][3],
+                                             full_bar(p.stage), pol_t);
+                    }
+                }
                 p.advance(C::STAGES);
             }
             if (!ok) break;
@@ -425,6 +483,19 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 }
 
 // ====================================================================== router
+template <int LO, int N>
+__device__ __forceinline__ void argmax_range(const float (&v)[OMNI_E], float &bv, int &bi) {
+    if constexpr (N == 1) { bv = v[LO]; bi = LO; }
+    else {
+        float lv, rv; int li, ri;
+        argmax_range<LO, N / 2>(v, lv, li);
+        argmax_range<LO + N / 2, N / 2>(v, rv, ri);
+        const bool right = rv > lv;
+        bv = right ? rv : lv;
+        bi = right ? ri : li;
+    }
+}
+
 constexpr int RT_STAGES = 6;
 constexpr int RT_STAGE_BYTES = 2 * A_TILE_BYTES;        // 128 token rows + 128 expert rows, 64 K each
 constexpr int RT_THREADS = 256;                         // warp 0 TMA, 1 MMA, 2 TMEM, 3 spare, 4..7 epilogue
@@ -535,17 +606,27 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     ip[0] = make_int4(0, 1, 2, 3); ip[1] = make_int4(4, 5, 6, 7);
                     wp[0] = make_float4(0.f, 0.f, 0.f, 0.f); wp[1] = wp[0];
                 } else {
-                    // nine rounds of arg-max in registers; strict '>' keeps the lowest id on ties
-                    float tv[9]; int ti[9];
-#pragma unroll
+                    // Nine rounds of arg-max over the 128 registers as a balanced tournament
+                    // (depth 7, so the compare/select chains overlap); the right child wins
+                    // only on strict '>', which keeps the lowest expert id on ties.  The round
+                    // is a real loop: unrolled nine times its ~90 KB of straight-line code
+                    // made the epilogue instruction-fetch bound.  Results go through shared
+                    // memory (the pipeline stages are idle by now) to keep `r` out of register
+                    // indexing.
+                    float *sel_v = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+                    int *sel_i = reinterpret_cast<int *>(sel_v + 9 * 128);
+                    const int et = threadIdx.x - 128;
+#pragma unroll 1
                     for (int r = 0; r < 9; r++) {
-                        float bv = v[0]; int bi = 0;
-#pragma unroll
-                        for (int i = 1; i < OMNI_E; i++) if (v[i] > bv) { bv = v[i]; bi = i; }
-                        tv[r] = bv; ti[r] = bi;
+                        float bv; int bi;
+                        argmax_range<0, OMNI_E>(v, bv, bi);
+                        sel_v[r * 128 + et] = bv; sel_i[r * 128 + et] = bi;
 #pragma unroll
                         for (int i = 0; i < OMNI_E; i++) if (i == bi) v[i] = -CUDART_INF_F;
                     }
+                    float tv[9]; int ti[9];
+#pragma unroll
+                    for (int r = 0; r < 9; r++) { tv[r] = sel_v[r * 128 + et]; ti[r] = sel_i[r * 128 + et]; }
                     bool close = exact_all != 0;
 #pragma unroll
                     for (int k = 0; k < 8; k++) close |= (tv[k] - tv[k + 1]) < 2.f * eps;
@@ -587,10 +668,13 @@ extern "C" {
 
 cudaError_t omni_sm100_configure(void) {
     cudaError_t e;
-    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmSmem<MODE_GATEUP>::TOTAL_BYTES);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmSmem<MODE_GATEUP>::TOTAL_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_DOWN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmSmem<MODE_DOWN>::TOTAL_BYTES);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(router_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);
@@ -609,8 +693,17 @@ cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap 
                                      void *h, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
-    expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status);
+    expert_gemm_kernel<MODE_GATEUP, false><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, nullptr, (__nv_bfloat16 *)h, st.status);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_gateup_gather_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_xrow, const omni_sort_state st,
+                                            void *h, int n_sm, cudaStream_t s) {
+    TokMaps tok;
+    for (int i = 0; i < 4; i++) tok.m[i] = *tm_xrow;
+    expert_gemm_kernel<MODE_GATEUP, true><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, st.rowmap, (__nv_bfloat16 *)h, st.status);
     return cudaGetLastError();
 }
 
@@ -618,8 +711,8 @@ cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *t
                                    void *d, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
-    expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1, (__nv_bfloat16 *)d, st.status);
+    expert_gemm_kernel<MODE_DOWN, false><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1, nullptr, (__nv_bfloat16 *)d, st.status);
     return cudaGetLastError();
 }
 

@@ -35,7 +35,9 @@ EXPORTS = [
     "clef_omni_bind_layer", "clef_omni_encode_moe", "clef_omni_forward_host", "clef_omni_stage_router",
     "clef_omni_stage_route", "clef_omni_stage_assign", "clef_omni_stage_experts", "clef_omni_read",
     "clef_omni_set_option", "clef_omni_profile", "clef_omni_arena_bytes",
+    "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
 ]
+EP_HANDLES, EP_HANDLE_BYTES = 5, 64
 
 
 def load_library(path: Path | None = None) -> C.CDLL:
@@ -65,6 +67,10 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_set_option": (C.c_bool, [vp, cc, C.c_long]),
         "clef_omni_profile": (C.c_bool, [vp, C.POINTER(C.c_float)]),
         "clef_omni_arena_bytes": (cz, [vp]),
+        "clef_omni_ep_export": (C.c_bool, [vp, vp, cc, cz]),
+        "clef_omni_ep_connect": (C.c_bool, [vp, ci, ci, vp, cc, cz]),
+        "clef_omni_ep_connect_local": (C.c_bool, [vp, ci, ci, C.POINTER(vp), cc, cz]),
+        "clef_omni_ep_disconnect": (None, [vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -142,7 +148,8 @@ class OmniBackend:
         (and kept alive by this object)."""
         if where is None:
             where = DEVICE if isinstance(router, torch.Tensor) and router.is_cuda else HOST
-        for t, shape in ((router, (E, H)), (gate_up, (E, 2 * F, H)), (down, (E, H, F))):
+        n_local = gate_up.shape[0]      # 128, or the rank's slice for device tensors under expert parallelism
+        for t, shape in ((router, (E, H)), (gate_up, (n_local, 2 * F, H)), (down, (n_local, H, F))):
             if tuple(t.shape) != shape or t.dtype != torch.bfloat16:
                 raise ValueError(f"expected bfloat16 {shape}, got {t.dtype} {tuple(t.shape)}")
         if bias is not None and (tuple(bias.shape) != (E,) or bias.dtype != torch.float32):
@@ -218,6 +225,28 @@ class OmniBackend:
             out = np.empty(1, np.uint32 if what == "status" else np.int32)
         self._check(self.lib.clef_omni_read(self._g, what.encode(), _ptr(out), out.nbytes, self._err, _ERRLEN))
         return out
+
+    # -- expert parallelism
+    def ep_export(self) -> bytes:
+        """This rank's exchange-buffer handles (5 x 64 bytes) for the other ranks."""
+        buf = C.create_string_buffer(EP_HANDLES * EP_HANDLE_BYTES)
+        self._check(self.lib.clef_omni_ep_export(self._g, buf, self._err, _ERRLEN))
+        return buf.raw
+
+    def ep_connect(self, rank: int, world: int, all_handles: bytes):
+        """all_handles: the ep_export() bytes of every rank, concatenated in rank order."""
+        if len(all_handles) != world * EP_HANDLES * EP_HANDLE_BYTES:
+            raise ValueError("need one handle block per rank")
+        buf = C.create_string_buffer(all_handles, len(all_handles))
+        self._check(self.lib.clef_omni_ep_connect(self._g, rank, world, buf, self._err, _ERRLEN))
+
+    def ep_connect_local(self, rank: int, world: int, backends):
+        """Ranks that live in this process: backends[r] is rank r's OmniBackend."""
+        arr = (C.c_void_p * world)(*[b._g for b in backends])
+        self._check(self.lib.clef_omni_ep_connect_local(self._g, rank, world, arr, self._err, _ERRLEN))
+
+    def ep_disconnect(self):
+        self.lib.clef_omni_ep_disconnect(self._g)
 
     def set_option(self, name: str, value: int):
         if not self.lib.clef_omni_set_option(self._g, name.encode(), int(value)):

@@ -62,7 +62,8 @@ void clef_omni_begin(clef_gpu *g);
 /* clef_omni_complete (clef_metal_omni.m:161-167): waits for the stream, then reports a
  * nonzero status word as an error.  Bit 0: nonfinite router values (clef.metal:2364).
  * Bit 3: an expert id outside [0,128) reached the permutation.  Bit 4: a bounded device-side
- * wait ran out.  A failed launch or stream error is reported here too. */
+ * wait ran out.  Bit 5: more rows were routed to one rank than its buffers hold (expert
+ * parallel only).  A failed launch or stream error is reported here too. */
 bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen);
 /* clef_omni_keepalive (clef_metal_omni.m:138-147): read-only touch of every arena buffer. */
 void clef_omni_keepalive(clef_gpu *g);
@@ -104,6 +105,28 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
  * activations live in host memory. */
 bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
                             const int32_t *seq_bounds, char *err, size_t errlen);
+
+/* ---- expert parallelism over the GPUs of one node (no counterpart in the reference, which
+ *      is single-device; defined by the 1/2/4/8-GPU configurations) -------------------- */
+
+/* The 128 experts are sharded in contiguous ranges of 128/world per rank; tokens stay with the
+ * rank that owns them.  Rows travel by peer stores into buffers each rank exports to the others
+ * (CUDA IPC between processes, direct peer access inside one process).  Order of calls on
+ * every rank: open, reserve, ep_export, [exchange handles], ep_connect, bind_layer, then
+ * begin / encode_moe / complete as usual; every rank must make the same sequence of encode_moe
+ * calls (T <= 16384 per call, T may differ per rank).  After connect:
+ *   - bind_layer with CLEF_OMNI_HOST uploads only the rank's expert slice (router in full);
+ *     with CLEF_OMNI_DEVICE gate_up/down must already be the rank's slice
+ *     [128/world][1536][2048] and [128/world][2048][768].
+ *   - results are bitwise those of the single-GPU path on the same tokens. */
+typedef struct { unsigned char reserved[64]; } clef_omni_ipc_handle;
+enum { CLEF_OMNI_EP_HANDLES = 5, CLEF_OMNI_EP_MAX_WORLD = 8 };
+bool clef_omni_ep_export(clef_gpu *g, clef_omni_ipc_handle out[CLEF_OMNI_EP_HANDLES], char *err, size_t errlen);
+/* all = world x CLEF_OMNI_EP_HANDLES handles, rank-major, as exported by every rank */
+bool clef_omni_ep_connect(clef_gpu *g, int rank, int world, const clef_omni_ipc_handle *all, char *err, size_t errlen);
+/* same, for contexts that live in one process: peers[r] is rank r's context */
+bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *const *peers, char *err, size_t errlen);
+void clef_omni_ep_disconnect(clef_gpu *g);
 
 /* ---- stage entry points (model-free tests, mirroring tests/test_omni_*.m) ---------- */
 
