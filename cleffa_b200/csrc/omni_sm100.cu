@@ -483,17 +483,41 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 }
 
 // ====================================================================== router
-template <int LO, int N>
-__device__ __forceinline__ void argmax_range(const float (&v)[OMNI_E], float &bv, int &bi) {
-    if constexpr (N == 1) { bv = v[LO]; bi = LO; }
-    else {
-        float lv, rv; int li, ri;
-        argmax_range<LO, N / 2>(v, lv, li);
-        argmax_range<LO + N / 2, N / 2>(v, rv, ri);
-        const bool right = rv > lv;
-        bv = right ? rv : lv;
-        bi = right ? ri : li;
-    }
+// Top-9 of 128 per thread without data-dependent branches or predicates: logits become
+// order-preserving unsigned keys whose low 7 bits carry (127 - expert id); bitonic networks of
+// min/max sort eight groups of 16 and merge them, keeping the best 16 each time.  Equal values
+// order by lower id.  The 7 borrowed bits cost a relative 2^-16 in the comparison, which the
+// near-tie threshold accounts for; selected values are re-read at full precision afterwards.
+__device__ __forceinline__ void ce_desc(uint32_t &x, uint32_t &y) { const uint32_t hi = max(x, y), lo = min(x, y); x = hi; y = lo; }
+
+template <int OFF>
+__device__ __forceinline__ void sort16_desc(uint32_t (&k)[OMNI_E]) {
+#pragma unroll
+    for (int size = 2; size <= 16; size <<= 1)
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1)
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int l = i ^ stride;
+                if (l > i) {
+                    if ((i & size) == 0) ce_desc(k[OFF + i], k[OFF + l]);
+                    else ce_desc(k[OFF + l], k[OFF + i]);
+                }
+            }
+}
+
+// k[A..A+16) and k[B..B+16) sorted descending -> k[A..A+16) = their best 16, sorted descending
+template <int A, int B>
+__device__ __forceinline__ void merge_top16(uint32_t (&k)[OMNI_E]) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) k[A + i] = max(k[A + i], k[B + 15 - i]);
+#pragma unroll
+    for (int stride = 8; stride > 0; stride >>= 1)
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int l = i ^ stride;
+            if (l > i) ce_desc(k[A + i], k[A + l]);
+        }
 }
 
 constexpr int RT_STAGES = 6;
@@ -606,30 +630,31 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     ip[0] = make_int4(0, 1, 2, 3); ip[1] = make_int4(4, 5, 6, 7);
                     wp[0] = make_float4(0.f, 0.f, 0.f, 0.f); wp[1] = wp[0];
                 } else {
-                    // Nine rounds of arg-max over the 128 registers as a balanced tournament
-                    // (depth 7, so the compare/select chains overlap); the right child wins
-                    // only on strict '>', which keeps the lowest expert id on ties.  The round
-                    // is a real loop: unrolled nine times its ~90 KB of straight-line code
-                    // made the epilogue instruction-fetch bound.  Results go through shared
-                    // memory (the pipeline stages are idle by now) to keep `r` out of register
-                    // indexing.
-                    float *sel_v = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
-                    int *sel_i = reinterpret_cast<int *>(sel_v + 9 * 128);
+                    // keep the full-precision row in shared memory (the pipeline stages are
+                    // idle by now): column layout, so a thread's dynamic index never conflicts
+                    float *col = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
                     const int et = threadIdx.x - 128;
-#pragma unroll 1
-                    for (int r = 0; r < 9; r++) {
-                        float bv; int bi;
-                        argmax_range<0, OMNI_E>(v, bv, bi);
-                        sel_v[r * 128 + et] = bv; sel_i[r * 128 + et] = bi;
+                    uint32_t key[OMNI_E];
 #pragma unroll
-                        for (int i = 0; i < OMNI_E; i++) if (i == bi) v[i] = -CUDART_INF_F;
+                    for (int i = 0; i < OMNI_E; i++) {
+                        col[i * 128 + et] = v[i];
+                        const uint32_t u = __float_as_uint(v[i]);
+                        const uint32_t ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                        key[i] = (ord & ~127u) | (uint32_t)(127 - i);
                     }
+                    sort16_desc<0>(key); sort16_desc<16>(key); sort16_desc<32>(key); sort16_desc<48>(key);
+                    sort16_desc<64>(key); sort16_desc<80>(key); sort16_desc<96>(key); sort16_desc<112>(key);
+                    merge_top16<0, 16>(key); merge_top16<32, 48>(key); merge_top16<64, 80>(key); merge_top16<96, 112>(key);
+                    merge_top16<0, 32>(key); merge_top16<64, 96>(key);
+                    merge_top16<0, 64>(key);
                     float tv[9]; int ti[9];
 #pragma unroll
-                    for (int r = 0; r < 9; r++) { tv[r] = sel_v[r * 128 + et]; ti[r] = sel_i[r * 128 + et]; }
+                    for (int r = 0; r < 9; r++) { ti[r] = 127 - (int)(key[r] & 127u); tv[r] = col[ti[r] * 128 + et]; }
+                    // near-tie threshold: the assumed accumulation error plus what the borrowed key bits can hide
+                    const float thr = 2.f * eps + fmaxf(fabsf(tv[0]), fabsf(tv[8])) * 6.1035156e-5f;   // 2^-14
                     bool close = exact_all != 0;
 #pragma unroll
-                    for (int k = 0; k < 8; k++) close |= (tv[k] - tv[k + 1]) < 2.f * eps;
+                    for (int k = 0; k < 8; k++) close |= (tv[k] - tv[k + 1]) < thr;
                     float p[8], sum = 0.f;
 #pragma unroll
                     for (int k = 0; k < 8; k++) { p[k] = expf(tv[k] - tv[0]); sum += p[k]; }
