@@ -55,7 +55,7 @@ struct clef_gpu {
     int trace_first, trace_rows, trace_layers;
     bool trace_valid;
     /* options */
-    bool debug_poison, router_exact, profile, debug_stamps, fuse_gather;
+    bool debug_poison, router_exact, profile, debug_stamps;
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
@@ -496,20 +496,9 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
-    const bool fused = g->gemm_impl == 0 && g->fuse_gather;
-    if (!fused && !launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
+    if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
-    if (fused) {
-        /* gate/up fetches its token rows from xn itself (TMA gather4): no permuted copy */
-        CUtensorMap tm_xrow;
-        if (!make_map(g, &tm_xrow, xn, (uint64_t)rows, OMNI_H, 1, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
-            note_failure(g, "activation row descriptor", cudaErrorInvalidValue);
-            return false;
-        }
-        if (!launched(g, "gate/up experts", omni_launch_gateup_gather_sm100(&L->tm_gate_up, &tm_xrow, s->sort, s->h, g->n_sm, g->stream))) return false;
-        stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
-    } else if (g->gemm_impl == 0) {
+    if (g->gemm_impl == 0) {
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
         stage_mark(g, 3);
         if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
@@ -707,7 +696,6 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
-    else if (!strcmp(name, "fuse_gather")) g->fuse_gather = value != 0;
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }
     else return false;

@@ -108,10 +108,9 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
     __syncthreads();
     if (le < EL && *n_local_rows <= OMNI_ROWS) {
         const int off = scan[le], firstt = tiles[le];
-        for (int j = 0; j < nt; j++) {
-            const int len = min(OMNI_TILE_N, n - j * OMNI_TILE_N);
-            st.ttiles[firstt + j] = omni_ttile{le, off + j * OMNI_TILE_N, len, firstt | (nt << 16)};
-        }
+        const int base = nt ? n / nt : 0, extra = nt ? n % nt : 0;      // near-equal tiles, as in assign_scan_kernel
+        for (int j = 0; j < nt; j++)
+            st.ttiles[firstt + j] = omni_ttile{le, off + j * base + min(j, extra), base + (j < extra), firstt | (nt << 16)};
     }
 }
 

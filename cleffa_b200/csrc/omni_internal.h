@@ -35,7 +35,7 @@ typedef struct {
     int32_t *rowmap;       /* [rows*8] token of each permuted row     */
     int32_t *slots;        /* [rows*8] permuted row of assignment i   */
     int32_t *segcount;     /* [MAX_SEGS][E] per-segment histograms, then exclusive bases */
-    omni_ttile *ttiles;    /* [MAX_TTILES] expert-major: an expert's full tiles, then its remainder */
+    omni_ttile *ttiles;    /* [MAX_TTILES] expert-major, an expert's rows in near-equal tiles */
     int32_t *n_ttiles;     /* [1]                                     */
     int32_t *sched;        /* [2] work counters of the two expert-product kernels, zeroed by the scan */
     uint32_t *status;      /* [1]                                     */
@@ -86,9 +86,6 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
 /* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, int n_sm, cudaStream_t s);
-/* tm_xrow: the activation matrix [T][2048] with box {64, 1} for TMA gather4; st.rowmap gives the rows */
-cudaError_t omni_launch_gateup_gather_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_xrow, const omni_sort_state st,
-                                            void *h, int n_sm, cudaStream_t s);
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                    void *d, int n_sm, cudaStream_t s);
 

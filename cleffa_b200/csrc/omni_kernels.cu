@@ -327,13 +327,14 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         st.counts[e] = n;
         st.offsets[e] = off;
         if (e == OMNI_E - 1) st.offsets[OMNI_E] = scan_a[e];
-        // expert-major tile list: the expert's full tiles, then its remainder
+        // expert-major tile list
         const int nt = (n + OMNI_TILE_N - 1) / OMNI_TILE_N;
         const int first = scan_b[e] - nt;
-        for (int j = 0; j < nt; j++) {
-            const int len = min(OMNI_TILE_N, n - j * OMNI_TILE_N);
-            st.ttiles[first + j] = omni_ttile{e, off + j * OMNI_TILE_N, len, first | (nt << 16)};
-        }
+        // an expert's rows are split into nt tiles of near-equal length: tiles that share a
+        // weight tile then advance at the same pace and meet in L2
+        const int base = nt ? n / nt : 0, extra = nt ? n % nt : 0;
+        for (int j = 0; j < nt; j++)
+            st.ttiles[first + j] = omni_ttile{e, off + j * base + min(j, extra), base + (j < extra), first | (nt << 16)};
         if (e == 0) { *st.n_ttiles = scan_b[OMNI_E - 1]; st.sched[0] = 0; st.sched[1] = 0; }
     }
 }

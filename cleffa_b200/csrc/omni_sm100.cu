@@ -95,15 +95,6 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
 }
-// Four rows picked by index from a 2-D tensor (box {64, 1}), written as four consecutive
-// 128-byte rows of the swizzled tile.
-__device__ __forceinline__ void tma_gather4_hint(uint32_t dst, const CUtensorMap *map, int x, int r0, int r1, int r2, int r3,
-                                                 uint32_t bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(policy) : "memory");
-}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -178,76 +169,84 @@ struct PipeState {
 // ====================================================================== grouped expert products
 enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
 
+// Weights come from HBM (about 2 us away under load), token rows mostly from L2: the two operands
+// therefore have their own shared-memory rings, the weight ring deeper than the token ring,
+// each filled by its own producer thread so the weight loads can run further ahead.
 template <int MODE> struct GemmCfg;
 template <> struct GemmCfg<MODE_GATEUP> {
-    static constexpr int KTOT = OMNI_H, NACC = 2, NBUF = 1, STAGES = 3, MTILES = OMNI_F / 128;
+    static constexpr int KTOT = OMNI_H, NACC = 2, NBUF = 1, W_STAGES = 4, T_STAGES = 3, MTILES = OMNI_F / 128;
     static constexpr int W_ROWS_PER_EXPERT = 2 * OMNI_F, OUT_COLS = OMNI_F;
 };
 template <> struct GemmCfg<MODE_DOWN> {
-    static constexpr int KTOT = OMNI_F, NACC = 1, NBUF = 2, STAGES = 4, MTILES = OMNI_H / 128;
+    static constexpr int KTOT = OMNI_F, NACC = 1, NBUF = 2, W_STAGES = 6, T_STAGES = 4, MTILES = OMNI_H / 128;
     static constexpr int W_ROWS_PER_EXPERT = OMNI_H, OUT_COLS = OMNI_H;
 };
 
-constexpr int GEMM_THREADS = 384;            // warp 0 TMA, 1 MMA, 2 TMEM, 3 spare, 4..11 epilogue
+constexpr int GEMM_THREADS = 384;            // warp 0 scheduler + weight TMA, 1 MMA, 2 TMEM, 3 token TMA, 4..11 epilogue
 constexpr int EPI_WARPS = 8;
+constexpr int T_TILE_BYTES = OMNI_TILE_N * BK * 2;   // 32 KiB: up to 256 token rows
 
 template <int MODE> struct GemmSmem {
-    static constexpr int STAGE_BYTES = GemmCfg<MODE>::NACC * A_TILE_BYTES + OMNI_TILE_N * BK * 2;
-    static constexpr int TOTAL_BYTES = GemmCfg<MODE>::STAGES * STAGE_BYTES + 1024 + 512;
+    static constexpr int W_BYTES = GemmCfg<MODE>::NACC * A_TILE_BYTES;
+    static constexpr int RING_BYTES = GemmCfg<MODE>::W_STAGES * W_BYTES + GemmCfg<MODE>::T_STAGES * T_TILE_BYTES;
+    static constexpr int TOTAL_BYTES = RING_BYTES + 1024 + 512;
 };
+static_assert(GemmSmem<MODE_GATEUP>::TOTAL_BYTES <= 232448 && GemmSmem<MODE_DOWN>::TOTAL_BYTES <= 232448, "shared memory budget");
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 // Work distribution.  The work list is expert-major: for one expert, every (weight tile m,
 // token tile j) pair is consecutive, so CTAs that run at the same time share either the token
 // rows or the weight rows through L2 and each weight byte leaves HBM once even when an expert
-// has a second (remainder) token tile.  Items differ in cost, so CTAs claim them one at a time
-// from a device counter; warp 0 claims and hands the decoded item to the MMA thread and the
-// epilogue warps through a small shared-memory ring.
+// has more than one token tile.  Items differ in cost, so CTAs claim them one at a time from a
+// device counter; warp 0 claims and hands the decoded item to the token producer, the MMA
+// thread and the epilogue warps through a small shared-memory ring.
 struct WorkSlot { int expert, row0, len, m; };
 constexpr int RING = 4;
 
-//
-// GATHER (gate/up only): the token rows are not read from a permuted copy but fetched from the
-// activation matrix itself with TMA gather4, four rows per instruction, by the 32 lanes of the
-// producer warp (row indices come from the row map of the counting sort).  This removes the
-// permuted copy from HBM altogether; the activations (16.8 MB at T=4096) stay in L2.
-template <int MODE, bool GATHER>
+template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ TokMaps tm_tok,
                    const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
-                   int32_t *__restrict__ work_counter, const int32_t *__restrict__ rowmap,
-                   __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
-    static_assert(!GATHER || MODE == MODE_GATEUP, "only the gate/up product gathers its token rows");
+                   int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
-    constexpr int STAGE_BYTES = GemmSmem<MODE>::STAGE_BYTES;
+    constexpr int WS = C::W_STAGES, TS = C::T_STAGES;
+    constexpr int W_BYTES = GemmSmem<MODE>::W_BYTES;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = smem_base + C::STAGES * STAGE_BYTES;   // 8-byte aligned
-    // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2], drain, work_full[RING], work_empty[RING]
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
-    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
-    const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 4);
-    auto wfull_bar = [&](int r) { return bar_base + 8u * (2 * C::STAGES + 5 + r); };
-    auto wempty_bar = [&](int r) { return bar_base + 8u * (2 * C::STAGES + 5 + RING + r); };
-    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * (2 * C::STAGES + 5 + 2 * RING);
+    const uint32_t tok_base = smem_base + WS * W_BYTES;
+    const uint32_t bar_base = smem_base + GemmSmem<MODE>::RING_BYTES;   // 8-byte aligned
+    // barriers: wfull[WS] wempty[WS] tfull[TS] tempty[TS] acc_full[2] acc_empty[2] drain item_full[RING] item_empty[RING]
+    auto wfull_bar = [&](int s) { return bar_base + 8u * s; };
+    auto wempty_bar = [&](int s) { return bar_base + 8u * (WS + s); };
+    auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * WS + s); };
+    auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * WS + TS + s); };
+    auto afull_bar = [&](int b) { return bar_base + 8u * (2 * WS + 2 * TS + b); };
+    auto aempty_bar = [&](int b) { return bar_base + 8u * (2 * WS + 2 * TS + 2 + b); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * WS + 2 * TS + 4);
+    auto ifull_bar = [&](int r) { return bar_base + 8u * (2 * WS + 2 * TS + 5 + r); };
+    auto iempty_bar = [&](int r) { return bar_base + 8u * (2 * WS + 2 * TS + 5 + RING + r); };
+    constexpr int N_BARS = 2 * WS + 2 * TS + 5 + 2 * RING;
+    static_assert(N_BARS * 8 + 16 + 8 * 4 + 8 * 4 + RING * 16 <= 512, "barrier block");
+    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * N_BARS;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
-    volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);   // [STAGES] parity armed by the producer, -1 none
-    volatile WorkSlot *ring = reinterpret_cast<volatile WorkSlot *>(misc + 32);
+    volatile int *armed_w = reinterpret_cast<volatile int *>(misc + 16);        // [8] parity armed per weight stage, -1 none
+    volatile int *armed_t = reinterpret_cast<volatile int *>(misc + 16 + 32);   // [8] same for the token ring
+    volatile WorkSlot *ring = reinterpret_cast<volatile WorkSlot *>(misc + 16 + 64);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_work = *n_ttiles * C::MTILES;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); armed[s] = -1; }
-        for (int b = 0; b < 2; b++) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EPI_WARPS); }
+        for (int s = 0; s < WS; s++) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 1); }
+        for (int s = 0; s < TS; s++) { mbar_init(tfull_bar(s), 1); mbar_init(tempty_bar(s), 1); }
+        for (int s = 0; s < 8; s++) { armed_w[s] = -1; armed_t[s] = -1; }
+        for (int b = 0; b < 2; b++) { mbar_init(afull_bar(b), 1); mbar_init(aempty_bar(b), EPI_WARPS); }
         mbar_init(drain_bar, 1);
-        for (int r = 0; r < RING; r++) { mbar_init(wfull_bar(r), 1); mbar_init(wempty_bar(r), 1 + EPI_WARPS); }
+        for (int r = 0; r < RING; r++) { mbar_init(ifull_bar(r), 1); mbar_init(iempty_bar(r), 2 + EPI_WARPS); }
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_w);
@@ -259,115 +258,119 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0 && (GATHER || lane == 0)) {
-        // ---------------------------------------------------------- scheduler + TMA producer
-        // Lane 0 claims work and issues the tiled loads; with GATHER all 32 lanes stay in the
-        // loop and each issues its share of the gather4 loads.
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- scheduler + weight producer
+        // Claiming and decoding an item costs an atomic and two dependent global loads (~2 us).
+        // They are software-pipelined behind the TMA issue loop: while item i is being loaded,
+        // item i+1 is decoded (its claim came back one iteration ago) and item i+2 is claimed.
         PipeState p, wr;
-        const uint64_t pol_w1 = l2_policy_evict_first(), pol_t = l2_policy_evict_last();
-        int cur = 0;
-        if (lane == 0) cur = atomicAdd(work_counter, 1);
+        const uint64_t pol_w1 = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+        auto lookup = [&](int w, int &m, int &cnt) {          // item -> (weight tile m, tile-list index)
+            const omni_ttile t0 = ttiles[w / C::MTILES];
+            const int first = t0.group & 0xffff;
+            cnt = t0.group >> 16;
+            const int local = w - first * C::MTILES;
+            m = local / cnt;
+            return first + local % cnt;
+        };
+        int cur_m = 0, cur_cnt = 1;
+        omni_ttile cur = omni_ttile{0, 0, -1, 0};
+        int w0 = atomicAdd(work_counter, 1);
+        int w1 = atomicAdd(work_counter, 1);                  // index of the item after the current one
+        if (w0 < n_work) cur = ttiles[lookup(w0, cur_m, cur_cnt)];
         for (;;) {
-            int expert = 0, row0 = 0, len = -2, m = 0, cnt = 1, next = 0;
-            if (lane == 0) {
-                if (mbar_wait(wempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) {
-                    if (cur >= n_work) {
-                        ring[wr.stage].len = -1;              // tells the consumers to stop
-                        mbar_arrive(wfull_bar(wr.stage));
-                        len = -1;
-                    } else {
-                        // item -> (expert group, weight tile m, token tile j): see assign_scan_kernel
-                        const omni_ttile t0 = ttiles[cur / C::MTILES];
-                        const int first = t0.group & 0xffff;
-                        cnt = t0.group >> 16;
-                        const int local = cur - first * C::MTILES;
-                        m = local / cnt;
-                        const omni_ttile tt = ttiles[first + local % cnt];
-                        expert = tt.expert; row0 = tt.row0; len = tt.len;
-                        ring[wr.stage].expert = expert; ring[wr.stage].row0 = row0;
-                        ring[wr.stage].len = len; ring[wr.stage].m = m;
-                        mbar_arrive(wfull_bar(wr.stage));
-                        wr.advance(RING);
-                        next = atomicAdd(work_counter, 1);    // claimed early: its latency hides behind the loads below
-                    }
-                }
+            if (!mbar_wait(iempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) break;
+            if (cur.len < 0) {
+                ring[wr.stage].len = -1;                      // tells the consumers to stop
+                mbar_arrive(ifull_bar(wr.stage));
+                break;
             }
-            if (GATHER) {
-                row0 = __shfl_sync(0xffffffffu, row0, 0);
-                len = __shfl_sync(0xffffffffu, len, 0);
-            }
-            if (len < 0) break;                               // -1: no more work, -2: a wait ran out
-            const int bi = tok_box_index(len);
-            const int ngather = (len + 3) >> 2;               // gather4 instructions per stage
-            const uint32_t bytes = C::NACC * A_TILE_BYTES + (GATHER ? ngather * 512u : (32u << bi) * (BK * 2));
-            const int wrow = expert * C::W_ROWS_PER_EXPERT + m * 128;
+            ring[wr.stage].expert = cur.expert; ring[wr.stage].row0 = cur.row0;
+            ring[wr.stage].len = cur.len; ring[wr.stage].m = cur_m;
+            mbar_arrive(ifull_bar(wr.stage));
+            wr.advance(RING);
+            const int w2 = atomicAdd(work_counter, 1);        // consumed two iterations from now
+            const bool has_next = w1 < n_work;
+            omni_ttile head = omni_ttile{0, 0, 0, 0};
+            if (has_next) head = ttiles[w1 / C::MTILES];      // first dependent load: in flight during the loop below
+            int nxt_m = 0, nxt_cnt = 1;
+            const int wrow = cur.expert * C::W_ROWS_PER_EXPERT + cur_m * 128;
             // a weight tile is read once per token tile of its expert: keep it in L2 while
             // the expert's other token tiles (claimed by neighbouring CTAs) still need it
-            const uint64_t pol_w = cnt > 1 ? pol_t : pol_w1;
-            int tok[2][4];                                     // this lane's source rows: groups lane and lane+32
-            if (GATHER) {
-#pragma unroll
-                for (int h = 0; h < 2; h++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int r = 4 * (lane + 32 * h) + i;
-                        tok[h][i] = rowmap[row0 + (r < len ? r : len - 1)];
-                    }
-            }
+            const uint64_t pol_w = cur_cnt > 1 ? pol_keep : pol_w1;
+            omni_ttile nxt = omni_ttile{0, 0, -1, 0};
             bool ok = true;
             for (int ks = 0; ks < KSTAGES; ks++) {
-                if (lane == 0) ok = mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
-                if (GATHER) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (ks == KSTAGES / 4 && has_next) {           // first load has landed: issue the second
+                    const int first = head.group & 0xffff;
+                    nxt_cnt = head.group >> 16;
+                    const int local = w1 - first * C::MTILES;
+                    nxt_m = local / nxt_cnt;
+                    nxt = ttiles[first + local % nxt_cnt];
+                }
+                ok = mbar_wait(wempty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
                 if (!ok) break;
-                const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
-                if (lane == 0) {
-                    armed[p.stage] = (int)p.phase;
-                    mbar_expect_tx(full_bar(p.stage), bytes);
-                    tma_load_2d_hint(sa, &tm_w, ks * BK, wrow, full_bar(p.stage), pol_w);
-                    if (C::NACC == 2) tma_load_2d_hint(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, full_bar(p.stage), pol_w);
-                    if (!GATHER) tma_load_2d_hint(sa + C::NACC * A_TILE_BYTES, &tm_tok.m[bi], ks * BK, row0, full_bar(p.stage), pol_t);
-                }
-                if (GATHER) {
-                    const uint32_t sb = sa + C::NACC * A_TILE_BYTES;
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int gidx = lane + 32 * h;
-                        if (gidx < ngather)
-                            tma_gather4_hint(sb + gidx * 512, &tm_tok.m[0], ks * BK, tok[h][0], tok[h][1], tok[h][2], tok[h][3],
-                                             full_bar(p.stage), pol_t);
-                    }
-                }
-                p.advance(C::STAGES);
+                const uint32_t sa = smem_base + p.stage * W_BYTES;
+                armed_w[p.stage] = (int)p.phase;
+                mbar_expect_tx(wfull_bar(p.stage), W_BYTES);
+                tma_load_2d_hint(sa, &tm_w, ks * BK, wrow, wfull_bar(p.stage), pol_w);
+                if (C::NACC == 2) tma_load_2d_hint(sa + A_TILE_BYTES, &tm_w, ks * BK, wrow + OMNI_F, wfull_bar(p.stage), pol_w);
+                p.advance(WS);
             }
             if (!ok) break;
-            cur = next;
+            cur = nxt; cur_m = nxt_m; cur_cnt = nxt_cnt;
+            w1 = w2;
+        }
+    } else if (warp == 3 && lane == 0) {
+        // ---------------------------------------------------------- token producer
+        PipeState p, wr;
+        const uint64_t pol_t = l2_policy_evict_last();
+        bool ok = true;
+        while (ok) {
+            ok = mbar_wait(ifull_bar(wr.stage), wr.phase, abort_flag, status);
+            if (!ok) break;
+            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len;
+            mbar_arrive(iempty_bar(wr.stage));
+            wr.advance(RING);
+            if (len < 0) break;
+            const int bi = tok_box_index(len);
+            const uint32_t bytes = (32u << bi) * (BK * 2);
+            for (int ks = 0; ks < KSTAGES; ks++) {
+                ok = mbar_wait(tempty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
+                if (!ok) break;
+                armed_t[p.stage] = (int)p.phase;
+                mbar_expect_tx(tfull_bar(p.stage), bytes);
+                tma_load_2d_hint(tok_base + p.stage * T_TILE_BYTES, &tm_tok.m[bi], ks * BK, row0, tfull_bar(p.stage), pol_t);
+                p.advance(TS);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------- MMA issuer
-        PipeState p, wr;
+        PipeState pw, pt, wr;
         bool ok = true;
         for (int it = 0; ok; it++) {
-            ok = mbar_wait(wfull_bar(wr.stage), wr.phase, abort_flag, status);
+            ok = mbar_wait(ifull_bar(wr.stage), wr.phase, abort_flag, status);
             if (!ok) break;
             const int len = ring[wr.stage].len;
-            mbar_arrive(wempty_bar(wr.stage));
+            mbar_arrive(iempty_bar(wr.stage));
             wr.advance(RING);
             if (len < 0) break;
             const int n_mma = (len + 15) & ~15;
             const uint32_t idesc = idesc_bf16(128, n_mma);
             const int buf = it % C::NBUF;
             const uint32_t use = (uint32_t)(it / C::NBUF);
-            ok = mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u, abort_flag, status);
+            ok = mbar_wait(aempty_bar(buf), (use & 1u) ^ 1u, abort_flag, status);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d0 = tmem_base + (C::NBUF == 2 ? buf * 256 : 0);
             for (int ks = 0; ks < KSTAGES; ks++) {
-                ok = mbar_wait(full_bar(p.stage), p.phase, abort_flag, status);
+                ok = mbar_wait(wfull_bar(pw.stage), pw.phase, abort_flag, status) &&
+                     mbar_wait(tfull_bar(pt.stage), pt.phase, abort_flag, status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sa = smem_base + p.stage * STAGE_BYTES;
+                const uint32_t sa = smem_base + pw.stage * W_BYTES;
                 const uint64_t da0 = smem_desc_sw128(sa);
-                const uint64_t db = smem_desc_sw128(sa + C::NACC * A_TILE_BYTES);
+                const uint64_t db = smem_desc_sw128(tok_base + pt.stage * T_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++) {
                     const uint32_t acc = (ks | k) ? 1u : 0u;
@@ -375,11 +378,13 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     if (C::NACC == 2)
                         umma_bf16(d0 + 256, smem_desc_sw128(sa + A_TILE_BYTES) + 2u * k, db + 2u * k, idesc, acc);
                 }
-                umma_commit(empty_bar(p.stage));     // frees the stage when these MMAs have read it
-                p.advance(C::STAGES);
+                umma_commit(wempty_bar(pw.stage));   // both stages are free once these MMAs have read them
+                umma_commit(tempty_bar(pt.stage));
+                pw.advance(WS);
+                pt.advance(TS);
             }
             if (!ok) break;
-            umma_commit(tfull_bar(buf));             // accumulator complete
+            umma_commit(afull_bar(buf));             // accumulator complete
         }
         // Whatever happened, wait (bounded) until every MMA issued by this thread retired
         // before TMEM is released.
@@ -395,16 +400,16 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         PipeState wr;
         bool ok = true;
         for (int it = 0; ok; it++) {
-            ok = mbar_wait(wfull_bar(wr.stage), wr.phase, abort_flag, status);
+            ok = mbar_wait(ifull_bar(wr.stage), wr.phase, abort_flag, status);
             if (!ok) break;
             const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, m = ring[wr.stage].m;
             __syncwarp();
-            if (lane == 0) mbar_arrive(wempty_bar(wr.stage));
+            if (lane == 0) mbar_arrive(iempty_bar(wr.stage));
             wr.advance(RING);
             if (len < 0) break;
             const int buf = it % C::NBUF;
             const uint32_t use = (uint32_t)(it / C::NBUF);
-            ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, status);
+            ok = mbar_wait(afull_bar(buf), use & 1u, abort_flag, status);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (C::NBUF == 2 ? buf * 256 : 0);
@@ -434,7 +439,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(buf));
+                if (lane == 0) mbar_arrive(aempty_bar(buf));
                 unsigned short *o16 = reinterpret_cast<unsigned short *>(orow);
 #pragma unroll
                 for (int ci = 0; ci < 4; ci++) {
@@ -461,7 +466,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(buf));
+                if (lane == 0) mbar_arrive(aempty_bar(buf));
             }
         }
     }
@@ -471,11 +476,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
         // a wait ran out: give copies already in flight a bounded chance to land
-        for (int s = 0; s < C::STAGES; s++) {
-            const int par = armed[s];
+        for (int s = 0; s < WS + TS; s++) {
+            const int par = s < WS ? armed_w[s] : armed_t[s - WS];
             if (par < 0) continue;
+            const uint32_t bar = s < WS ? wfull_bar(s) : tfull_bar(s - WS);
             const uint64_t t0 = globaltimer_ns();
-            while (!mbar_try_wait(full_bar(s), (uint32_t)par) && globaltimer_ns() - t0 < 50000000ull) {}
+            while (!mbar_try_wait(bar, (uint32_t)par) && globaltimer_ns() - t0 < 50000000ull) {}
         }
     }
     __syncthreads();
@@ -693,13 +699,10 @@ extern "C" {
 
 cudaError_t omni_sm100_configure(void) {
     cudaError_t e;
-    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmSmem<MODE_GATEUP>::TOTAL_BYTES);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_GATEUP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             GemmSmem<MODE_GATEUP>::TOTAL_BYTES);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_DOWN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmSmem<MODE_DOWN>::TOTAL_BYTES);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(router_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);
@@ -718,17 +721,8 @@ cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap 
                                      void *h, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
-    expert_gemm_kernel<MODE_GATEUP, false><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, nullptr, (__nv_bfloat16 *)h, st.status);
-    return cudaGetLastError();
-}
-
-cudaError_t omni_launch_gateup_gather_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_xrow, const omni_sort_state st,
-                                            void *h, int n_sm, cudaStream_t s) {
-    TokMaps tok;
-    for (int i = 0; i < 4; i++) tok.m[i] = *tm_xrow;
-    expert_gemm_kernel<MODE_GATEUP, true><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, st.rowmap, (__nv_bfloat16 *)h, st.status);
+    expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status);
     return cudaGetLastError();
 }
 
@@ -736,8 +730,8 @@ cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *t
                                    void *d, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
-    expert_gemm_kernel<MODE_DOWN, false><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1, nullptr, (__nv_bfloat16 *)d, st.status);
+    expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1, (__nv_bfloat16 *)d, st.status);
     return cudaGetLastError();
 }
 

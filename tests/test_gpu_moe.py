@@ -76,20 +76,6 @@ def test_tcgen05_and_check_kernels_agree(bound0):
     assert orc.rel_l2(fast["out"], slow["out"]) < 5e-3          # both round h and d to BF16; sums differ in order
 
 
-@pytest.mark.parametrize("T", [1, 5, 100, 300, 1025, 4096])
-def test_gather_fused_into_gate_up_is_bitwise_the_same(bound0, T):
-    # token rows fetched by TMA gather4 straight from the activations vs. the permuted copy
-    b = bound0
-    x = orc.make_activations(77 + T, T)
-    plain = run_block(b, 0, x)
-    b.set_option("fuse_gather", 1)
-    try:
-        fused = run_block(b, 0, x)
-    finally:
-        b.set_option("fuse_gather", 0)
-    assert np.array_equal(plain["ids"], fused["ids"]) and torch.equal(plain["out"], fused["out"])
-
-
 def test_golden_ids_of_config1(bound0):
     from pathlib import Path
     g = np.load(Path(__file__).resolve().parent / "golden" / "route_c1.npz")
