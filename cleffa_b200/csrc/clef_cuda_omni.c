@@ -855,3 +855,21 @@ void clef_omni_ep_disconnect(clef_gpu *g) {
     memset(&g->ep, 0, sizeof g->ep);
     cudaGetLastError();
 }
+
+/* ---------------------------------------------------------------- allocation-free entry point */
+bool clef_omni_assign_noalloc(const int32_t *ids, int rows, int32_t *counts, int32_t *offsets, int32_t *rowmap,
+                              int32_t *slots, uint32_t *status, void *stream, char *err, size_t errlen) {
+    int max_rows = 0;
+    if (!ids || !counts || !offsets || !rowmap || !slots) {
+        set_err(err, errlen, "cuda: invalid Omni assignment dispatch");
+        return false;
+    }
+    cudaError_t e = omni_noalloc_assign(ids, rows, counts, offsets, rowmap, slots, status, (cudaStream_t)stream, &max_rows);
+    if (e == cudaSuccess) return true;
+    cudaGetLastError();
+    if (rows <= 0 || rows > max_rows)
+        set_err(err, errlen, "cuda: allocation-free Omni assignment takes 1..%d tokens, got %d", max_rows, rows);
+    else
+        set_err(err, errlen, "cuda: allocation-free Omni assignment failed: %s", cudaGetErrorString(e));
+    return false;
+}

@@ -77,6 +77,10 @@ cudaError_t omni_launch_touch(const void *p, uint32_t *sink, cudaStream_t s);
 cudaError_t omni_launch_trace(const float *logits, const int32_t *ids, const float *weights, int rows, int start,
                               int first, int captured, int layer, void *trace, cudaStream_t s);
 
+/* the sort with its scratch in a static device array (no allocation); *max_rows = its limit */
+cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, int32_t *offsets, int32_t *rowmap,
+                                int32_t *slots, uint32_t *status, cudaStream_t s, int *max_rows);
+
 /* ---- tcgen05 kernels (omni_sm100.cu) ---- */
 cudaError_t omni_sm100_configure(void);   /* opt-in shared-memory sizes; call once per device */
 cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,

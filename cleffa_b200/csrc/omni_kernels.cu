@@ -610,4 +610,51 @@ cudaError_t omni_launch_trace(const float *logits, const int32_t *ids, const flo
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- assignment without allocation
+// Scratch of the sort (segment histograms, tile list, counters) for at most
+// CLEF_OMNI_NOALLOC_MAX_ROWS tokens, reserved in the module image: about 72 KB on every GPU
+// that loads the library, for the life of the process.
+namespace {
+constexpr int NOALLOC_MAX_ROWS = 4096;
+constexpr int NOALLOC_MAX_SEGS = NOALLOC_MAX_ROWS * OMNI_TOP / OMNI_SEG;
+struct NoAllocScratch {
+    int32_t segcount[NOALLOC_MAX_SEGS * OMNI_E];
+    omni_ttile ttiles[NOALLOC_MAX_ROWS * OMNI_TOP / OMNI_TILE_N + OMNI_E];
+    int32_t n_ttiles, sched[2];
+    uint32_t status;
+};
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+// Device address of the array above, per device.  In host code the symbol's name is only a
+// stand-in; the usable address comes from cudaGetSymbolAddress with that device current.
+static NoAllocScratch *g_noalloc_ptr[64];
+}  // namespace
+
+cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, int32_t *offsets, int32_t *rowmap,
+                                int32_t *slots, uint32_t *status, cudaStream_t s, int *max_rows) {
+    if (max_rows) *max_rows = NOALLOC_MAX_ROWS;
+    if (rows <= 0 || rows > NOALLOC_MAX_ROWS) return cudaErrorInvalidValue;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!g_noalloc_ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        g_noalloc_ptr[dev] = static_cast<NoAllocScratch *>(p);
+    }
+    NoAllocScratch *sc = g_noalloc_ptr[dev];
+    if (!status) {
+        // the shared status word keeps whatever the previous call left: start it at zero
+        e = cudaMemsetAsync(&sc->status, 0, sizeof(uint32_t), s);
+        if (e != cudaSuccess) return e;
+        status = &sc->status;
+    }
+    omni_sort_state st;
+    st.counts = counts; st.offsets = offsets; st.rowmap = rowmap; st.slots = slots;
+    st.segcount = sc->segcount; st.ttiles = sc->ttiles; st.n_ttiles = &sc->n_ttiles; st.sched = sc->sched;
+    st.status = status;
+    return omni_launch_assign(ids, rows, st, s);
+}
+
 }  // extern "C"

@@ -36,7 +36,9 @@ EXPORTS = [
     "clef_omni_stage_route", "clef_omni_stage_assign", "clef_omni_stage_experts", "clef_omni_read",
     "clef_omni_set_option", "clef_omni_profile", "clef_omni_arena_bytes",
     "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
+    "clef_omni_assign_noalloc",
 ]
+NOALLOC_MAX_ROWS = 4096
 EP_HANDLES, EP_HANDLE_BYTES = 5, 64
 
 
@@ -71,6 +73,7 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_ep_connect": (C.c_bool, [vp, ci, ci, vp, cc, cz]),
         "clef_omni_ep_connect_local": (C.c_bool, [vp, ci, ci, C.POINTER(vp), cc, cz]),
         "clef_omni_ep_disconnect": (None, [vp]),
+        "clef_omni_assign_noalloc": (C.c_bool, [vp, ci, vp, vp, vp, vp, vp, vp, cc, cz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -90,6 +93,18 @@ def _ptr(t):
             raise ValueError("array must be contiguous")
         return C.c_void_p(t.ctypes.data)
     raise TypeError(type(t))
+
+
+def assign_noalloc(ids: torch.Tensor, counts, offsets, rowmap, slots, status=None, stream: int | None = None, lib=None):
+    """clef_omni_assign_noalloc: the counting sort for callers that must not allocate.  All
+    tensors are caller-owned CUDA tensors on the current device; nothing is allocated here or
+    in the library.  Raises OmniError with the library's message when the call is refused."""
+    lib = lib or load_library()
+    err = C.create_string_buffer(_ERRLEN)
+    ok = lib.clef_omni_assign_noalloc(_ptr(ids), ids.shape[0], _ptr(counts), _ptr(offsets), _ptr(rowmap), _ptr(slots),
+                                      _ptr(status), C.c_void_p(stream) if stream else None, err, _ERRLEN)
+    if not ok:
+        raise OmniError(err.value.decode())
 
 
 class OmniBackend:

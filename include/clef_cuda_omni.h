@@ -146,6 +146,29 @@ bool clef_omni_stage_assign(clef_gpu *g, const int32_t *ids, int rows, int32_t *
 bool clef_omni_stage_experts(clef_gpu *g, int layer, const void *xn, const int32_t *ids, const float *weights,
                              float *x, int T, char *err, size_t errlen);
 
+/* ---- a call that never allocates --------------------------------------------------- */
+
+/* No counterpart in the reference.  Some hosts cannot take a device allocation on their hot
+ * path at all: code that runs while a CUDA stream is being captured, a real-time loop that
+ * must not touch the driver's allocator, a plug-in that is handed a fixed memory budget and
+ * no context of its own.  Every other entry point here works on a context whose arena comes
+ * from cudaMalloc.  This one needs no context: it is the stable counting sort of
+ * clef_omni_stage_assign (same inputs, same outputs, same bits) with its scratch -- segment
+ * histograms, tile list, counters, about 72 KB -- in a fixed device array that is part of the
+ * library image, so every GPU that loads the library carries it until the process exits.
+ *   - at most CLEF_OMNI_NOALLOC_MAX_ROWS tokens per call; more is refused with a message;
+ *   - ids, counts[128], offsets[129], rowmap[rows*8], slots[rows*8] are device pointers on the
+ *     current device; status (device, one word, may be NULL) receives bit 3 when an expert id
+ *     is out of range, as in clef_omni_complete; the caller clears it;
+ *   - work is enqueued on `stream` (a cudaStream_t, NULL = default stream); nothing is waited for;
+ *   - the first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams, no ordering between them) race on it.  Nothing in it has to be zero on entry. */
+enum { CLEF_OMNI_NOALLOC_MAX_ROWS = 4096 };
+bool clef_omni_assign_noalloc(const int32_t *ids, int rows, int32_t *counts, int32_t *offsets, int32_t *rowmap,
+                              int32_t *slots, uint32_t *status, void *stream, char *err, size_t errlen);
+
 /* ---- introspection, options, profiling -------------------------------------------- */
 
 /* Copies an arena buffer of the last pass to host memory after waiting for the stream:
