@@ -37,6 +37,9 @@ WEIGHT_BYTES = (E * H + E * 2 * F * H + E * H * F) * 2
 KERNELS_PER_PASS = 9     # router, exact pass, histogram, scan, scatter, gather, gate/up, down, combine
 KERNELS_PER_PASS_EP = 13 # ... with plan, dispatch, return and two barriers instead of gather
 METRIC = "MoE-layer prefill tokens/sec at T=4096"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at T=4096, from the ncu
+# capture summarised in profiles/ncu_full_router_gather_experts_combine_T4096.md
+GATEUP_DRAM_TRAFFIC_T4096 = 1_082_537_000 + 44_738_560
 
 
 def measured_peaks():
@@ -182,24 +185,55 @@ def ours(args):
     bounds = workloads.varlen_bounds(SEED, T_TOKENS)
     res_host = torch.zeros(T_TOKENS, H).pin_memory()
 
-    # A dedicated stream: the library launches on it and the timing events are recorded on it
-    # (the legacy default stream has handle 0, which the C-ABI reads as "create your own").
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    b = OmniBackend(local, stream=stream.cuda_stream)
-    b.reserve(T_TOKENS)
+    # Dedicated streams: the library launches on them and the timing events are recorded on the
+    # main one (the legacy default stream has handle 0, which the C-ABI reads as "create your own").
+    # With expert parallelism the tokens of a rank are split into `micro` independent
+    # micro-batches, each driven through its own library context and stream, so that one
+    # micro-batch's peer transfers overlap the other's expert products.
+    micro = max(1, args.micro if args.micro else (2 if world > 1 else 1))
+    main_stream = torch.cuda.Stream()
+    torch.cuda.set_stream(main_stream)
+    streams = [main_stream] + [torch.cuda.Stream() for _ in range(micro - 1)]
+    bs = [OmniBackend(local, stream=st.cuda_stream) for st in streams]
+    for b in bs:
+        b.reserve(T_TOKENS)
     if world > 1:
         # expert parallel: 128/world experts per GPU; every rank maps every rank's exchange buffers
-        handles = [None] * world
-        dist.all_gather_object(handles, b.ep_export())
-        b.ep_connect(rank, world, b"".join(handles))
-    b.bind_layer(0, router, gate_up, down)
+        el = E // world
+        dev_w = (router.cuda(), gate_up[rank * el:(rank + 1) * el].cuda(), down[rank * el:(rank + 1) * el].cuda())
+        for b in bs:
+            handles = [None] * world
+            dist.all_gather_object(handles, b.ep_export())
+            b.ep_connect(rank, world, b"".join(handles))
+            b.bind_layer(0, *dev_w)                      # one device copy of the rank's expert slice, shared
+        if micro > 1:
+            for bi in bs:
+                bi.set_option("reserve_sms", args.reserve)   # room for the other micro-batch's small kernels
+        if micro > 1 and not args.no_gate:
+            # stagger the micro-batches: context i starts its dispatch when context i-1 finished its own,
+            # so one micro-batch's transfers run under the other's expert products instead of in lock-step
+            gates = [torch.cuda.Event() for _ in range(micro)]
+            for i, (ev, st) in enumerate(zip(gates, streams)):
+                ev.record(st)                            # gives every event a handle; the first waits pass
+            torch.cuda.synchronize()
+            for i, bi in enumerate(bs):
+                bi.ep_gate(gates[(i - 1) % micro].cuda_event, gates[i].cuda_event)
+    else:
+        bs[0].bind_layer(0, router, gate_up, down)
+    b = bs[0]
     xn = x_host.cuda()
     x = torch.zeros(T_TOKENS, H, device="cuda")
+    cuts = [T_TOKENS * i // micro for i in range(micro + 1)]
+    torch.cuda.synchronize()
 
     def step():
-        b.begin()
-        b.encode_moe(0, xn, x, bounds)
+        if micro == 1:
+            b.begin()
+            b.encode_moe(0, xn, x, bounds)
+            return
+        for i, bi in enumerate(bs):
+            bi.begin()
+            bi.encode_moe(0, xn[cuts[i]:cuts[i + 1]], x[cuts[i]:cuts[i + 1]])
 
     def barrier():
         if world > 1:
@@ -208,22 +242,42 @@ def ours(args):
 
     for _ in range(max(3, args.warmup)):
         step()
-    b.complete()
+    for bi in bs:
+        bi.complete()
 
     # ---- device-resident timing (value) with per-stage marks for the roofline
     b.set_option("profile", 1)
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
-        start.record(stream)
+        start.record(main_stream)
+        for st in streams[1:]:
+            st.wait_event(start)
         for _ in range(args.steps):
             step()
-        stop.record(stream)
+        for st in streams[1:]:
+            done = torch.cuda.Event()
+            done.record(st)
+            main_stream.wait_event(done)
+        stop.record(main_stream)
         barrier()
-    b.complete()
+    for bi in bs:
+        bi.complete()
     elapsed_ms = start.elapsed_time(stop)
     stages = b.profile()
     b.set_option("profile", 0)
+    clock_summary = clocks.summary()
+    if clock_summary["samples"] < 5:
+        # K steps last a few milliseconds, less than one nvidia-smi sample: keep the same loop
+        # running for about a second (untimed) so that the clocks under this load are seen
+        with ClockSampler(local) as probe:
+            t_end = time.perf_counter() + 1.0
+            while time.perf_counter() < t_end:
+                for _ in range(20):
+                    step()
+                for bi in bs:
+                    bi.complete()
+        clock_summary = dict(probe.summary(), note="sampled over a 1 s untimed continuation of the timed loop")
 
     # ---- end to end through the host-buffer call (copies inside the timed region)
     for _ in range(2):
@@ -251,15 +305,17 @@ def ours(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(world), "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world}, tokens data-parallel, peer-store dispatch/return over NVLink", "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
+            "config": {"workload": workload_name(world), "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world}, tokens data-parallel, peer-store dispatch/return over NVLink, {micro} micro-batches per rank on separate streams", "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s",
                     "h2d_bytes_per_step": T_TOKENS * H * 2 + T_TOKENS * H * 4, "d2h_bytes_per_step": T_TOKENS * H * 4},
-            "gpu_launches": (KERNELS_PER_PASS if world == 1 else KERNELS_PER_PASS_EP) * args.steps,
-            "clocks": clocks.summary(),
+            "gpu_launches": (KERNELS_PER_PASS if world == 1 else KERNELS_PER_PASS_EP * micro) * args.steps,
+            "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "expert_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                         "peak_source": peaks["source"], "traffic": None},
+                         "peak_source": peaks["source"],
+                         "traffic": GATEUP_DRAM_TRAFFIC_T4096 if (T_TOKENS == 4096 and world == 1) else None,
+                         "algorithmic_bytes": E * 2 * F * H * 2 + T_TOKENS * TOP * H * 2 + T_TOKENS * TOP * F * 2},
             "stages_ms": stages,
             "expert_gemms": {"tflops": EXPERT_FLOP_PER_TOKEN * T_TOKENS / (both_ms * 1e-3) / 1e12 if both_ms > 0 else 0.0,
                              "frac_of_bf16_peak": (EXPERT_FLOP_PER_TOKEN * T_TOKENS / (both_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]) if both_ms > 0 else 0.0},
@@ -276,9 +332,11 @@ def ours(args):
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
-        b.ep_disconnect()
+        for bi in bs:
+            bi.ep_disconnect()
         dist.barrier()
-    b.close()
+    for bi in bs:
+        bi.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -292,6 +350,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU (default: the headline 4096)")
+    ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
+    ap.add_argument("--reserve", type=int, default=8, help="SMs the expert kernels leave free when micro-batching")
+    ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank (default: 1 on one GPU, 2 with expert parallelism)")
     args = ap.parse_args()
     T_TOKENS = args.tokens
     if args.impl == "reference":

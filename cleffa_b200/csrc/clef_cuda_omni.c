@@ -58,6 +58,7 @@ struct clef_gpu {
     bool debug_poison, router_exact, profile, debug_stamps;
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
+    int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
     long launch_fail_at, launch_count;
     /* pass state */
@@ -76,6 +77,7 @@ struct clef_gpu {
         uint32_t epoch;
         void *dret; int32_t *rowinfo, *counts, *send_base, *n_local_rows; uint32_t *flags;
         void *opened[OMNI_EP_MAX][OMNI_EP_BUFFERS];
+        cudaEvent_t gate_wait, gate_record;   /* optional host-supplied events around the dispatch phase */
     } ep;
     CUresult (*encode_tiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -499,9 +501,9 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
     if (g->gemm_impl == 0) {
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm - g->reserve_sms, g->stream))) return false;
     } else {
         if (!launched(g, "gate/up experts (check kernel)", omni_launch_gateup_simple(s->xg, L->gate_up, s->sort.offsets, rows8, s->h, g->stream))) return false;
         stage_mark(g, 3);
@@ -522,14 +524,16 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
     const omni_ep_peers *pe = &g->ep.peers;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
     if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->stream))) return false;
-    if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, g->stream))) return false;
+    if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->stream, g->ep.gate_wait, 0))) return false;
+    if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, g->n_sm, g->stream))) return false;
     if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
+    if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
     stage_mark(g, 2);
-    if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm, g->stream))) return false;
+    if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm - g->reserve_sms, g->stream))) return false;
     stage_mark(g, 3);
-    if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm, g->stream))) return false;
+    if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm - g->reserve_sms, g->stream))) return false;
     stage_mark(g, 4);
-    if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, g->ep.n_local_rows, g->stream))) return false;
+    if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, g->ep.n_local_rows, g->n_sm, g->stream))) return false;
     if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
     if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
@@ -696,6 +700,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
+    else if (!strcmp(name, "reserve_sms")) { if (value < 0 || value >= g->n_sm) return false; g->reserve_sms = (int)value; }
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }
     else return false;
@@ -840,6 +845,13 @@ bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *cons
     }
     cudaSetDevice(g->device);
     g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = false; g->ep.epoch = 0;
+    return true;
+}
+
+bool clef_omni_ep_gate(clef_gpu *g, void *wait_event, void *record_event) {
+    if (!g) return false;
+    g->ep.gate_wait = (cudaEvent_t)wait_event;
+    g->ep.gate_record = (cudaEvent_t)record_event;
     return true;
 }
 

@@ -98,9 +98,9 @@ cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_so
                                 int32_t *n_local_rows, cudaStream_t s);
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, cudaStream_t s);
 cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
-                                    const int32_t *send_base, int rows8, cudaStream_t s);
+                                    const int32_t *send_base, int rows8, int n_sm, cudaStream_t s);
 cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
-                                  const int32_t *n_local_rows, cudaStream_t s);
+                                  const int32_t *n_local_rows, int n_sm, cudaStream_t s);
 
 #ifdef __cplusplus
 }
