@@ -190,7 +190,7 @@ def ours(args):
     # With expert parallelism the tokens of a rank are split into `micro` independent
     # micro-batches, each driven through its own library context and stream, so that one
     # micro-batch's peer transfers overlap the other's expert products.
-    micro = max(1, args.micro if args.micro else (2 if world > 1 else 1))
+    micro = max(1, args.micro if args.micro else 1)
     main_stream = torch.cuda.Stream()
     torch.cuda.set_stream(main_stream)
     streams = [main_stream] + [torch.cuda.Stream() for _ in range(micro - 1)]
@@ -352,7 +352,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU (default: the headline 4096)")
     ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
     ap.add_argument("--reserve", type=int, default=8, help="SMs the expert kernels leave free when micro-batching")
-    ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank (default: 1 on one GPU, 2 with expert parallelism)")
+    ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank, each on its own context and stream (default 1)")
     args = ap.parse_args()
     T_TOKENS = args.tokens
     if args.impl == "reference":

@@ -78,6 +78,10 @@ struct clef_gpu {
         void *dret; int32_t *rowinfo, *counts, *send_base, *n_local_rows; uint32_t *flags;
         void *opened[OMNI_EP_MAX][OMNI_EP_BUFFERS];
         cudaEvent_t gate_wait, gate_record;   /* optional host-supplied events around the dispatch phase */
+        cudaStream_t side;                    /* dispatch runs here, under the gate/up kernel */
+        cudaEvent_t ev_planned, ev_dispatched, ev_down[OMNI_EP_RET_GROUPS], ev_returned;
+        int32_t *need;                        /* [128] rows each group of local experts must receive */
+        int32_t *ret_bounds;                  /* [2][RET_GROUPS+1] tile and row bounds of the down/return groups */
     } ep;
     CUresult (*encode_tiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -501,9 +505,9 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
     if (g->gemm_impl == 0) {
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm - g->reserve_sms, g->stream))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm - g->reserve_sms, g->stream))) return false;
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, g->n_sm - g->reserve_sms, g->stream))) return false;
     } else {
         if (!launched(g, "gate/up experts (check kernel)", omni_launch_gateup_simple(s->xg, L->gate_up, s->sort.offsets, rows8, s->h, g->stream))) return false;
         stage_mark(g, 3);
@@ -523,17 +527,35 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
     const int rows8 = rows * OMNI_TOP;
     const omni_ep_peers *pe = &g->ep.peers;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
-    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->stream))) return false;
-    if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->stream, g->ep.gate_wait, 0))) return false;
-    if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, g->n_sm, g->stream))) return false;
-    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
-    if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
+    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds, g->stream))) return false;
+    /* Dispatch goes to a side stream and the gate/up kernel starts at once on the main stream:
+     * its token producer waits per expert until that expert's rows (from every rank) have
+     * arrived, so the transfer runs under the expert products instead of in front of them. */
+    if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->ep.side, g->ep.gate_wait, 0))) return false;
+    if (!launched(g, "dispatch fork", cudaEventRecord(g->ep.ev_planned, g->stream))) return false;
+    if (!launched(g, "dispatch fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_planned, 0))) return false;
+    if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, g->n_sm, g->ep.side))) return false;
+    if (!launched(g, "dispatch join", cudaEventRecord(g->ep.ev_dispatched, g->ep.side))) return false;
+    if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->ep.side))) return false;
     stage_mark(g, 2);
-    if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, g->n_sm - g->reserve_sms, g->stream))) return false;
+    if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
+                                                                 g->ep.need, omni_ep_group_size(pe->world), g->n_sm - g->reserve_sms, g->stream))) return false;
     stage_mark(g, 3);
-    if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->n_sm - g->reserve_sms, g->stream))) return false;
+    /* The down product runs as RET_GROUPS launches over successive groups of local experts; as
+     * soon as one is done its result rows start travelling back on the side stream, under the
+     * next group's product (plain stream dependencies, nothing on this GPU spins on another
+     * of its own kernels). */
+    for (int rg = 0; rg < OMNI_EP_RET_GROUPS; rg++) {
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg,
+                                                                g->n_sm - g->reserve_sms, g->stream))) return false;
+        if (!launched(g, "return fork", cudaEventRecord(g->ep.ev_down[rg], g->stream))) return false;
+        if (!launched(g, "return fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_down[rg], 0))) return false;
+        if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, g->ep.ret_bounds + OMNI_EP_RET_GROUPS + 1, rg,
+                                                                         g->n_sm, g->ep.side))) return false;
+    }
     stage_mark(g, 4);
-    if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, g->ep.n_local_rows, g->n_sm, g->stream))) return false;
+    if (!launched(g, "return join", cudaEventRecord(g->ep.ev_returned, g->ep.side))) return false;
+    if (!launched(g, "return join", cudaStreamWaitEvent(g->stream, g->ep.ev_returned, 0))) return false;
     if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
     if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
@@ -730,23 +752,32 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
     void *dret = dev_alloc(g, (size_t)OMNI_ROWS * OMNI_H * 2);
     int32_t *rowinfo = dev_alloc(g, (size_t)OMNI_ROWS * 4);
     int32_t *counts = dev_alloc(g, (size_t)OMNI_EP_MAX * OMNI_E * 4);
-    uint32_t *flags = dev_alloc(g, 256);
+    uint32_t *flags = dev_alloc(g, (size_t)OMNI_EP_FLAG_WORDS * 4);
     int32_t *send_base = dev_alloc(g, (size_t)OMNI_E * 4);
     int32_t *n_local = dev_alloc(g, 256);
-    bool ok = dret && rowinfo && counts && flags && send_base && n_local;
-    if (ok) ok = cudaMemsetAsync(flags, 0, 256, g->stream) == cudaSuccess &&
+    int32_t *need = dev_alloc(g, (size_t)OMNI_E * 4);
+    int32_t *ret_bounds = dev_alloc(g, 256);
+    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && ret_bounds;
+    if (ok && !g->ep.side) ok = cudaStreamCreateWithFlags(&g->ep.side, cudaStreamNonBlocking) == cudaSuccess &&
+                                cudaEventCreateWithFlags(&g->ep.ev_planned, cudaEventDisableTiming) == cudaSuccess &&
+                                cudaEventCreateWithFlags(&g->ep.ev_dispatched, cudaEventDisableTiming) == cudaSuccess &&
+                                cudaEventCreateWithFlags(&g->ep.ev_returned, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < OMNI_EP_RET_GROUPS && ok; i++)
+        if (!g->ep.ev_down[i]) ok = cudaEventCreateWithFlags(&g->ep.ev_down[i], cudaEventDisableTiming) == cudaSuccess;
+    if (ok) ok = cudaMemsetAsync(flags, 0, (size_t)OMNI_EP_FLAG_WORDS * 4, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(need, 0, (size_t)OMNI_E * 4, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(counts, 0, (size_t)OMNI_EP_MAX * OMNI_E * 4, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(n_local, 0, 256, g->stream) == cudaSuccess &&
                  cudaStreamSynchronize(g->stream) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
-        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local};
+        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, ret_bounds};
         for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
         set_err(err, errlen, "cuda: cannot allocate Omni expert-parallel buffers (previous buffers kept)");
         return false;
     }
     g->ep.dret = dret; g->ep.rowinfo = rowinfo; g->ep.counts = counts; g->ep.flags = flags;
-    g->ep.send_base = send_base; g->ep.n_local_rows = n_local;
+    g->ep.send_base = send_base; g->ep.n_local_rows = n_local; g->ep.need = need; g->ep.ret_bounds = ret_bounds;
     return true;
 }
 
@@ -862,7 +893,12 @@ void clef_omni_ep_disconnect(clef_gpu *g) {
     if (g->ep.ipc)
         for (int r = 0; r < OMNI_EP_MAX; r++) for (int i = 0; i < OMNI_EP_BUFFERS; i++)
             if (g->ep.opened[r][i]) { cudaIpcCloseMemHandle(g->ep.opened[r][i]); g->ep.opened[r][i] = NULL; }
-    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows};
+    if (g->ep.side) { cudaStreamSynchronize(g->ep.side); cudaStreamDestroy(g->ep.side); }
+    if (g->ep.ev_planned) cudaEventDestroy(g->ep.ev_planned);
+    if (g->ep.ev_dispatched) cudaEventDestroy(g->ep.ev_dispatched);
+    if (g->ep.ev_returned) cudaEventDestroy(g->ep.ev_returned);
+    for (int i = 0; i < OMNI_EP_RET_GROUPS; i++) if (g->ep.ev_down[i]) cudaEventDestroy(g->ep.ev_down[i]);
+    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds};
     for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
     memset(&g->ep, 0, sizeof g->ep);
     cudaGetLastError();

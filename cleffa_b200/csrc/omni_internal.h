@@ -37,7 +37,7 @@ typedef struct {
     int32_t *segcount;     /* [MAX_SEGS][E] per-segment histograms, then exclusive bases */
     omni_ttile *ttiles;    /* [MAX_TTILES] expert-major, an expert's rows in near-equal tiles */
     int32_t *n_ttiles;     /* [1]                                     */
-    int32_t *sched;        /* [2] work counters of the two expert-product kernels, zeroed by the scan */
+    int32_t *sched;        /* [8] work counters: [0] gate/up, [1..] down (one per launch group), zeroed by the scan */
     uint32_t *status;      /* [1]                                     */
 } omni_sort_state;
 
@@ -49,8 +49,16 @@ typedef struct {
     void *dret[OMNI_EP_MAX];        /* [ROWS][2048] bf16: expert outputs returned, source order  */
     int32_t *rowinfo[OMNI_EP_MAX];  /* [ROWS] (source rank << 20) | source permuted row          */
     int32_t *counts[OMNI_EP_MAX];   /* [EP_MAX][128] per-expert counts of every rank             */
-    uint32_t *flags[OMNI_EP_MAX];   /* [EP_MAX] barrier epochs, written by the peers             */
+    uint32_t *flags[OMNI_EP_MAX];   /* [EP_MAX] barrier epochs, written by the peers; from word
+                                       OMNI_EP_READY_WORD on: rows arrived per local expert       */
 } omni_ep_peers;
+enum { OMNI_EP_READY_WORD = 64, OMNI_EP_FLAG_WORDS = 64 + 128 };
+/* local experts are announced as "arrived" in groups of this many (eight groups per rank) */
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+static inline int omni_ep_group_size(int world) { const int el = OMNI_E / world; return el >= 8 ? el / 8 : 1; }
+enum { OMNI_EP_RET_GROUPS = 4 };   /* the down product runs as this many launches so that results travel back under it */
 
 /* ---- plain kernels (omni_kernels.cu) ---- */
 cudaError_t omni_launch_router_simple(const void *xn, const void *router, const float *bias, int T,
@@ -88,19 +96,25 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
                                      int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
                                      cudaStream_t s);
 /* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
+/* ready/need (may be NULL): rows that have arrived / must arrive per expert before its token
+ * rows may be read (expert parallelism: the rows are written by other GPUs while this runs) */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
-                                     void *h, int n_sm, cudaStream_t s);
+                                     void *h, const uint32_t *ready, const int32_t *need, int group_size, int n_sm,
+                                     cudaStream_t s);
+/* tile_bounds (may be NULL) + group: restrict the launch to tiles [tile_bounds[group], tile_bounds[group+1]) */
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                   void *d, int n_sm, cudaStream_t s);
+                                   void *d, const int32_t *tile_bounds, int group, int n_sm, cudaStream_t s);
 
 /* ---- expert parallel (omni_ep.cu) ---- */
+/* ret_bounds: [2][RET_GROUPS+1] tile bounds, then row bounds, of the groups the down product is launched in */
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, cudaStream_t s);
+                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, cudaStream_t s);
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, cudaStream_t s);
 cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
                                     const int32_t *send_base, int rows8, int n_sm, cudaStream_t s);
+/* rows [row_bounds[group], row_bounds[group+1]) */
 cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
-                                  const int32_t *n_local_rows, int n_sm, cudaStream_t s);
+                                  const int32_t *row_bounds, int group, int n_sm, cudaStream_t s);
 
 #ifdef __cplusplus
 }

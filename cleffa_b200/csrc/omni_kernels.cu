@@ -335,7 +335,8 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         const int base = nt ? n / nt : 0, extra = nt ? n % nt : 0;
         for (int j = 0; j < nt; j++)
             st.ttiles[first + j] = omni_ttile{e, off + j * base + min(j, extra), base + (j < extra), first | (nt << 16)};
-        if (e == 0) { *st.n_ttiles = scan_b[OMNI_E - 1]; st.sched[0] = 0; st.sched[1] = 0; }
+        if (e < 8) st.sched[e] = 0;
+        if (e == 0) *st.n_ttiles = scan_b[OMNI_E - 1];
     }
 }
 
@@ -620,7 +621,7 @@ constexpr int NOALLOC_MAX_SEGS = NOALLOC_MAX_ROWS * OMNI_TOP / OMNI_SEG;
 struct NoAllocScratch {
     int32_t segcount[NOALLOC_MAX_SEGS * OMNI_E];
     omni_ttile ttiles[NOALLOC_MAX_ROWS * OMNI_TOP / OMNI_TILE_N + OMNI_E];
-    int32_t n_ttiles, sched[2];
+    int32_t n_ttiles, sched[8];
     uint32_t status;
 };
 static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];

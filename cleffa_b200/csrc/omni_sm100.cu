@@ -47,6 +47,12 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -208,7 +214,9 @@ template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ TokMaps tm_tok,
                    const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
-                   int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status) {
+                   int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status,
+                   const uint32_t *__restrict__ ready, const int32_t *__restrict__ need, int group_size,
+                   const int32_t *__restrict__ tile_bounds, int tile_group) {
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
     constexpr int WS = C::W_STAGES, TS = C::T_STAGES;
@@ -238,7 +246,9 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     volatile WorkSlot *ring = reinterpret_cast<volatile WorkSlot *>(misc + 16 + 64);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_work = *n_ttiles * C::MTILES;
+    // the launch covers work items [work_lo, n_work): everything, or one group of experts
+    const int work_lo = tile_bounds ? tile_bounds[tile_group] * C::MTILES : 0;
+    const int n_work = tile_bounds ? min(tile_bounds[tile_group + 1], *n_ttiles) * C::MTILES : *n_ttiles * C::MTILES;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < WS; s++) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 1); }
@@ -275,8 +285,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         };
         int cur_m = 0, cur_cnt = 1;
         omni_ttile cur = omni_ttile{0, 0, -1, 0};
-        int w0 = atomicAdd(work_counter, 1);
-        int w1 = atomicAdd(work_counter, 1);                  // index of the item after the current one
+        int w0 = work_lo + atomicAdd(work_counter, 1);
+        int w1 = work_lo + atomicAdd(work_counter, 1);        // index of the item after the current one
         if (w0 < n_work) cur = ttiles[lookup(w0, cur_m, cur_cnt)];
         for (;;) {
             if (!mbar_wait(iempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) break;
@@ -289,7 +299,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             ring[wr.stage].len = cur.len; ring[wr.stage].m = cur_m;
             mbar_arrive(ifull_bar(wr.stage));
             wr.advance(RING);
-            const int w2 = atomicAdd(work_counter, 1);        // consumed two iterations from now
+            const int w2 = work_lo + atomicAdd(work_counter, 1);   // consumed two iterations from now
             const bool has_next = w1 < n_work;
             omni_ttile head = omni_ttile{0, 0, 0, 0};
             if (has_next) head = ttiles[w1 / C::MTILES];      // first dependent load: in flight during the loop below
@@ -325,14 +335,34 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // ---------------------------------------------------------- token producer
         PipeState p, wr;
         const uint64_t pol_t = l2_policy_evict_last();
+        int ready_group = -1;
         bool ok = true;
         while (ok) {
             ok = mbar_wait(ifull_bar(wr.stage), wr.phase, abort_flag, status);
             if (!ok) break;
-            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len;
+            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, expert = ring[wr.stage].expert;
             mbar_arrive(iempty_bar(wr.stage));
             wr.advance(RING);
             if (len < 0) break;
+            if (ready && expert / group_size != ready_group) {
+                // expert parallelism: this expert's rows are being written by other GPUs while the
+                // kernel runs; wait (bounded, polling gently) until its whole group has arrived
+                const int grp = expert / group_size;
+                const uint32_t want = (uint32_t)need[grp];
+                const uint64_t t0 = globaltimer_ns();
+                while (ld_acquire_sys_u32(ready + grp) != want) {
+                    __nanosleep(500);
+                    if (*abort_flag || globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                        *abort_flag = 1;
+                        atomicOr(status, OMNI_ST_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                }
+                if (!ok) break;
+                fence_proxy_async_all();          // the rows are read next by TMA (async proxy)
+                ready_group = grp;
+            }
             const int bi = tok_box_index(len);
             const uint32_t bytes = (32u << bi) * (BK * 2);
             for (int ks = 0; ks < KSTAGES; ks++) {
@@ -718,20 +748,22 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
 }
 
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
-                                     void *h, int n_sm, cudaStream_t s) {
+                                     void *h, const uint32_t *ready, const int32_t *need, int group_size, int n_sm,
+                                     cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
     expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status);
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status, ready, need, group_size > 0 ? group_size : 1, nullptr, 0);
     return cudaGetLastError();
 }
 
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                   void *d, int n_sm, cudaStream_t s) {
+                                   void *d, const int32_t *tile_bounds, int group, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
     expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1, (__nv_bfloat16 *)d, st.status);
+        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d, st.status, nullptr,
+        nullptr, 1, tile_bounds, group);
     return cudaGetLastError();
 }
 
