@@ -55,7 +55,7 @@ struct clef_gpu {
     int trace_first, trace_rows, trace_layers;
     bool trace_valid;
     /* options */
-    bool debug_poison, router_exact, profile, debug_stamps;
+    bool debug_poison, router_exact, profile, debug_stamps, ep_overlap;
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
@@ -310,7 +310,12 @@ bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen) {
     if (e == cudaSuccess) e = cudaMemcpy(&status, g->omni->status, 4, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni pass failed: %s", cudaGetErrorString(e)); return false; }
     if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
-    if (status & OMNI_ST_TIMEOUT) { set_err(err, errlen, "cuda: a bounded device wait ran out in an Omni expert kernel"); return false; }
+    if (status & OMNI_ST_TIMEOUT) {
+        set_err(err, errlen, "cuda: a bounded device wait ran out in an Omni expert kernel (%s, status 0x%x)",
+                status & OMNI_ST_TIMEOUT_BARRIER ? "barrier between ranks" :
+                status & OMNI_ST_TIMEOUT_ARRIVAL ? "rows from other ranks did not arrive" : "pipeline barrier", status);
+        return false;
+    }
     if (status & OMNI_ST_EP_OVERFLOW) { set_err(err, errlen, "cuda: more expert rows were routed to this rank than its Omni arena holds"); return false; }
     if (status & OMNI_ST_BAD_ID) { set_err(err, errlen, "cuda: expert id outside [0,128) reached the Omni permutation"); return false; }
     if (status) { set_err(err, errlen, "cuda: nonfinite Omni attention or router values"); return false; }
@@ -520,43 +525,62 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
 }
 
 /* Expert-parallel variant of run_experts: rows travel to the ranks that own their experts and
- * back by peer stores; three flag barriers order the phases (omni_ep.cu). */
+ * back by peer stores (omni_ep.cu).
+ *
+ * Default (ep_overlap = 0): the phases follow one another on the context's stream -- plan
+ * (+barrier), dispatch, barrier, gate/up, down, return, barrier, combine.
+ *
+ * ep_overlap = 1 (optional): dispatch goes to a side stream and the gate/up kernel starts at
+ * once, its token producer waiting per group of experts until that group's rows have arrived
+ * from every rank; the down product runs in RET_GROUPS launches and each group's results travel
+ * back on the side stream under the next group's product.  A copy kernel cannot share an SM with
+ * a resident expert-product CTA (which holds nearly all of its shared memory), so the expert
+ * kernels then leave reserve_sms SMs (default 16) to the copies.  Same bits as the default;
+ * measured 5 % faster on 8 GPUs at 4096 tokens per rank (0.733 against 0.768 ms per pass): the
+ * copies are slower on few SMs and the products slower on fewer, which eats most of the overlap. */
 static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, const int32_t *ids, const float *weights,
                            float *x, int rows) {
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
     const omni_ep_peers *pe = &g->ep.peers;
+    const bool overlap = g->ep_overlap;
+    const int32_t *row_bounds = g->ep.ret_bounds + OMNI_EP_RET_GROUPS + 1;
+    /* with overlap the persistent expert kernels leave some SMs to the copy kernels */
+    const int n_gemm = g->n_sm - (g->reserve_sms > 0 ? g->reserve_sms : overlap ? 16 : 0);
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
     if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds, g->stream))) return false;
-    /* Dispatch goes to a side stream and the gate/up kernel starts at once on the main stream:
-     * its token producer waits per expert until that expert's rows (from every rank) have
-     * arrived, so the transfer runs under the expert products instead of in front of them. */
-    if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->ep.side, g->ep.gate_wait, 0))) return false;
-    if (!launched(g, "dispatch fork", cudaEventRecord(g->ep.ev_planned, g->stream))) return false;
-    if (!launched(g, "dispatch fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_planned, 0))) return false;
-    if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, g->n_sm, g->ep.side))) return false;
-    if (!launched(g, "dispatch join", cudaEventRecord(g->ep.ev_dispatched, g->ep.side))) return false;
-    if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->ep.side))) return false;
-    stage_mark(g, 2);
-    if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
-                                                                 g->ep.need, omni_ep_group_size(pe->world), g->n_sm - g->reserve_sms, g->stream))) return false;
-    stage_mark(g, 3);
-    /* The down product runs as RET_GROUPS launches over successive groups of local experts; as
-     * soon as one is done its result rows start travelling back on the side stream, under the
-     * next group's product (plain stream dependencies, nothing on this GPU spins on another
-     * of its own kernels). */
-    for (int rg = 0; rg < OMNI_EP_RET_GROUPS; rg++) {
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg,
-                                                                g->n_sm - g->reserve_sms, g->stream))) return false;
-        if (!launched(g, "return fork", cudaEventRecord(g->ep.ev_down[rg], g->stream))) return false;
-        if (!launched(g, "return fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_down[rg], 0))) return false;
-        if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, g->ep.ret_bounds + OMNI_EP_RET_GROUPS + 1, rg,
-                                                                         g->n_sm, g->ep.side))) return false;
+    if (!overlap) {
+        if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->stream, g->ep.gate_wait, 0))) return false;
+        if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, 0, g->n_sm, g->stream))) return false;
+        if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
+        if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
+        stage_mark(g, 2);
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, n_gemm, g->stream))) return false;
+        stage_mark(g, 3);
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, n_gemm, g->stream))) return false;
+        stage_mark(g, 4);
+        if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, row_bounds, 0, OMNI_EP_RET_GROUPS, g->n_sm, g->stream))) return false;
+    } else {
+        if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->ep.side, g->ep.gate_wait, 0))) return false;
+        if (!launched(g, "dispatch fork", cudaEventRecord(g->ep.ev_planned, g->stream))) return false;
+        if (!launched(g, "dispatch fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_planned, 0))) return false;
+        if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, 1, g->n_sm, g->ep.side))) return false;
+        if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->ep.side))) return false;
+        stage_mark(g, 2);
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
+                                                                     g->ep.need, omni_ep_group_size(pe->world), n_gemm, g->stream))) return false;
+        stage_mark(g, 3);
+        for (int rg = 0; rg < OMNI_EP_RET_GROUPS; rg++) {
+            if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg, n_gemm, g->stream))) return false;
+            if (!launched(g, "return fork", cudaEventRecord(g->ep.ev_down[rg], g->stream))) return false;
+            if (!launched(g, "return fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_down[rg], 0))) return false;
+            if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, row_bounds, rg, rg + 1, g->n_sm, g->ep.side))) return false;
+        }
+        stage_mark(g, 4);
+        if (!launched(g, "return join", cudaEventRecord(g->ep.ev_returned, g->ep.side))) return false;
+        if (!launched(g, "return join", cudaStreamWaitEvent(g->stream, g->ep.ev_returned, 0))) return false;
     }
-    stage_mark(g, 4);
-    if (!launched(g, "return join", cudaEventRecord(g->ep.ev_returned, g->ep.side))) return false;
-    if (!launched(g, "return join", cudaStreamWaitEvent(g->stream, g->ep.ev_returned, 0))) return false;
-    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->stream))) return false;
+    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
     if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
     return true;
@@ -722,6 +746,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
+    else if (!strcmp(name, "ep_overlap")) g->ep_overlap = value != 0;
     else if (!strcmp(name, "reserve_sms")) { if (value < 0 || value >= g->n_sm) return false; g->reserve_sms = (int)value; }
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }
@@ -876,6 +901,24 @@ bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *cons
     }
     cudaSetDevice(g->device);
     g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = false; g->ep.epoch = 0;
+    return true;
+}
+
+bool clef_omni_ep_sync(clef_gpu *g, int timeout_ms, char *err, size_t errlen) {
+    if (!g || !g->omni || g->ep.world < 2) { set_err(err, errlen, "cuda: Omni expert parallelism is not connected"); return false; }
+    cudaSetDevice(g->device);
+    uint32_t status = 0;
+    const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+    cudaError_t e = cudaMemsetAsync(g->omni->status, 0, 4, g->stream);
+    if (e == cudaSuccess) e = omni_launch_ep_barrier(&g->ep.peers, ++g->ep.epoch, g->omni->status, limit, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e == cudaSuccess) e = cudaMemcpy(&status, g->omni->status, 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni rank barrier failed: %s", cudaGetErrorString(e)); return false; }
+    if (status) {
+        cudaMemset(g->omni->status, 0, 4);
+        set_err(err, errlen, "cuda: not every Omni rank reached the barrier within %d ms", timeout_ms > 0 ? timeout_ms : 2000);
+        return false;
+    }
     return true;
 }
 

@@ -28,7 +28,7 @@
 namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
-constexpr uint64_t SPIN_LIMIT_NS = 1000000000ull;
+constexpr uint64_t SPIN_LIMIT_NS = 2000000000ull;      // 2 s: every legitimate wait is far shorter
 
 __device__ __forceinline__ uint64_t now_ns() {
     uint64_t t;
@@ -53,7 +53,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 // One block.  Every rank tells every peer "I reached epoch E", then waits until all peers
 // said so.  Writes made by earlier kernels of this stream are ordered before the flag by the
 // system-scope fence.
-__device__ void flag_barrier(const omni_ep_peers &pe, uint32_t epoch, uint32_t *status) {
+__device__ void flag_barrier(const omni_ep_peers &pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns = SPIN_LIMIT_NS) {
     __threadfence_system();
     __syncthreads();
     const int t = threadIdx.x;
@@ -63,14 +63,14 @@ __device__ void flag_barrier(const omni_ep_peers &pe, uint32_t epoch, uint32_t *
         const uint64_t t0 = now_ns();
         // epochs only grow; '>=' in wrap-safe form
         while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-            if (now_ns() - t0 > SPIN_LIMIT_NS) { atomicOr(status, OMNI_ST_TIMEOUT); break; }
+            if (now_ns() - t0 > limit_ns) { atomicOr(status, OMNI_ST_TIMEOUT | OMNI_ST_TIMEOUT_BARRIER); break; }
         }
     }
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(128) ep_barrier_kernel(omni_ep_peers pe, uint32_t epoch, uint32_t *status) {
-    flag_barrier(pe, epoch, status);
+__global__ void __launch_bounds__(128) ep_barrier_kernel(omni_ep_peers pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns) {
+    flag_barrier(pe, epoch, status, limit_ns ? limit_ns : SPIN_LIMIT_NS);
 }
 
 // Publish my counts, barrier, then plan.  One block of 128 threads, thread e = expert e.
@@ -143,12 +143,14 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
 // group the block adds the number of rows it delivered to the owner's arrival counter of that
 // group (one system-scope release per block and group), which is what the owner's gate/up
 // kernel waits on before it reads those rows.
+template <bool SIGNAL>
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(omni_ep_peers pe, const uint4 *__restrict__ xn,
                                                           const int32_t *__restrict__ rowmap,
                                                           const int32_t *__restrict__ offsets,
                                                           const int32_t *__restrict__ send_base) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int G = pe.world, EL = OMNI_E / G, gsz = omni_ep_group_size(G);
+    // without SIGNAL (phases separated by a barrier) the owner's experts form one group and nothing is announced
+    const int G = pe.world, EL = OMNI_E / G, gsz = SIGNAL ? omni_ep_group_size(G) : EL;
     const int owner = (int)((blockIdx.x % G + pe.rank + 1) % G);
     const int sub = blockIdx.x / G, nsub = (gridDim.x - (blockIdx.x % G) + G - 1) / G;   // blocks serving this owner
     uint4 *xg = reinterpret_cast<uint4 *>(pe.xg[owner]);
@@ -170,6 +172,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(omni_ep_peers pe, cons
             for (int i = 0; i < 8; i++) out[lane + 32 * i] = v[i];
             if (lane == 0) info[dst] = (pe.rank << 20) | r;
         }
+        if (!SIGNAL) break;
+        __threadfence_system();          // every thread: its own row stores are out before the count is published
         __syncthreads();
         if (threadIdx.x == 0) {
             // rows of [lo, hi) that fell to this block: positions j with (j / 8) % nsub == sub
@@ -183,11 +187,11 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(omni_ep_peers pe, cons
 // One warp per local expert-major row: result row back to the source rank's permuted position.
 __global__ void __launch_bounds__(256) ep_return_kernel(omni_ep_peers pe, const uint4 *__restrict__ d,
                                                         const int32_t *__restrict__ rowinfo,
-                                                        const int32_t *__restrict__ row_bounds, int group) {
+                                                        const int32_t *__restrict__ row_bounds, int group, int group_end) {
     const int lane = threadIdx.x & 31;
     const int warps = gridDim.x * 8;
     const int first = row_bounds[group];
-    int n = row_bounds[group + 1];
+    int n = row_bounds[group_end];
     if (n > OMNI_ROWS) n = 0;
     for (int r = first + blockIdx.x * 8 + (threadIdx.x >> 5); r < n; r += warps) {
         const int info = rowinfo[r];
@@ -212,26 +216,28 @@ cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_so
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, cudaStream_t s) {
-    ep_barrier_kernel<<<1, 128, 0, s>>>(*pe, epoch, status);
+cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
+                                   cudaStream_t s) {
+    ep_barrier_kernel<<<1, 128, 0, s>>>(*pe, epoch, status, limit_ns);
     return cudaGetLastError();
 }
 
 cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
-                                    const int32_t *send_base, int rows8, int n_sm, cudaStream_t s) {
+                                    const int32_t *send_base, int rows8, int signal, int n_sm, cudaStream_t s) {
     // One block per SM at most: the copy is bound by NVLink, not by parallelism, and a small
     // footprint (256 threads x 32 registers) lets it share SMs with a running expert-product
     // kernel of another micro-batch instead of waiting for it.
     (void)rows8;
     int blocks = n_sm - n_sm % pe->world;                // the same number of blocks for every owner
     if (blocks < pe->world) blocks = pe->world;
-    ep_dispatch_kernel<<<blocks, 256, 0, s>>>(*pe, (const uint4 *)xn, rowmap, offsets, send_base);
+    if (signal) ep_dispatch_kernel<true><<<blocks, 256, 0, s>>>(*pe, (const uint4 *)xn, rowmap, offsets, send_base);
+    else ep_dispatch_kernel<false><<<blocks, 256, 0, s>>>(*pe, (const uint4 *)xn, rowmap, offsets, send_base);
     return cudaGetLastError();
 }
 
 cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
-                                  const int32_t *row_bounds, int group, int n_sm, cudaStream_t s) {
-    ep_return_kernel<<<n_sm, 256, 0, s>>>(*pe, (const uint4 *)d, rowinfo, row_bounds, group);
+                                  const int32_t *row_bounds, int group, int group_end, int n_sm, cudaStream_t s) {
+    ep_return_kernel<<<n_sm, 256, 0, s>>>(*pe, (const uint4 *)d, rowinfo, row_bounds, group, group_end);
     return cudaGetLastError();
 }
 

@@ -22,7 +22,9 @@ enum {
 };
 
 /* status word bits (clef_omni_complete) */
-enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_EP_OVERFLOW = 32u };
+enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_EP_OVERFLOW = 32u,
+       /* which bounded wait ran out (set together with OMNI_ST_TIMEOUT) */
+       OMNI_ST_TIMEOUT_BARRIER = 64u, OMNI_ST_TIMEOUT_ARRIVAL = 128u };
 
 /* One token tile of one expert: rows [row0, row0+len) of the permuted buffers. */
 /* group = index of the expert's first tile | (its tile count << 16) */
@@ -53,11 +55,11 @@ typedef struct {
                                        OMNI_EP_READY_WORD on: rows arrived per local expert       */
 } omni_ep_peers;
 enum { OMNI_EP_READY_WORD = 64, OMNI_EP_FLAG_WORDS = 64 + 128 };
-/* local experts are announced as "arrived" in groups of this many (eight groups per rank) */
+/* local experts are announced as "arrived" in groups of this many (four groups per rank) */
 #ifdef __CUDACC__
 __host__ __device__
 #endif
-static inline int omni_ep_group_size(int world) { const int el = OMNI_E / world; return el >= 8 ? el / 8 : 1; }
+static inline int omni_ep_group_size(int world) { const int el = OMNI_E / world; return el >= 4 ? el / 4 : 1; }
 enum { OMNI_EP_RET_GROUPS = 4 };   /* the down product runs as this many launches so that results travel back under it */
 
 /* ---- plain kernels (omni_kernels.cu) ---- */
@@ -109,12 +111,14 @@ cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *t
 /* ret_bounds: [2][RET_GROUPS+1] tile bounds, then row bounds, of the groups the down product is launched in */
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
                                 int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, cudaStream_t s);
-cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, cudaStream_t s);
+/* limit_ns = 0: the default bound */
+cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
+                                   cudaStream_t s);
 cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
-                                    const int32_t *send_base, int rows8, int n_sm, cudaStream_t s);
-/* rows [row_bounds[group], row_bounds[group+1]) */
+                                    const int32_t *send_base, int rows8, int signal, int n_sm, cudaStream_t s);
+/* rows [row_bounds[group], row_bounds[group_end]) */
 cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
-                                  const int32_t *row_bounds, int group, int n_sm, cudaStream_t s);
+                                  const int32_t *row_bounds, int group, int group_end, int n_sm, cudaStream_t s);
 
 #ifdef __cplusplus
 }

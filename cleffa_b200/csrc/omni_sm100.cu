@@ -354,7 +354,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     __nanosleep(500);
                     if (*abort_flag || globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
                         *abort_flag = 1;
-                        atomicOr(status, OMNI_ST_TIMEOUT);
+                        atomicOr(status, OMNI_ST_TIMEOUT | OMNI_ST_TIMEOUT_ARRIVAL);
                         ok = false;
                         break;
                     }

@@ -36,7 +36,7 @@ EXPORTS = [
     "clef_omni_stage_route", "clef_omni_stage_assign", "clef_omni_stage_experts", "clef_omni_read",
     "clef_omni_set_option", "clef_omni_profile", "clef_omni_arena_bytes",
     "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
-    "clef_omni_assign_noalloc", "clef_omni_ep_gate",
+    "clef_omni_assign_noalloc", "clef_omni_ep_gate", "clef_omni_ep_sync",
 ]
 NOALLOC_MAX_ROWS = 4096
 EP_HANDLES, EP_HANDLE_BYTES = 5, 64
@@ -74,6 +74,7 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_ep_connect_local": (C.c_bool, [vp, ci, ci, C.POINTER(vp), cc, cz]),
         "clef_omni_ep_disconnect": (None, [vp]),
         "clef_omni_ep_gate": (C.c_bool, [vp, vp, vp]),
+        "clef_omni_ep_sync": (C.c_bool, [vp, ci, cc, cz]),
         "clef_omni_assign_noalloc": (C.c_bool, [vp, ci, vp, vp, vp, vp, vp, vp, cc, cz]),
     }
     for name, (res, args) in sig.items():
@@ -260,6 +261,10 @@ class OmniBackend:
         """Ranks that live in this process: backends[r] is rank r's OmniBackend."""
         arr = (C.c_void_p * world)(*[b._g for b in backends])
         self._check(self.lib.clef_omni_ep_connect_local(self._g, rank, world, arr, self._err, _ERRLEN))
+
+    def ep_sync(self, timeout_ms: int = 20000):
+        """Barrier across the ranks (every rank must call it), waited for on the host."""
+        self._check(self.lib.clef_omni_ep_sync(self._g, timeout_ms, self._err, _ERRLEN))
 
     def ep_gate(self, wait_event: int | None, record_event: int | None):
         """cudaEvent_t handles (ints) the dispatch phase waits on / records; None for none."""

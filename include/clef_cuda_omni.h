@@ -127,6 +127,12 @@ bool clef_omni_ep_connect(clef_gpu *g, int rank, int world, const clef_omni_ipc_
 /* same, for contexts that live in one process: peers[r] is rank r's context */
 bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *const *peers, char *err, size_t errlen);
 void clef_omni_ep_disconnect(clef_gpu *g);
+/* One barrier across the ranks on the context's stream, waited for on the host.  Every rank
+ * calls it once after all ranks have connected (it also makes the first, slow touch of the
+ * peers' memory happen here and not in the first pass) and may call it again to realign ranks.
+ * Inside a pass every wait on another rank is bounded by 2 s; ranks that start a pass further
+ * apart than that fail the pass with status bit 4. */
+bool clef_omni_ep_sync(clef_gpu *g, int timeout_ms, char *err, size_t errlen);
 /* Overlap of transfers and expert products is the host's choice: drive two (or more) contexts
  * per GPU on separate streams, each with a share of the rank's tokens (micro-batches), all
  * bound to one device copy of the weights.  To keep their phases staggered instead of in
@@ -186,7 +192,8 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
 /* Options: "debug_poison" 0/1 (CLEF_DEBUG_POISON), "router_exact" 0/1 (decide every row with
  * FP64 logits), "router_eps" (bound on the tensor-core logit error, x1e-9), "gemm" 0 =
  * tcgen05 kernels, 1 = plain CUDA-core check kernels, "router" likewise, "profile" 0/1,
- * "reserve_sms" N (the persistent expert kernels use all SMs but N, so that kernels of another
+ * "ep_overlap" 0/1 (expert parallelism: run the transfers under the expert kernels instead of
+ * between them; same results), "reserve_sms" N (the persistent expert kernels use all SMs but N, so that kernels of another
  * context on the same GPU -- another micro-batch -- are not locked out while they run),
  * "alloc_fail_at" N / "launch_fail_at" N (host-side fault injection, 0 = off). */
 bool clef_omni_set_option(clef_gpu *g, const char *name, long value);

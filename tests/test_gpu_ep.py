@@ -24,12 +24,13 @@ def run_single(weights, x, bias=None):
         return out.cpu(), b.read("ids", x.shape[0])
 
 
-def run_sharded(weights, x, splits, bias=None, passes=1):
+def run_sharded(weights, x, splits, bias=None, passes=1, overlap=False):
     world = len(splits)
     backends = [OmniBackend(r) for r in range(world)]
     try:
         for b in backends:
             b.reserve(1)
+            b.set_option("ep_overlap", int(overlap))
         for r, b in enumerate(backends):
             b.ep_connect_local(r, world, backends)
         for b in backends:
@@ -54,11 +55,12 @@ def run_sharded(weights, x, splits, bias=None, passes=1):
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("splits", [(300, 212), (1, 511), (2048, 2048)])
-def test_two_ranks_equal_single_gpu_bitwise(weights0, splits):
+def test_two_ranks_equal_single_gpu_bitwise(weights0, splits, overlap):
     x = orc.make_activations(60 + splits[0], sum(splits))
     want, _ = run_single(weights0, x)
-    got = run_sharded(weights0, x, splits, passes=2)      # second pass reuses every exchange buffer
+    got = run_sharded(weights0, x, splits, passes=2, overlap=overlap)   # second pass reuses every exchange buffer
     assert torch.equal(got, want)
 
 
@@ -79,4 +81,4 @@ def test_all_ranks_equal_single_gpu_bitwise(weights0):
     splits = tuple([257] * (world - 1) + [100])
     x = orc.make_activations(71, sum(splits))
     want, _ = run_single(weights0, x)
-    assert torch.equal(run_sharded(weights0, x, splits), want)
+    assert torch.equal(run_sharded(weights0, x, splits, passes=3), want)
