@@ -226,12 +226,34 @@ def ours(args):
     else:
         bs[0].bind_layer(0, router, gate_up, down)
     b = bs[0]
+    n_layers = max(1, args.layers)
+    if n_layers > 1:
+        # BASELINE configuration 3 on one GPU: a stack of MoE sublayers, each followed by the
+        # residual add, independent random-init weights per layer generated on the device
+        if world != 1:
+            raise SystemExit("--layers needs --gpus 1")
+        b.reserve(T_TOKENS, n_layer=n_layers)
+        g = torch.Generator(device="cuda").manual_seed(SEED)
+        stack = []
+        for l in range(1, n_layers):
+            wl = tuple((torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                       for shape in ((E, H), (E, 2 * F, H), (E, H, F)))
+            b.bind_layer(l, *wl)
+            stack.append(wl)
     xn = x_host.cuda()
     x = torch.zeros(T_TOKENS, H, device="cuda")
+    x0 = xn.float() if n_layers > 1 else None
     cuts = [T_TOKENS * i // micro for i in range(micro + 1)]
     torch.cuda.synchronize()
 
     def step():
+        if n_layers > 1:
+            b.begin()
+            x.copy_(x0)                         # every step starts from the same N(0,1) residual stream
+            for l in range(n_layers):
+                xn.copy_(x)                     # FP32 residual -> BF16 layer input (the norm's place)
+                b.encode_moe(l, xn, x, bounds)
+            return
         if micro == 1:
             b.begin()
             b.encode_moe(0, xn, x, bounds)
@@ -318,11 +340,11 @@ def ours(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(world), "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world}, tokens data-parallel, peer-store dispatch/return over NVLink, {micro} micro-batches per rank on separate streams", "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
+            "config": {"workload": workload_name(world) + (f", {n_layers} stacked layers with residual adds, weights generated on the device" if n_layers > 1 else ""), "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world}, tokens data-parallel, peer-store dispatch/return over NVLink, {micro} micro-batches per rank on separate streams", "l2": "each step streams 1.21 GB of expert weights (> 126 MB L2); no explicit flush",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s",
                     "h2d_bytes_per_step": T_TOKENS * H * 2 + T_TOKENS * H * 4, "d2h_bytes_per_step": T_TOKENS * H * 4},
-            "gpu_launches": (KERNELS_PER_PASS if world == 1 else KERNELS_PER_PASS_EP * micro) * args.steps,
+            "gpu_launches": (KERNELS_PER_PASS * n_layers if world == 1 else KERNELS_PER_PASS_EP * micro) * args.steps,
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "expert_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
@@ -366,6 +388,7 @@ def main():
     ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
     ap.add_argument("--reserve", type=int, default=0, help="SMs the expert kernels leave to the copy kernels with expert parallelism (0: the library default, 32)")
     ap.add_argument("--overlap", action="store_true", help="expert parallelism: run the transfers under the expert kernels")
+    ap.add_argument("--layers", type=int, default=1, help="stack of MoE sublayers with residual adds (one GPU; BASELINE configuration 3 uses 48 at --tokens 16384)")
     ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank, each on its own context and stream (default 1)")
     args = ap.parse_args()
     T_TOKENS = args.tokens

@@ -69,6 +69,9 @@ struct clef_gpu {
     long prof_passes;
     void *stage_x, *stage_res;          /* forward_host staging */
     size_t stage_cap;
+    cudaStream_t copy_stream;           /* forward_host: the residual upload runs beside the expert kernels */
+    cudaEvent_t residual_uploaded;
+    bool wait_residual;                 /* the combine of the current pass must wait for that upload */
     /* expert parallelism (omni_ep.cu); world <= 1 means off */
     struct {
         int rank, world;
@@ -215,6 +218,8 @@ void clef_cuda_omni_close(clef_gpu *g) {
     if (g->trace) cudaFree(g->trace);
     if (g->stage_x) cudaFree(g->stage_x);
     if (g->stage_res) cudaFree(g->stage_res);
+    if (g->copy_stream) { cudaStreamSynchronize(g->copy_stream); cudaStreamDestroy(g->copy_stream); }
+    if (g->residual_uploaded) cudaEventDestroy(g->residual_uploaded);
     for (int p = 0; p < PROF_SLOTS; p++) for (int i = 0; i < N_STAGE_EVENTS; i++) if (g->ev[p][i]) cudaEventDestroy(g->ev[p][i]);
     if (g->own_stream) cudaStreamDestroy(g->stream);
     free(g);
@@ -519,6 +524,7 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
         if (!launched(g, "down experts (check kernel)", omni_launch_down_simple(s->h, L->down, s->sort.offsets, rows8, s->d, g->stream))) return false;
     }
     stage_mark(g, 4);
+    if (g->wait_residual && !launched(g, "residual upload join", cudaStreamWaitEvent(g->stream, g->residual_uploaded, 0))) return false;
     if (!launched(g, "combine", omni_launch_combine(s->d, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
     return true;
@@ -581,6 +587,7 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
         if (!launched(g, "return join", cudaStreamWaitEvent(g->stream, g->ep.ev_returned, 0))) return false;
     }
     if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
+    if (g->wait_residual && !launched(g, "residual upload join", cudaStreamWaitEvent(g->stream, g->residual_uploaded, 0))) return false;
     if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
     return true;
@@ -648,11 +655,26 @@ bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *
         g->stage_x = nx; g->stage_res = nr; g->stage_cap = (size_t)T;
     }
     clef_omni_begin(g);
+    /* The router and the expert products only need xn; the FP32 residual (twice the bytes) is
+     * first touched by the combine, so it is uploaded on a second stream beside them. */
+    if (!g->copy_stream) {
+        if (cudaStreamCreateWithFlags(&g->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&g->residual_uploaded, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            set_err(err, errlen, "cuda: cannot create the Omni upload stream");
+            return false;
+        }
+    }
     cudaError_t e = cudaMemcpyAsync(g->stage_x, xn_host, (size_t)T * OMNI_H * 2, cudaMemcpyHostToDevice, g->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(g->stage_res, x_host, (size_t)T * OMNI_H * 4, cudaMemcpyHostToDevice, g->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(g->stage_res, x_host, (size_t)T * OMNI_H * 4, cudaMemcpyHostToDevice, g->copy_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(g->residual_uploaded, g->copy_stream);
     if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot upload Omni activations: %s", cudaGetErrorString(e)); return false; }
-    if (!clef_omni_encode_moe(g, layer, g->stage_x, g->stage_res, T, n_seq, seq_bounds, err, errlen)) {
+    g->wait_residual = true;
+    const bool encoded = clef_omni_encode_moe(g, layer, g->stage_x, g->stage_res, T, n_seq, seq_bounds, err, errlen);
+    g->wait_residual = false;
+    if (!encoded) {
         cudaStreamSynchronize(g->stream);
+        cudaStreamSynchronize(g->copy_stream);
         return false;
     }
     e = cudaMemcpyAsync(x_host, g->stage_res, (size_t)T * OMNI_H * 4, cudaMemcpyDeviceToHost, g->stream);

@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(256) assign_hist_kernel(const int32_t *__restr
 // per-segment bases, writes counts/offsets and the token-tile list of the expert GEMMs.
 __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_state st) {
     __shared__ int part[8][OMNI_E];
-    __shared__ int cnt[OMNI_E], scan_a[OMNI_E], scan_b[OMNI_E], scan_c[OMNI_E];
+    __shared__ int cnt[OMNI_E], scan_a[OMNI_E], scan_b[OMNI_E];
     const int e = threadIdx.x & (OMNI_E - 1), grp = threadIdx.x >> 7;
     const int per = (nseg + 7) / 8;
     const int s0 = grp * per, s1 = min(nseg, s0 + per);
@@ -310,15 +310,14 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         cnt[e] = total;
         scan_a[e] = total;                          // rows
         scan_b[e] = (total + OMNI_TILE_N - 1) / OMNI_TILE_N;   // token tiles
-        scan_c[e] = 0;
     }
     __syncthreads();
     // inclusive Hillis-Steele scans over the 128 experts
     for (int d = 1; d < OMNI_E; d <<= 1) {
-        int a = 0, b = 0, c = 0;
-        if (grp == 0 && e >= d) { a = scan_a[e - d]; b = scan_b[e - d]; c = scan_c[e - d]; }
+        int a = 0, b = 0;
+        if (grp == 0 && e >= d) { a = scan_a[e - d]; b = scan_b[e - d]; }
         __syncthreads();
-        if (grp == 0) { scan_a[e] += a; scan_b[e] += b; scan_c[e] += c; }
+        if (grp == 0) { scan_a[e] += a; scan_b[e] += b; }
         __syncthreads();
     }
     if (grp == 0) {

@@ -173,3 +173,25 @@ def test_forward_host_equals_device_path(bound0):
     host = res.clone()
     bound0.forward_host(0, x, host)
     assert torch.equal(host, dev)
+
+
+def test_three_layer_stack_teacher_forced(backend):
+    # configuration 3 in miniature: MoE sublayers with a residual add, independent weights per
+    # layer.  Routing flips compound across layers, so every layer is checked on the input the
+    # GPU actually fed it (its own residual, rounded to BF16), and the end is checked too.
+    T, layers = 96, 3
+    ws = [orc.make_weights(20 + l) for l in range(layers)]
+    for l, w in enumerate(ws):
+        backend.bind_layer(l, *w)
+    x = orc.make_activations(30, T).float().cuda()           # FP32 residual stream
+    ref = x.cpu().double()
+    for l in range(layers):
+        xn = x.to(torch.bfloat16)                            # stands in for the FFN norm
+        before = x.clone()
+        backend.begin(); backend.encode_moe(l, xn, x); backend.complete()
+        got = dict(out=(x - before).cpu(), ids=backend.read("ids", T), weights=backend.read("weights", T),
+                   logits=backend.read("logits", T), counts=backend.read("counts"), offsets=backend.read("offsets"),
+                   slots=backend.read("slots", T), rowmap=backend.read("rowmap", T))
+        check_against_oracle(got, xn.cpu(), ws[l])
+        ref = ref + orc.experts(ref.to(torch.bfloat16), got["ids"].astype(np.int64), got["weights"].astype(np.float64), ws[l][1], ws[l][2])
+    assert orc.rel_l2(x.cpu(), ref) <= REL_L2_GATE
