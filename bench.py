@@ -197,6 +197,9 @@ def ours(args):
     bs = [OmniBackend(local, stream=st.cuda_stream) for st in streams]
     for b in bs:
         b.reserve(T_TOKENS)
+        for kv in args.option:                           # library options, name=value (for A/B runs)
+            name, _, val = kv.partition("=")
+            b.set_option(name, int(val))
     if world > 1:
         # expert parallel: 128/world experts per GPU; every rank maps every rank's exchange buffers
         el = E // world
@@ -387,6 +390,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU (default: the headline 4096)")
     ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
     ap.add_argument("--reserve", type=int, default=0, help="SMs the expert kernels leave to the copy kernels with expert parallelism (0: the library default, 32)")
+    ap.add_argument("--option", action="append", default=[], help="library option name=value (clef_omni_set_option), repeatable")
     ap.add_argument("--overlap", action="store_true", help="expert parallelism: run the transfers under the expert kernels")
     ap.add_argument("--layers", type=int, default=1, help="stack of MoE sublayers with residual adds (one GPU; BASELINE configuration 3 uses 48 at --tokens 16384)")
     ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank, each on its own context and stream (default 1)")

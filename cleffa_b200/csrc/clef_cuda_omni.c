@@ -59,6 +59,7 @@ struct clef_gpu {
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
+    int fused_gather;                   /* gate/up fetches its token rows through rowmap (no gather kernel) */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
     long launch_fail_at, launch_count;
     /* pass state */
@@ -151,6 +152,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     g->device = device;
     g->n_sm = prop.multiProcessorCount;
     g->router_eps = 5e-4f;
+    g->fused_gather = 1;
     void *fn = NULL;
     enum cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -512,10 +514,14 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
-    if (!launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
+    /* the tensor-core gate/up kernel fetches its token rows through rowmap itself; the copy
+     * into expert order is only made for the check kernels (or when "fused_gather" is 0) */
+    const bool fused = g->gemm_impl == 0 && g->fused_gather;
+    if (!fused && !launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
     if (g->gemm_impl == 0) {
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, g->n_sm - g->reserve_sms, g->stream))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
+                                                                     fused ? s->sort.rowmap : NULL, g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
         if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, g->n_sm - g->reserve_sms, g->stream))) return false;
     } else {
@@ -561,7 +567,7 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
         if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
         if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
         stage_mark(g, 2);
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, n_gemm, g->stream))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, n_gemm, g->stream))) return false;
         stage_mark(g, 3);
         if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, n_gemm, g->stream))) return false;
         stage_mark(g, 4);
@@ -574,7 +580,7 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
         if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->ep.side))) return false;
         stage_mark(g, 2);
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
-                                                                     g->ep.need, omni_ep_group_size(pe->world), n_gemm, g->stream))) return false;
+                                                                     g->ep.need, omni_ep_group_size(pe->world), NULL, NULL, n_gemm, g->stream))) return false;
         stage_mark(g, 3);
         for (int rg = 0; rg < OMNI_EP_RET_GROUPS; rg++) {
             if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg, n_gemm, g->stream))) return false;
@@ -769,6 +775,8 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "ep_overlap")) g->ep_overlap = value != 0;
+    else if (!strcmp(name, "dependent_launch")) omni_set_dependent_launch(value != 0);
+    else if (!strcmp(name, "fused_gather")) g->fused_gather = value != 0;
     else if (!strcmp(name, "reserve_sms")) { if (value < 0 || value >= g->n_sm) return false; g->reserve_sms = (int)value; }
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }

@@ -99,13 +99,19 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
                                      cudaStream_t s);
 /* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
 /* ready/need (may be NULL): rows that have arrived / must arrive per expert before its token
- * rows may be read (expert parallelism: the rows are written by other GPUs while this runs) */
+ * rows may be read (expert parallelism: the rows are written by other GPUs while this runs).
+ * gather_src/gather_rows (may be NULL): the kernel fetches token row i of the permuted order from
+ * row gather_rows[i] of gather_src ([rows][2048] BF16) itself and tm_x4 is not used */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
-                                     void *h, const uint32_t *ready, const int32_t *need, int group_size, int n_sm,
-                                     cudaStream_t s);
+                                     void *h, const uint32_t *ready, const int32_t *need, int group_size,
+                                     const void *gather_src, const int32_t *gather_rows, int n_sm, cudaStream_t s);
 /* tile_bounds (may be NULL) + group: restrict the launch to tiles [tile_bounds[group], tile_bounds[group+1]) */
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                    void *d, const int32_t *tile_bounds, int group, int n_sm, cudaStream_t s);
+
+/* Programmatic dependent launch of the pass's kernel chain (process-wide, default on) */
+void omni_set_dependent_launch(int on);
+int omni_dependent_launch_enabled(void);
 
 /* ---- expert parallel (omni_ep.cu) ---- */
 /* ret_bounds: [2][RET_GROUPS+1] tile bounds, then row bounds, of the groups the down product is launched in */

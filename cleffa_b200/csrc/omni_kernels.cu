@@ -16,6 +16,7 @@
 #include <stdint.h>
 
 #include "omni_internal.h"
+#include "omni_pdl.cuh"
 
 namespace {
 
@@ -181,6 +182,8 @@ __global__ void __launch_bounds__(128) recheck_kernel(const __nv_bfloat16 *__res
                                                       const int32_t *__restrict__ n_flag, int T, float eps,
                                                       int32_t *__restrict__ ids, float *__restrict__ weights) {
     __shared__ double exact_s[OMNI_E];
+    dep_wait();
+    dep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int n = *n_flag;
     if (n > T) n = T;
@@ -265,6 +268,8 @@ __global__ void __launch_bounds__(256) route_pairs_kernel(const float *__restric
 __global__ void __launch_bounds__(256) assign_hist_kernel(const int32_t *__restrict__ ids, int A, int nseg,
                                                           int32_t *__restrict__ segcount, uint32_t *__restrict__ status) {
     __shared__ int hist[8][OMNI_E];
+    dep_wait();
+    dep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int seg = blockIdx.x * 8 + warp;
 #pragma unroll
@@ -289,6 +294,8 @@ __global__ void __launch_bounds__(256) assign_hist_kernel(const int32_t *__restr
 __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_state st) {
     __shared__ int part[8][OMNI_E];
     __shared__ int cnt[OMNI_E], scan_a[OMNI_E], scan_b[OMNI_E];
+    dep_wait();
+    dep_launch();
     const int e = threadIdx.x & (OMNI_E - 1), grp = threadIdx.x >> 7;
     const int per = (nseg + 7) / 8;
     const int s0 = grp * per, s1 = min(nseg, s0 + per);
@@ -342,6 +349,8 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
 __global__ void __launch_bounds__(256) assign_scatter_kernel(const int32_t *__restrict__ ids, int A, int nseg,
                                                              omni_sort_state st) {
     __shared__ int base[8][OMNI_E];
+    dep_wait();
+    dep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int seg = blockIdx.x * 8 + warp;
     if (seg >= nseg) return;
@@ -371,6 +380,8 @@ __global__ void __launch_bounds__(256) assign_scatter_kernel(const int32_t *__re
 // xg[row] = xn[rowmap[row]]: 4 KiB per row, one warp per row, 16-byte lanes.
 __global__ void __launch_bounds__(256) gather_kernel(const uint4 *__restrict__ xn, const int32_t *__restrict__ rowmap,
                                                      int rows8, uint4 *__restrict__ xg) {
+    dep_wait();
+    dep_launch();
     const int lane = threadIdx.x & 31;
     const int warps = gridDim.x * 8;
     for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < rows8; r += warps) {
@@ -391,6 +402,8 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint4 *__restrict__ x
 __global__ void __launch_bounds__(256) combine_kernel(const uint4 *__restrict__ d, const int32_t *__restrict__ ids,
                                                       const float *__restrict__ weights,
                                                       const int32_t *__restrict__ slots, float *__restrict__ x) {
+    dep_wait();
+    dep_launch();
     const long t = blockIdx.x;
     int id[8], sl[8]; float w[8];
 #pragma unroll
@@ -519,6 +532,11 @@ __global__ void trace_kernel(const float *__restrict__ logits, const int32_t *__
 // ====================================================================== launchers
 extern "C" {
 
+// Process-wide switch for programmatic dependent launch of the pass's kernel chain.
+static int g_dependent_launch = 1;
+int omni_dependent_launch_enabled(void) { return g_dependent_launch; }
+void omni_set_dependent_launch(int on) { g_dependent_launch = on != 0; }
+
 cudaError_t omni_launch_router_simple(const void *xn, const void *router, const float *bias, int T, float *logits,
                                       cudaStream_t s) {
     router_simple_kernel<<<T, 128, 0, s>>>((const __nv_bfloat16 *)xn, (const __nv_bfloat16 *)router, bias, logits);
@@ -536,9 +554,8 @@ cudaError_t omni_launch_recheck(const void *xn, const void *router, const float 
                                 float *weights, uint32_t *status, cudaStream_t s) {
     (void)status;
     int blocks = T < 148 * 8 ? T : 148 * 8;
-    recheck_kernel<<<blocks, 128, 0, s>>>((const __nv_bfloat16 *)xn, (const __nv_bfloat16 *)router, bias, logits,
-                                          flag_rows, n_flag, T, eps, ids, weights);
-    return cudaGetLastError();
+    return omni_launch_chain(recheck_kernel, dim3(blocks), dim3(128), 0, s, (const __nv_bfloat16 *)xn, (const __nv_bfloat16 *)router, bias, logits,
+                             flag_rows, n_flag, T, eps, ids, weights);
 }
 
 cudaError_t omni_launch_router_exact(const void *xn, const void *router, const float *bias, int T, double *logits,
@@ -557,23 +574,21 @@ cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st,
     const int A = rows * OMNI_TOP;
     const int nseg = (A + OMNI_SEG - 1) / OMNI_SEG;
     const int blocks = (nseg + 7) / 8;
-    assign_hist_kernel<<<blocks, 256, 0, s>>>(ids, A, nseg, st.segcount, st.status);
-    assign_scan_kernel<<<1, 1024, 0, s>>>(nseg, st);
-    assign_scatter_kernel<<<blocks, 256, 0, s>>>(ids, A, nseg, st);
-    return cudaGetLastError();
+    cudaError_t e = omni_launch_chain(assign_hist_kernel, dim3(blocks), dim3(256), 0, s, ids, A, nseg, st.segcount, st.status);
+    if (e == cudaSuccess) e = omni_launch_chain(assign_scan_kernel, dim3(1), dim3(1024), 0, s, nseg, st);
+    if (e == cudaSuccess) e = omni_launch_chain(assign_scatter_kernel, dim3(blocks), dim3(256), 0, s, ids, A, nseg, st);
+    return e;
 }
 
 cudaError_t omni_launch_gather(const void *xn, const int32_t *rowmap, int rows8, void *xg, cudaStream_t s) {
     int blocks = (rows8 + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    gather_kernel<<<blocks, 256, 0, s>>>((const uint4 *)xn, rowmap, rows8, (uint4 *)xg);
-    return cudaGetLastError();
+    return omni_launch_chain(gather_kernel, dim3(blocks), dim3(256), 0, s, (const uint4 *)xn, rowmap, rows8, (uint4 *)xg);
 }
 
 cudaError_t omni_launch_combine(const void *d, const int32_t *ids, const float *weights, const int32_t *slots,
                                 float *x, int T, cudaStream_t s) {
-    combine_kernel<<<T, 256, 0, s>>>((const uint4 *)d, ids, weights, slots, x);
-    return cudaGetLastError();
+    return omni_launch_chain(combine_kernel, dim3(T), dim3(256), 0, s, (const uint4 *)d, ids, weights, slots, x);
 }
 
 cudaError_t omni_launch_gateup_simple(const void *xg, const void *gate_up, const int32_t *offsets, int rows8, void *h,

@@ -22,6 +22,7 @@
 #include <stdint.h>
 
 #include "omni_internal.h"
+#include "omni_pdl.cuh"
 
 namespace {
 
@@ -53,6 +54,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p) {
     return v;
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// 16-byte asynchronous copies global -> shared (the LSU path, for rows that are not contiguous)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -190,6 +199,7 @@ template <> struct GemmCfg<MODE_DOWN> {
 
 constexpr int GEMM_THREADS = 384;            // warp 0 scheduler + weight TMA, 1 MMA, 2 TMEM, 3 token TMA, 4..11 epilogue
 constexpr int EPI_WARPS = 8;
+constexpr int GATHER_THREADS = 64;                  // warps 2 and 3 when the kernel gathers its token rows itself
 constexpr int T_TILE_BYTES = OMNI_TILE_N * BK * 2;   // 32 KiB: up to 256 token rows
 
 template <int MODE> struct GemmSmem {
@@ -216,7 +226,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    const omni_ttile *__restrict__ ttiles, const int32_t *__restrict__ n_ttiles,
                    int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status,
                    const uint32_t *__restrict__ ready, const int32_t *__restrict__ need, int group_size,
-                   const int32_t *__restrict__ tile_bounds, int tile_group) {
+                   const int32_t *__restrict__ tile_bounds, int tile_group,
+                   const __nv_bfloat16 *__restrict__ gather_src, const int32_t *__restrict__ gather_rows) {
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
     constexpr int WS = C::W_STAGES, TS = C::T_STAGES;
@@ -246,27 +257,29 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     volatile WorkSlot *ring = reinterpret_cast<volatile WorkSlot *>(misc + 16 + 64);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the launch covers work items [work_lo, n_work): everything, or one group of experts
-    const int work_lo = tile_bounds ? tile_bounds[tile_group] * C::MTILES : 0;
-    const int n_work = tile_bounds ? min(tile_bounds[tile_group + 1], *n_ttiles) * C::MTILES : *n_ttiles * C::MTILES;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < WS; s++) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 1); }
-        for (int s = 0; s < TS; s++) { mbar_init(tfull_bar(s), 1); mbar_init(tempty_bar(s), 1); }
+        for (int s = 0; s < TS; s++) { mbar_init(tfull_bar(s), gather_src ? GATHER_THREADS : 1); mbar_init(tempty_bar(s), 1); }
         for (int s = 0; s < 8; s++) { armed_w[s] = -1; armed_t[s] = -1; }
         for (int b = 0; b < 2; b++) { mbar_init(afull_bar(b), 1); mbar_init(aempty_bar(b), EPI_WARPS); }
         mbar_init(drain_bar, 1);
-        for (int r = 0; r < RING; r++) { mbar_init(ifull_bar(r), 1); mbar_init(iempty_bar(r), 2 + EPI_WARPS); }
+        for (int r = 0; r < RING; r++) { mbar_init(ifull_bar(r), 1); mbar_init(iempty_bar(r), (gather_src ? GATHER_THREADS : 1) + 1 + EPI_WARPS); }
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_w);
         for (int i = 0; i < 4; i++) prefetch_tmap(&tm_tok.m[i]);
     }
     if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 512); tmem_relinquish(); }
+    dep_wait();                 // everything above overlaps the tail of the previous kernel
+    dep_launch();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the launch covers work items [work_lo, n_work): everything, or one group of experts
+    const int work_lo = tile_bounds ? tile_bounds[tile_group] * C::MTILES : 0;
+    const int n_work = tile_bounds ? min(tile_bounds[tile_group + 1], *n_ttiles) * C::MTILES : *n_ttiles * C::MTILES;
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- scheduler + weight producer
@@ -331,6 +344,74 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             cur = nxt; cur_m = nxt_m; cur_cnt = nxt_cnt;
             w1 = w2;
         }
+    } else if ((warp == 2 || warp == 3) && gather_src) {
+        // ---------------------------------------------------------- token producer, gathering
+        // The token rows of an expert are scattered over the activation matrix.  Instead of a
+        // kernel that first copies them into expert order (a write and a read of T*8 rows in
+        // HBM), these 64 threads fetch them here: 16-byte asynchronous copies, eight threads per
+        // 128-byte row segment, stored in the 128-byte-swizzled layout the MMA descriptors
+        // expect (chunk c of row r at c ^ (r & 7) inside its 8-row group).  A stage is handed to
+        // the MMA thread two stages after it was issued, once this thread's copies have landed
+        // and are ordered before the tensor core's reads.
+        constexpr int LAG = 2;
+        static_assert(TS > LAG, "token ring too short for the copy lag");
+        const uint64_t pol_t = l2_policy_evict_last();    // every row is read again for each weight tile
+        const int gt = threadIdx.x - 64;                  // 0..63
+        const int c = gt & 7, rb = gt >> 3;               // chunk of the row segment, row inside the 8-row group
+        const uint32_t dst_off = (uint32_t)(rb * 128 + ((c ^ rb) << 4));
+        const char *src0 = reinterpret_cast<const char *>(gather_src) + c * 16;
+        PipeState p, pend, wr;
+        int off[OMNI_TILE_N / 8], off_next[OMNI_TILE_N / 8];   // byte offsets of this thread's rows, -1 past the tile
+        // takes the next item from the ring and starts the loads of its row indices
+        auto next_item = [&](int (&o)[OMNI_TILE_N / 8]) -> int {
+            if (!mbar_wait(ifull_bar(wr.stage), wr.phase, abort_flag, status)) return -1;
+            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len;
+            mbar_arrive(iempty_bar(wr.stage));
+            wr.advance(RING);
+#pragma unroll
+            for (int i = 0; i < OMNI_TILE_N / 8; i++) {
+                const int r = rb + 8 * i;
+                o[i] = r < len ? gather_rows[row0 + r] * (OMNI_H * 2) : -1;
+            }
+            return len;
+        };
+        int len = next_item(off);
+        while (len >= 0) {
+            bool ok = true;
+            for (int ks = 0; ks < KSTAGES; ks++) {
+                if (ks >= LAG) {
+                    // hand over the oldest stage before blocking on a free one: the MMA thread
+                    // must never wait for this loop to issue further copies
+                    cp_async_wait<LAG - 1>();
+                    fence_proxy_async_smem();
+                    mbar_arrive(tfull_bar(pend.stage));
+                    pend.advance(TS);
+                }
+                ok = mbar_wait(tempty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
+                if (!ok) break;
+                const uint32_t sb = tok_base + p.stage * T_TILE_BYTES + dst_off;
+                const char *src = src0 + ks * (BK * 2);
+#pragma unroll
+                for (int i = 0; i < OMNI_TILE_N / 8; i++)
+                    if (off[i] >= 0) cp_async16(sb + i * 1024, src + off[i], pol_t);
+                cp_async_commit();
+                p.advance(TS);
+            }
+            if (!ok) break;
+            // the next item's row indices travel while the last two stages of this one land
+            len = next_item(off_next);
+            cp_async_wait<1>();
+            fence_proxy_async_smem();
+            mbar_arrive(tfull_bar(pend.stage));
+            pend.advance(TS);
+            cp_async_wait<0>();
+            fence_proxy_async_smem();
+            mbar_arrive(tfull_bar(pend.stage));
+            pend.advance(TS);
+#pragma unroll
+            for (int i = 0; i < OMNI_TILE_N / 8; i++) off[i] = off_next[i];
+        }
+        cp_async_wait<0>();
     } else if (warp == 3 && lane == 0) {
         // ---------------------------------------------------------- token producer
         PipeState p, wr;
@@ -593,6 +674,8 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         prefetch_tmap(&tm_w);
     }
     if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 128); tmem_relinquish(); }
+    dep_wait();                 // everything above overlaps the tail of the previous kernel
+    dep_launch();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -742,29 +825,28 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
                                      int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
                                      cudaStream_t s) {
-    router_sm100_kernel<<<(T + 127) / 128, RT_THREADS, RT_SMEM_BYTES, s>>>(*tm_x, *tm_w, bias, T, eps, exact_all, logits,
-                                                                          ids, weights, flag_rows, n_flag, status, dbg);
-    return cudaGetLastError();
+    return omni_launch_chain(router_sm100_kernel, dim3((T + 127) / 128), dim3(RT_THREADS), RT_SMEM_BYTES, s, *tm_x, *tm_w, bias, T,
+                             eps, exact_all, logits, ids, weights, flag_rows, n_flag, status, dbg);
 }
 
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
-                                     void *h, const uint32_t *ready, const int32_t *need, int group_size, int n_sm,
-                                     cudaStream_t s) {
+                                     void *h, const uint32_t *ready, const int32_t *need, int group_size,
+                                     const void *gather_src, const int32_t *gather_rows, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
-    expert_gemm_kernel<MODE_GATEUP><<<n_sm, GEMM_THREADS, GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status, ready, need, group_size > 0 ? group_size : 1, nullptr, 0);
-    return cudaGetLastError();
+    return omni_launch_chain(expert_gemm_kernel<MODE_GATEUP>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s,
+                             *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status, ready, need,
+                             group_size > 0 ? group_size : 1, nullptr, 0, (const __nv_bfloat16 *)gather_src, gather_rows);
 }
 
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                    void *d, const int32_t *tile_bounds, int group, int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
-    expert_gemm_kernel<MODE_DOWN><<<n_sm, GEMM_THREADS, GemmSmem<MODE_DOWN>::TOTAL_BYTES, s>>>(
-        *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d, st.status, nullptr,
-        nullptr, 1, tile_bounds, group);
-    return cudaGetLastError();
+    return omni_launch_chain(expert_gemm_kernel<MODE_DOWN>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_DOWN>::TOTAL_BYTES, s,
+                             *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d,
+                             st.status, nullptr, nullptr, 1, tile_bounds, group, (const __nv_bfloat16 *)nullptr,
+                             (const int32_t *)nullptr);
 }
 
 }  // extern "C"

@@ -195,6 +195,10 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
  * "ep_overlap" 0/1 (expert parallelism: run the transfers under the expert kernels instead of
  * between them; same results), "reserve_sms" N (the persistent expert kernels use all SMs but N, so that kernels of another
  * context on the same GPU -- another micro-batch -- are not locked out while they run),
+ * "fused_gather" 0/1 (default 1: the gate/up kernel fetches its token rows through the permutation
+ * itself instead of reading a copy in expert order made by a separate kernel; same results),
+ * "dependent_launch" 0/1 (default 1, process-wide: the kernels of a pass are launched so that each one's
+ * prologue overlaps the tail of the one before),
  * "alloc_fail_at" N / "launch_fail_at" N (host-side fault injection, 0 = off). */
 bool clef_omni_set_option(clef_gpu *g, const char *name, long value);
 /* With "profile" on every pass records stage marks on the stream without waiting.  This call

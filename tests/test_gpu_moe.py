@@ -76,6 +76,23 @@ def test_tcgen05_and_check_kernels_agree(bound0):
     assert orc.rel_l2(fast["out"], slow["out"]) < 5e-3          # both round h and d to BF16; sums differ in order
 
 
+@pytest.mark.parametrize("T", [1, 37, 300, 2500])
+def test_launch_variants_give_the_same_bits(bound0, T):
+    """The gate/up kernel fetching its rows through the permutation, the separate gather
+    kernel, and dependent launch on or off are ways of scheduling the same arithmetic."""
+    b = bound0
+    x = orc.make_activations(17, T)
+    base = run_block(b, 0, x)
+    try:
+        for fused, dep in ((0, 1), (1, 0), (0, 0)):
+            b.set_option("fused_gather", fused); b.set_option("dependent_launch", dep)
+            other = run_block(b, 0, x)
+            assert np.array_equal(base["ids"], other["ids"]) and np.array_equal(base["slots"], other["slots"])
+            assert np.array_equal(base["out"], other["out"]), (fused, dep)
+    finally:
+        b.set_option("fused_gather", 1); b.set_option("dependent_launch", 1)
+
+
 def test_golden_ids_of_config1(bound0):
     from pathlib import Path
     g = np.load(Path(__file__).resolve().parent / "golden" / "route_c1.npz")
