@@ -34,8 +34,8 @@ H, F, E, TOP = 2048, 768, 128, 8
 GATEUP_FLOP_PER_TOKEN = 2 * H * (2 * F) * TOP          # 50,331,648
 EXPERT_FLOP_PER_TOKEN = GATEUP_FLOP_PER_TOKEN + 2 * F * H * TOP   # 75,497,472
 WEIGHT_BYTES = (E * H + E * 2 * F * H + E * H * F) * 2
-KERNELS_PER_PASS = 9     # router, exact pass, histogram, scan, scatter, gather, gate/up, down, combine
-KERNELS_PER_PASS_EP = 13 # ... with plan, dispatch, return and two barriers instead of gather
+KERNELS_PER_PASS = 8     # router, exact pass, histogram, scan, scatter, gate/up (gathers its rows), down, combine
+KERNELS_PER_PASS_EP = 13 # ... plus plan, dispatch, return and two barriers
 METRIC = "MoE-layer prefill tokens/sec at T=4096"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at T=4096, from the ncu
 # capture summarised in profiles/ncu_full_router_gather_experts_combine_T4096.md
@@ -276,25 +276,40 @@ def ours(args):
     for bi in bs:
         bi.complete()
 
-    # ---- device-resident timing (value) with per-stage marks for the roofline
-    b.set_option("profile", 1)
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        start.record(main_stream)
-        for st in streams[1:]:
-            st.wait_event(start)
-        for _ in range(args.steps):
-            step()
-        for st in streams[1:]:
-            done = torch.cuda.Event()
-            done.record(st)
-            main_stream.wait_event(done)
-        stop.record(main_stream)
+    # ---- device-resident timing.  Two timed regions of the same K steps: the first gives
+    # `value`; the second repeats it with a CUDA event recorded between the stages of every pass
+    # and gives the per-kernel durations for the roofline.  The marks are kept out of the first
+    # region because they cost about 20 us per pass and stop a kernel's prologue from
+    # overlapping the previous kernel's tail.
+    def timed_region():
         barrier()
-    for bi in bs:
-        bi.complete()
-    elapsed_ms = start.elapsed_time(stop)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as sampler:
+            start.record(main_stream)
+            for st in streams[1:]:
+                st.wait_event(start)
+            for _ in range(args.steps):
+                step()
+            for st in streams[1:]:
+                done = torch.cuda.Event()
+                done.record(st)
+                main_stream.wait_event(done)
+            stop.record(main_stream)
+            barrier()
+        for bi in bs:
+            bi.complete()
+        return start.elapsed_time(stop), sampler
+
+    elapsed_ms, clocks = timed_region()
+    if args.kernels_only and world == 1:
+        # for captures under a profiler: the warm-up and the K timed steps, nothing else
+        if rank == 0:
+            print(json.dumps({"kernels_only": True, "ms_per_step": elapsed_ms / args.steps, "tokens": T_TOKENS, "n_gpus": world}))
+        for bi in bs:
+            bi.close()
+        return
+    b.set_option("profile", 1)
+    marked_ms, _ = timed_region()
     stages = b.profile()
     b.set_option("profile", 0)
     if world > 1:
@@ -355,6 +370,7 @@ def ours(args):
                          "traffic": GATEUP_DRAM_TRAFFIC_T4096 if (T_TOKENS == 4096 and world == 1) else None,
                          "algorithmic_bytes": E * 2 * F * H * 2 + T_TOKENS * TOP * H * 2 + T_TOKENS * TOP * F * 2},
             "stages_ms": stages,
+            "stages_note": f"from a second timed region of the same {args.steps} steps with an event recorded between stages ({marked_ms / args.steps:.4f} ms per step)",
             "expert_gemms": {"tflops": EXPERT_FLOP_PER_TOKEN * T_TOKENS / (both_ms * 1e-3) / 1e12 if both_ms > 0 else 0.0,
                              "frac_of_bf16_peak": (EXPERT_FLOP_PER_TOKEN * T_TOKENS / (both_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]) if both_ms > 0 else 0.0},
             "hbm": {"weights_gbs_over_layer": WEIGHT_BYTES / (elapsed_ms / args.steps * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"]},
@@ -390,6 +406,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU (default: the headline 4096)")
     ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
     ap.add_argument("--reserve", type=int, default=0, help="SMs the expert kernels leave to the copy kernels with expert parallelism (0: the library default, 32)")
+    ap.add_argument("--kernels-only", action="store_true", help="run the warm-up and the timed steps and stop (for profiler captures; one GPU)")
     ap.add_argument("--option", action="append", default=[], help="library option name=value (clef_omni_set_option), repeatable")
     ap.add_argument("--overlap", action="store_true", help="expert parallelism: run the transfers under the expert kernels")
     ap.add_argument("--layers", type=int, default=1, help="stack of MoE sublayers with residual adds (one GPU; BASELINE configuration 3 uses 48 at --tokens 16384)")

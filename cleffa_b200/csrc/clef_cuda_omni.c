@@ -59,6 +59,7 @@ struct clef_gpu {
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
+    int fused_router;                   /* the router kernel counts experts per sort segment (no histogram kernel) */
     int fused_gather;                   /* gate/up fetches its token rows through rowmap (no gather kernel) */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
     long launch_fail_at, launch_count;
@@ -153,6 +154,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     g->n_sm = prop.multiProcessorCount;
     g->router_eps = 5e-4f;
     g->fused_gather = 1;
+    g->fused_router = 1;
     void *fn = NULL;
     enum cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -487,8 +489,10 @@ static bool check_pass(clef_gpu *g, int layer, bool need_weights, char *err, siz
 static void stage_mark(clef_gpu *g, int i) { if (g->profile) cudaEventRecord(g->ev[g->prof_passes % PROF_SLOTS][i], g->stream); }
 
 /* router + exact pass for one chunk; fills arena ids/weights/logits */
-static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int rows) {
+static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int rows, bool *have_counts) {
     omni_arena *s = g->omni;
+    bool fused = false;
+    *have_counts = false;
     if (!launched(g, "flag reset", cudaMemsetAsync(s->n_flag, 0, 4, g->stream))) return false;
     if (g->router_impl == 0) {
         CUtensorMap tm_x;
@@ -496,24 +500,30 @@ static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int row
             note_failure(g, "router activation descriptor", cudaErrorInvalidValue);
             return false;
         }
+        /* default: the router kernel also counts the experts per sort segment and the exact
+         * pass moves the counts of the rows it re-decides, so no histogram kernel is launched */
+        fused = g->fused_router != 0;
         if (!launched(g, "router", omni_launch_router_sm100(&tm_x, &L->tm_router, L->bias, rows, g->router_eps, g->router_exact,
                                                             s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status,
-                                                            g->debug_stamps ? s->stamps : NULL, g->stream))) return false;
+                                                            g->debug_stamps ? s->stamps : NULL, fused ? s->sort.segcount : NULL,
+                                                            g->stream))) return false;
     } else {
         if (!launched(g, "router (check kernel)", omni_launch_router_simple(xn, L->router, L->bias, rows, s->logits, g->stream))) return false;
         if (!launched(g, "route", omni_launch_select(s->logits, rows, g->router_eps, g->router_exact, s->ids, s->weights,
                                                      s->flag_rows, s->n_flag, s->status, g->stream))) return false;
     }
-    return launched(g, "router exact pass", omni_launch_recheck(xn, L->router, L->bias, s->logits, s->flag_rows, s->n_flag, rows,
-                                                                g->router_eps, s->ids, s->weights, s->status, g->stream));
+    if (!launched(g, "router exact pass", omni_launch_recheck(fused ? s->sort.segcount : NULL, xn, L->router, L->bias, s->logits, s->flag_rows,
+                                                              s->n_flag, rows, g->router_eps, s->ids, s->weights, s->status, g->stream))) return false;
+    *have_counts = fused;
+    return true;
 }
 
 /* permutation + expert products + combine for one chunk, routing taken from ids/weights */
 static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const int32_t *ids, const float *weights,
-                        float *x, int rows) {
+                        float *x, int rows, bool have_counts) {
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
-    if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
+    if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, have_counts, g->stream))) return false;
     /* the tensor-core gate/up kernel fetches its token rows through rowmap itself; the copy
      * into expert order is only made for the check kernels (or when "fused_gather" is 0) */
     const bool fused = g->gemm_impl == 0 && g->fused_gather;
@@ -551,7 +561,7 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
  * measured 5 % faster on 8 GPUs at 4096 tokens per rank (0.733 against 0.768 ms per pass): the
  * copies are slower on few SMs and the products slower on fewer, which eats most of the overlap. */
 static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, const int32_t *ids, const float *weights,
-                           float *x, int rows) {
+                           float *x, int rows, bool have_counts) {
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
     const omni_ep_peers *pe = &g->ep.peers;
@@ -559,7 +569,7 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
     const int32_t *row_bounds = g->ep.ret_bounds + OMNI_EP_RET_GROUPS + 1;
     /* with overlap the persistent expert kernels leave some SMs to the copy kernels */
     const int n_gemm = g->n_sm - (g->reserve_sms > 0 ? g->reserve_sms : overlap ? 16 : 0);
-    if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, g->stream))) return false;
+    if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, have_counts, g->stream))) return false;
     if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds, g->stream))) return false;
     if (!overlap) {
         if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->stream, g->ep.gate_wait, 0))) return false;
@@ -629,13 +639,14 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
         const int rows = T - start < OMNI_CHUNK ? T - start : OMNI_CHUNK;
         const char *xn_c = (const char *)xn + (size_t)start * OMNI_H * 2;
         stage_mark(g, 0);
-        bool ok = run_router(g, L, xn_c, rows);
+        bool have_counts = false;
+        bool ok = run_router(g, L, xn_c, rows, &have_counts);
         if (ok && g->trace && layer < g->trace_layers && start + rows > g->trace_first)
             ok = launched(g, "route capture", omni_launch_trace(s->logits, s->ids, s->weights, rows, start, g->trace_first,
                                                                 g->trace_rows, layer, g->trace, g->stream));
         stage_mark(g, 1);
-        if (ok) ok = g->ep.world > 1 ? run_experts_ep(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows)
-                                     : run_experts(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows);
+        if (ok) ok = g->ep.world > 1 ? run_experts_ep(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows, have_counts)
+                                     : run_experts(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows, have_counts);
         if (!ok) { set_err(err, errlen, "%s", g->fail_msg); return false; }
         book_profile(g);
         g->last_T = rows;
@@ -719,7 +730,7 @@ bool clef_omni_stage_assign(clef_gpu *g, const int32_t *ids, int rows, int32_t *
     }
     omni_sort_state st = g->omni->sort;
     st.counts = counts; st.offsets = offsets; st.rowmap = rowmap; st.slots = slots;
-    if (!launched(g, "assign", omni_launch_assign(ids, rows, st, g->stream))) {
+    if (!launched(g, "assign", omni_launch_assign(ids, rows, st, 0, g->stream))) {
         set_err(err, errlen, "%s", g->fail_msg);
         return false;
     }
@@ -734,7 +745,7 @@ bool clef_omni_stage_experts(clef_gpu *g, int layer, const void *xn, const int32
         return false;
     }
     stage_mark(g, 0); stage_mark(g, 1);
-    if (!run_experts(g, &g->layer[layer], xn, ids, weights, x, T)) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    if (!run_experts(g, &g->layer[layer], xn, ids, weights, x, T, false)) { set_err(err, errlen, "%s", g->fail_msg); return false; }
     book_profile(g);
     g->last_T = T;
     return true;
@@ -776,6 +787,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "ep_overlap")) g->ep_overlap = value != 0;
     else if (!strcmp(name, "dependent_launch")) omni_set_dependent_launch(value != 0);
+    else if (!strcmp(name, "fused_router")) g->fused_router = value != 0;
     else if (!strcmp(name, "fused_gather")) g->fused_gather = value != 0;
     else if (!strcmp(name, "reserve_sms")) { if (value < 0 || value >= g->n_sm) return false; g->reserve_sms = (int)value; }
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }

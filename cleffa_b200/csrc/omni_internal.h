@@ -67,14 +67,15 @@ cudaError_t omni_launch_router_simple(const void *xn, const void *router, const 
                                       float *logits, cudaStream_t s);
 cudaError_t omni_launch_select(const float *logits, int T, float eps, int exact_all, int32_t *ids, float *weights,
                                int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s);
-cudaError_t omni_launch_recheck(const void *xn, const void *router, const float *bias, const float *logits,
+cudaError_t omni_launch_recheck(int32_t *segcount, const void *xn, const void *router, const float *bias, const float *logits,
                                 const int32_t *flag_rows, const int32_t *n_flag, int T, float eps,
                                 int32_t *ids, float *weights, uint32_t *status, cudaStream_t s);
 cudaError_t omni_launch_router_exact(const void *xn, const void *router, const float *bias, int T,
                                      double *logits, cudaStream_t s);
 cudaError_t omni_launch_route_pairs(const float *hi, const float *lo, int rows, int32_t *ids, float *weights,
                                     uint32_t *status, cudaStream_t s);
-cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st, cudaStream_t s);
+/* have_counts: st.segcount already holds the per-segment expert counts of ids (the router kernel wrote them) */
+cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st, int have_counts, cudaStream_t s);
 cudaError_t omni_launch_gather(const void *xn, const int32_t *rowmap, int rows8, void *xg, cudaStream_t s);
 cudaError_t omni_launch_combine(const void *d, const int32_t *ids, const float *weights, const int32_t *slots,
                                 float *x, int T, cudaStream_t s);
@@ -96,7 +97,10 @@ cudaError_t omni_sm100_configure(void);   /* opt-in shared-memory sizes; call on
 cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
                                      int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
-                                     cudaStream_t s);
+                                     int32_t *segcount, cudaStream_t s);
+/* segcount (may be NULL): the kernel also writes the per-segment expert counts of the counting
+ * sort for the ids it selected; omni_launch_recheck must then be given the same pointer so that
+ * the rows it re-decides move their counts */
 /* tm_x4 / tm_h4: four maps of the same buffer with box heights 32, 64, 128 and 256 rows */
 /* ready/need (may be NULL): rows that have arrived / must arrive per expert before its token
  * rows may be read (expert parallelism: the rows are written by other GPUs while this runs).

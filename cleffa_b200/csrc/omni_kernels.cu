@@ -16,72 +16,10 @@
 #include <stdint.h>
 
 #include "omni_internal.h"
+#include "omni_exact.cuh"
 #include "omni_pdl.cuh"
 
 namespace {
-
-constexpr unsigned FULL = 0xffffffffu;
-
-__device__ __forceinline__ float bf16_bits_to_float(uint32_t b16) { return __uint_as_float(b16 << 16); }
-
-// ------------------------------------------------------------------ warp-level top-k
-// Order: larger value first, equal values -> lower expert id first (clef.metal:2376-2382).
-struct Best { double v; int id; };
-
-__device__ __forceinline__ bool better(double v, int id, double ov, int oid) {
-    return v > ov || (v == ov && id < oid);
-}
-
-__device__ __forceinline__ Best warp_argmax(double v, int id) {
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) {
-        const double ov = __shfl_xor_sync(FULL, v, s);
-        const int oid = __shfl_xor_sync(FULL, id, s);
-        if (better(ov, oid, v, id)) { v = ov; id = oid; }
-    }
-    return Best{v, id};
-}
-
-// Each lane owns experts lane, lane+32, lane+64, lane+96.  Extracts the `n` best (n <= 9)
-// in order into top_v/top_id (identical on every lane).  Taken entries become -inf.
-template <int N>
-__device__ __forceinline__ void warp_topn(double (&val)[4], int lane, double (&top_v)[N], int (&top_id)[N]) {
-#pragma unroll
-    for (int r = 0; r < N; r++) {
-        double bv = val[0]; int bid = lane;
-#pragma unroll
-        for (int j = 1; j < 4; j++) if (better(val[j], lane + 32 * j, bv, bid)) { bv = val[j]; bid = lane + 32 * j; }
-        const Best b = warp_argmax(bv, bid);
-        top_v[r] = b.v; top_id[r] = b.id;
-#pragma unroll
-        for (int j = 0; j < 4; j++) if (lane + 32 * j == b.id) val[j] = -CUDART_INF;
-    }
-}
-
-// Lanes 0..7 hold the selected logits; weights are softmax over the selected eight, which
-// equals softmax over all experts renormalised by the selected sum (clef.metal:2393).
-__device__ __forceinline__ void write_selection(const double (&top_v)[9], const int (&top_id)[9], int lane,
-                                                int32_t *ids, float *weights, long row) {
-    double p = 0.0;
-#pragma unroll
-    for (int k = 0; k < 8; k++) if (lane == k) p = exp(top_v[k] - top_v[0]);
-    double sum = p;
-#pragma unroll
-    for (int s = 4; s > 0; s >>= 1) sum += __shfl_xor_sync(FULL, sum, s);
-    if (lane < 8) {
-        int id = 0;
-#pragma unroll
-        for (int k = 0; k < 8; k++) if (lane == k) id = top_id[k];
-        ids[row * 8 + lane] = id;
-        weights[row * 8 + lane] = (float)(p / sum);
-    }
-}
-
-__device__ __forceinline__ void write_fallback(int lane, int32_t *ids, float *weights, long row, uint32_t *status) {
-    // clef.metal:2362-2367: report once, keep the pass well-defined.
-    if (lane == 0) atomicOr(status, OMNI_ST_NONFINITE);
-    if (lane < 8) { ids[row * 8 + lane] = lane; weights[row * 8 + lane] = 0.0f; }
-}
 
 // ------------------------------------------------------------------ check-path logits
 // One block per token, one thread per expert; FP32 accumulation.  Slow: a cross-check for
@@ -136,93 +74,22 @@ __global__ void __launch_bounds__(256) select_kernel(const float *__restrict__ l
     if (close && lane == 0) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
 }
 
-// ------------------------------------------------------------------ exact dot (FP64 sum of exact products)
-// A lane owns K elements lane*8 + 256*i .. +7 (i < 8): one 16-byte load per step.
-struct XRow { uint4 q[8]; };
-
-__device__ __forceinline__ XRow load_xrow(const __nv_bfloat16 *xn, long row, int lane) {
-    XRow r;
-    const uint4 *p = reinterpret_cast<const uint4 *>(xn + row * OMNI_H);
-#pragma unroll
-    for (int i = 0; i < 8; i++) r.q[i] = __ldg(p + lane + 32 * i);
-    return r;
-}
-
-// bf16*bf16 is exact in FP32 (8+8 significand bits); the FP64 sum of 2048 such terms is
-// accurate to ~1e-13, far inside the 1e-9 bound of tests/test_omni_router.m:44.
-__device__ __forceinline__ double exact_dot(const XRow &x, const __nv_bfloat16 *wrow, int lane) {
-    const uint4 *p = reinterpret_cast<const uint4 *>(wrow);
-    uint4 w[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) w[i] = __ldg(p + lane + 32 * i);
-    double acc[4] = {0.0, 0.0, 0.0, 0.0};      // four chains: the FP64 adds overlap instead of serialising
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const uint32_t xu[4] = {x.q[i].x, x.q[i].y, x.q[i].z, x.q[i].w};
-        const uint32_t wu[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            acc[j] += (double)(bf16_bits_to_float(xu[j] & 0xffffu) * bf16_bits_to_float(wu[j] & 0xffffu));
-            acc[j] += (double)(bf16_bits_to_float(xu[j] >> 16) * bf16_bits_to_float(wu[j] >> 16));
-        }
-    }
-    double sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(FULL, sum, s);
-    return sum;
-}
-
-// One block (four warps) per flagged row: exact logits for every expert that can still reach
-// the top eight (approximate logit within 2*eps of the approximate 8th), spread over the
-// warps, then the final order by warp 0.
+// One block (four warps) per flagged row.
 __global__ void __launch_bounds__(128) recheck_kernel(const __nv_bfloat16 *__restrict__ xn,
                                                       const __nv_bfloat16 *__restrict__ w,
                                                       const float *__restrict__ bias, const float *__restrict__ logits,
                                                       const int32_t *__restrict__ flag_rows,
                                                       const int32_t *__restrict__ n_flag, int T, float eps,
-                                                      int32_t *__restrict__ ids, float *__restrict__ weights) {
+                                                      int32_t *__restrict__ ids, float *__restrict__ weights,
+                                                      int32_t *__restrict__ segcount) {
     __shared__ double exact_s[OMNI_E];
     dep_wait();
     dep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int n = *n_flag;
     if (n > T) n = T;
-    for (int f = blockIdx.x; f < n; f += gridDim.x) {
-        const long row = flag_rows[f];
-        exact_s[threadIdx.x] = -CUDART_INF;
-        double val[4], approx[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) approx[j] = val[j] = (double)logits[row * OMNI_E + lane + 32 * j];
-        double top_v[8]; int top_id[8];
-        warp_topn<8>(val, lane, top_v, top_id);               // every warp finds the same threshold
-        const double floor_v = top_v[7] - 2.0 * (double)eps;
-        const XRow x = load_xrow(xn, row, lane);
-        __syncthreads();
-        int c = 0;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            unsigned m = __ballot_sync(FULL, approx[j] >= floor_v);
-            while (m) {
-                const int src = __ffs(m) - 1;
-                m &= m - 1;
-                if ((c++ & 3) != warp) continue;              // candidates round-robin over the warps
-                const int e = src + 32 * j;
-                double v = exact_dot(x, w + (long)e * OMNI_H, lane);
-                if (bias) v += (double)bias[e];
-                if (lane == 0) exact_s[e] = v;
-            }
-        }
-        __syncthreads();
-        if (warp == 0) {
-            double exact[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) exact[j] = exact_s[lane + 32 * j];
-            double fin_v[9]; int fin_id[9];
-            warp_topn<9>(exact, lane, fin_v, fin_id);         // the 9th is unused here
-            write_selection(fin_v, fin_id, lane, ids, weights, row);
-        }
-        __syncthreads();
-    }
+    for (int f = blockIdx.x; f < n; f += gridDim.x)
+        recheck_row(xn, w, bias, logits, flag_rows[f], eps, ids, weights, segcount, exact_s, lane, warp, [] { __syncthreads(); });
 }
 
 // Exact logits for every (token, expert): tests only (tests/test_omni_router.m).
@@ -549,13 +416,13 @@ cudaError_t omni_launch_select(const float *logits, int T, float eps, int exact_
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_recheck(const void *xn, const void *router, const float *bias, const float *logits,
+cudaError_t omni_launch_recheck(int32_t *segcount, const void *xn, const void *router, const float *bias, const float *logits,
                                 const int32_t *flag_rows, const int32_t *n_flag, int T, float eps, int32_t *ids,
                                 float *weights, uint32_t *status, cudaStream_t s) {
     (void)status;
     int blocks = T < 148 * 8 ? T : 148 * 8;
     return omni_launch_chain(recheck_kernel, dim3(blocks), dim3(128), 0, s, (const __nv_bfloat16 *)xn, (const __nv_bfloat16 *)router, bias, logits,
-                             flag_rows, n_flag, T, eps, ids, weights);
+                             flag_rows, n_flag, T, eps, ids, weights, segcount);
 }
 
 cudaError_t omni_launch_router_exact(const void *xn, const void *router, const float *bias, int T, double *logits,
@@ -570,11 +437,12 @@ cudaError_t omni_launch_route_pairs(const float *hi, const float *lo, int rows, 
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st, cudaStream_t s) {
+cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st, int have_counts, cudaStream_t s) {
     const int A = rows * OMNI_TOP;
     const int nseg = (A + OMNI_SEG - 1) / OMNI_SEG;
     const int blocks = (nseg + 7) / 8;
-    cudaError_t e = omni_launch_chain(assign_hist_kernel, dim3(blocks), dim3(256), 0, s, ids, A, nseg, st.segcount, st.status);
+    cudaError_t e = cudaSuccess;
+    if (!have_counts) e = omni_launch_chain(assign_hist_kernel, dim3(blocks), dim3(256), 0, s, ids, A, nseg, st.segcount, st.status);
     if (e == cudaSuccess) e = omni_launch_chain(assign_scan_kernel, dim3(1), dim3(1024), 0, s, nseg, st);
     if (e == cudaSuccess) e = omni_launch_chain(assign_scatter_kernel, dim3(blocks), dim3(256), 0, s, ids, A, nseg, st);
     return e;
@@ -669,7 +537,7 @@ cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, i
     st.counts = counts; st.offsets = offsets; st.rowmap = rowmap; st.slots = slots;
     st.segcount = sc->segcount; st.ttiles = sc->ttiles; st.n_ttiles = &sc->n_ttiles; st.sched = sc->sched;
     st.status = status;
-    return omni_launch_assign(ids, rows, st, s);
+    return omni_launch_assign(ids, rows, st, 0, s);
 }
 
 }  // extern "C"

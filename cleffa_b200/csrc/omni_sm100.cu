@@ -646,7 +646,8 @@ __global__ void __launch_bounds__(RT_THREADS, 1)
 router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                     const float *__restrict__ bias, int T, float eps, int exact_all, float *__restrict__ logits,
                     int32_t *__restrict__ ids, float *__restrict__ weights, int32_t *__restrict__ flag_rows,
-                    int32_t *__restrict__ n_flag, uint32_t *__restrict__ status, unsigned long long *__restrict__ dbg) {
+                    int32_t *__restrict__ n_flag, uint32_t *__restrict__ status, unsigned long long *__restrict__ dbg,
+                    int32_t *__restrict__ segcount) {
     constexpr int KSTAGES = OMNI_H / BK;
     // optional per-CTA timestamps (ns): 0 start, 1 loads issued, 2 MMAs issued, 3 accumulator
     // ready, 4 logits stored, 5 selection stored
@@ -661,6 +662,9 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
     volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);
+    // expert counts per warp [4][128], in pipeline stages that are idle by then (behind the
+    // 64 KiB of full-precision logits)
+    int *hist = reinterpret_cast<int *>(smem_raw + (smem_base - smem_u32(smem_raw)) + OMNI_E * 128 * 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * 128;
@@ -786,6 +790,25 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 if (threadIdx.x == 128) stamp(5);
             }
         }
+        if (segcount) {
+            // Each warp's 32 tokens are one 256-assignment segment of the counting sort: count
+            // their experts here (the exact pass corrects the counts of the rows it changes).
+            int *h = hist + q * OMNI_E;
+#pragma unroll
+            for (int j = 0; j < 4; j++) h[lane + 32 * j] = 0;
+            __syncwarp();
+            if (row < T) {
+                const int4 a = *reinterpret_cast<const int4 *>(ids + row * 8), b = *reinterpret_cast<const int4 *>(ids + row * 8 + 4);
+                atomicAdd(h + a.x, 1); atomicAdd(h + a.y, 1); atomicAdd(h + a.z, 1); atomicAdd(h + a.w, 1);
+                atomicAdd(h + b.x, 1); atomicAdd(h + b.y, 1); atomicAdd(h + b.z, 1); atomicAdd(h + b.w, 1);
+            }
+            __syncwarp();
+            const int seg = blockIdx.x * 4 + q;
+            if (seg * OMNI_SEG < T * OMNI_TOP) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) segcount[(long)seg * OMNI_E + lane + 32 * j] = h[lane + 32 * j];
+            }
+        }
     }
 
     tc_fence_before();
@@ -824,9 +847,9 @@ cudaError_t omni_sm100_configure(void) {
 cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
                                      int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
-                                     cudaStream_t s) {
+                                     int32_t *segcount, cudaStream_t s) {
     return omni_launch_chain(router_sm100_kernel, dim3((T + 127) / 128), dim3(RT_THREADS), RT_SMEM_BYTES, s, *tm_x, *tm_w, bias, T,
-                             eps, exact_all, logits, ids, weights, flag_rows, n_flag, status, dbg);
+                             eps, exact_all, logits, ids, weights, flag_rows, n_flag, status, dbg, segcount);
 }
 
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,

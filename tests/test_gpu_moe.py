@@ -78,19 +78,23 @@ def test_tcgen05_and_check_kernels_agree(bound0):
 
 @pytest.mark.parametrize("T", [1, 37, 300, 2500])
 def test_launch_variants_give_the_same_bits(bound0, T):
-    """The gate/up kernel fetching its rows through the permutation, the separate gather
-    kernel, and dependent launch on or off are ways of scheduling the same arithmetic."""
+    """Fused or separate kernels (exact pass and histogram inside the router kernel, token
+    rows gathered by the gate/up kernel) and dependent launch on or off are ways of
+    scheduling the same arithmetic."""
     b = bound0
     x = orc.make_activations(17, T)
     base = run_block(b, 0, x)
+    opts = ("fused_router", "fused_gather", "dependent_launch")
     try:
-        for fused, dep in ((0, 1), (1, 0), (0, 0)):
-            b.set_option("fused_gather", fused); b.set_option("dependent_launch", dep)
+        for combo in ((0, 1, 1), (1, 0, 1), (1, 1, 0), (0, 0, 0)):
+            for name, v in zip(opts, combo):
+                b.set_option(name, v)
             other = run_block(b, 0, x)
-            assert np.array_equal(base["ids"], other["ids"]) and np.array_equal(base["slots"], other["slots"])
-            assert np.array_equal(base["out"], other["out"]), (fused, dep)
+            for key in ("ids", "slots", "counts", "rechecked", "out"):
+                assert np.array_equal(base[key], other[key]), (key, combo)
     finally:
-        b.set_option("fused_gather", 1); b.set_option("dependent_launch", 1)
+        for name in opts:
+            b.set_option(name, 1)
 
 
 def test_golden_ids_of_config1(bound0):
