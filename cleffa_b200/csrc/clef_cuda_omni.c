@@ -531,9 +531,9 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     stage_mark(g, 2);
     if (g->gemm_impl == 0) {
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
-                                                                     fused ? s->sort.rowmap : NULL, g->n_sm - g->reserve_sms, g->stream))) return false;
+                                                                     fused ? s->sort.rowmap : NULL, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, g->n_sm - g->reserve_sms, g->stream))) return false;
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
     } else {
         if (!launched(g, "gate/up experts (check kernel)", omni_launch_gateup_simple(s->xg, L->gate_up, s->sort.offsets, rows8, s->h, g->stream))) return false;
         stage_mark(g, 3);
@@ -577,9 +577,9 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
         if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
         if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
         stage_mark(g, 2);
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, n_gemm, g->stream))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, n_gemm == g->n_sm, n_gemm, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, n_gemm, g->stream))) return false;
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, n_gemm == g->n_sm, n_gemm, g->stream))) return false;
         stage_mark(g, 4);
         if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, row_bounds, 0, OMNI_EP_RET_GROUPS, g->n_sm, g->stream))) return false;
     } else {
@@ -590,10 +590,10 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
         if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->ep.side))) return false;
         stage_mark(g, 2);
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
-                                                                     g->ep.need, omni_ep_group_size(pe->world), NULL, NULL, n_gemm, g->stream))) return false;
+                                                                     g->ep.need, omni_ep_group_size(pe->world), NULL, NULL, 0, n_gemm, g->stream))) return false;
         stage_mark(g, 3);
         for (int rg = 0; rg < OMNI_EP_RET_GROUPS; rg++) {
-            if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg, n_gemm, g->stream))) return false;
+            if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg, 0, n_gemm, g->stream))) return false;
             if (!launched(g, "return fork", cudaEventRecord(g->ep.ev_down[rg], g->stream))) return false;
             if (!launched(g, "return fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_down[rg], 0))) return false;
             if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, row_bounds, rg, rg + 1, g->n_sm, g->ep.side))) return false;

@@ -108,10 +108,14 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
  * row gather_rows[i] of gather_src ([rows][2048] BF16) itself and tm_x4 is not used */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, const uint32_t *ready, const int32_t *need, int group_size,
-                                     const void *gather_src, const int32_t *gather_rows, int n_sm, cudaStream_t s);
-/* tile_bounds (may be NULL) + group: restrict the launch to tiles [tile_bounds[group], tile_bounds[group+1]) */
+                                     const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
+                                     cudaStream_t s);
+/* tile_bounds (may be NULL) + group: restrict the launch to tiles [tile_bounds[group], tile_bounds[group+1]).
+ * early_dependents (both launchers): let blocks of the next kernel in the stream become resident
+ * while this one runs; pass 0 when the grid leaves SMs free for kernels of another stream */
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                   void *d, const int32_t *tile_bounds, int group, int n_sm, cudaStream_t s);
+                                   void *d, const int32_t *tile_bounds, int group, int early_dependents, int n_sm,
+                                   cudaStream_t s);
 
 /* Programmatic dependent launch of the pass's kernel chain (process-wide, default on) */
 void omni_set_dependent_launch(int on);

@@ -227,7 +227,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    int32_t *__restrict__ work_counter, __nv_bfloat16 *__restrict__ out, uint32_t *__restrict__ status,
                    const uint32_t *__restrict__ ready, const int32_t *__restrict__ need, int group_size,
                    const int32_t *__restrict__ tile_bounds, int tile_group,
-                   const __nv_bfloat16 *__restrict__ gather_src, const int32_t *__restrict__ gather_rows) {
+                   const __nv_bfloat16 *__restrict__ gather_src, const int32_t *__restrict__ gather_rows,
+                   int early_dependents) {
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
     constexpr int WS = C::W_STAGES, TS = C::T_STAGES;
@@ -272,7 +273,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 512); tmem_relinquish(); }
     dep_wait();                 // everything above overlaps the tail of the previous kernel
-    dep_launch();
+    // Blocks of the next kernel that become resident early sit on whatever SM is free.  When
+    // this grid leaves SMs free on purpose (for copy kernels of another stream), it must not
+    // invite them.
+    if (early_dependents) dep_launch();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -854,22 +858,25 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap 
 
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, const uint32_t *ready, const int32_t *need, int group_size,
-                                     const void *gather_src, const int32_t *gather_rows, int n_sm, cudaStream_t s) {
+                                     const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
+                                     cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
     return omni_launch_chain(expert_gemm_kernel<MODE_GATEUP>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s,
                              *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status, ready, need,
-                             group_size > 0 ? group_size : 1, nullptr, 0, (const __nv_bfloat16 *)gather_src, gather_rows);
+                             group_size > 0 ? group_size : 1, nullptr, 0, (const __nv_bfloat16 *)gather_src, gather_rows,
+                             early_dependents);
 }
 
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                   void *d, const int32_t *tile_bounds, int group, int n_sm, cudaStream_t s) {
+                                   void *d, const int32_t *tile_bounds, int group, int early_dependents, int n_sm,
+                                   cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
     return omni_launch_chain(expert_gemm_kernel<MODE_DOWN>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_DOWN>::TOTAL_BYTES, s,
                              *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d,
                              st.status, nullptr, nullptr, 1, tile_bounds, group, (const __nv_bfloat16 *)nullptr,
-                             (const int32_t *)nullptr);
+                             (const int32_t *)nullptr, early_dependents);
 }
 
 }  // extern "C"
