@@ -18,7 +18,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-enum { MAX_LAYERS = 128, N_STAGE_EVENTS = 6, PROF_SLOTS = 64 };
+enum { MAX_LAYERS = 128, N_STAGE_EVENTS = 6, PROF_SLOTS = 64, HOST_PIECES = 16 };
 
 /* Route capture row, byte-compatible with omni_route_row (clef_metal_omni.m:15): 1088 bytes. */
 typedef struct { float logits[OMNI_E], low[OMNI_E]; int32_t ids[OMNI_TOP]; float weights[OMNI_TOP]; } omni_route_row;
@@ -71,8 +71,10 @@ struct clef_gpu {
     long prof_passes;
     void *stage_x, *stage_res;          /* forward_host staging */
     size_t stage_cap;
-    cudaStream_t copy_stream;           /* forward_host: the residual upload runs beside the expert kernels */
-    cudaEvent_t residual_uploaded;
+    /* forward_host: uploads, kernels and downloads of successive pieces of the batch overlap */
+    cudaStream_t copy_stream, out_stream;
+    cudaEvent_t ev_xn[HOST_PIECES], ev_res[HOST_PIECES], ev_done[HOST_PIECES];
+    cudaEvent_t residual_uploaded;      /* the ev_res[] entry of the piece being encoded */
     bool wait_residual;                 /* the combine of the current pass must wait for that upload */
     /* expert parallelism (omni_ep.cu); world <= 1 means off */
     struct {
@@ -223,7 +225,12 @@ void clef_cuda_omni_close(clef_gpu *g) {
     if (g->stage_x) cudaFree(g->stage_x);
     if (g->stage_res) cudaFree(g->stage_res);
     if (g->copy_stream) { cudaStreamSynchronize(g->copy_stream); cudaStreamDestroy(g->copy_stream); }
-    if (g->residual_uploaded) cudaEventDestroy(g->residual_uploaded);
+    if (g->out_stream) { cudaStreamSynchronize(g->out_stream); cudaStreamDestroy(g->out_stream); }
+    for (int i = 0; i < HOST_PIECES; i++) {
+        if (g->ev_xn[i]) cudaEventDestroy(g->ev_xn[i]);
+        if (g->ev_res[i]) cudaEventDestroy(g->ev_res[i]);
+        if (g->ev_done[i]) cudaEventDestroy(g->ev_done[i]);
+    }
     for (int p = 0; p < PROF_SLOTS; p++) for (int i = 0; i < N_STAGE_EVENTS; i++) if (g->ev[p][i]) cudaEventDestroy(g->ev[p][i]);
     if (g->own_stream) cudaStreamDestroy(g->stream);
     free(g);
@@ -671,32 +678,80 @@ bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *
         if (g->stage_res) cudaFree(g->stage_res);
         g->stage_x = nx; g->stage_res = nr; g->stage_cap = (size_t)T;
     }
-    clef_omni_begin(g);
-    /* The router and the expert products only need xn; the FP32 residual (twice the bytes) is
-     * first touched by the combine, so it is uploaded on a second stream beside them. */
     if (!g->copy_stream) {
-        if (cudaStreamCreateWithFlags(&g->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaEventCreateWithFlags(&g->residual_uploaded, cudaEventDisableTiming) != cudaSuccess) {
+        bool ok = cudaStreamCreateWithFlags(&g->copy_stream, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&g->out_stream, cudaStreamNonBlocking) == cudaSuccess;
+        for (int i = 0; i < HOST_PIECES && ok; i++)
+            ok = cudaEventCreateWithFlags(&g->ev_xn[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&g->ev_res[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&g->ev_done[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
             cudaGetLastError();
-            set_err(err, errlen, "cuda: cannot create the Omni upload stream");
+            set_err(err, errlen, "cuda: cannot create the Omni transfer streams");
             return false;
         }
     }
-    cudaError_t e = cudaMemcpyAsync(g->stage_x, xn_host, (size_t)T * OMNI_H * 2, cudaMemcpyHostToDevice, g->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(g->stage_res, x_host, (size_t)T * OMNI_H * 4, cudaMemcpyHostToDevice, g->copy_stream);
-    if (e == cudaSuccess) e = cudaEventRecord(g->residual_uploaded, g->copy_stream);
-    if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot upload Omni activations: %s", cudaGetErrorString(e)); return false; }
-    g->wait_residual = true;
-    const bool encoded = clef_omni_encode_moe(g, layer, g->stage_x, g->stage_res, T, n_seq, seq_bounds, err, errlen);
-    g->wait_residual = false;
-    if (!encoded) {
-        cudaStreamSynchronize(g->stream);
-        cudaStreamSynchronize(g->copy_stream);
+    if (seq_bounds) {
+        bool ok = n_seq >= 1 && seq_bounds[0] == 0 && seq_bounds[n_seq] == T;
+        for (int i = 0; i < n_seq && ok; i++) ok = seq_bounds[i] < seq_bounds[i + 1];
+        if (!ok) { set_err(err, errlen, "cuda: invalid Omni sequence bounds"); return false; }
+    } else if (n_seq != 1) {
+        set_err(err, errlen, "cuda: invalid Omni sequence bounds");
         return false;
     }
-    e = cudaMemcpyAsync(x_host, g->stage_res, (size_t)T * OMNI_H * 4, cudaMemcpyDeviceToHost, g->stream);
-    if (e != cudaSuccess) { set_err(err, errlen, "cuda: cannot download Omni residual: %s", cudaGetErrorString(e)); return false; }
-    return clef_omni_complete(g, err, errlen);
+    /* The link to the host is the slow part (12 KB up and 8 KB down per token), so the batch is
+     * cut into pieces of about a thousand tokens: while one piece is in the kernels the next is
+     * being uploaded and the previous one downloaded.  Tokens are independent, so the pieces
+     * give the same bits as one pass.  Inside a piece the router and the expert products only
+     * need xn; the FP32 residual is first touched by the combine and travels beside them.
+     * With expert parallelism every rank must issue the same passes: one piece. */
+    int n_piece = g->ep.world > 1 || T <= 1536 ? 1 : (T + 1023) / 1024;
+    if (n_piece > HOST_PIECES) n_piece = HOST_PIECES;
+    int per = ((T + n_piece - 1) / n_piece + 127) & ~127;
+    if (g->ep.world > 1) per = T;
+    clef_omni_begin(g);
+    cudaError_t e = cudaSuccess;
+    int n_used = 0;
+    for (int start = 0; start < T && e == cudaSuccess; start += per, n_used++) {
+        const size_t rows = (size_t)(T - start < per ? T - start : per), off = (size_t)start * OMNI_H;
+        e = cudaMemcpyAsync((char *)g->stage_x + off * 2, (const char *)xn_host + off * 2, rows * OMNI_H * 2, cudaMemcpyHostToDevice, g->copy_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(g->ev_xn[n_used], g->copy_stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync((float *)g->stage_res + off, x_host + off, rows * OMNI_H * 4, cudaMemcpyHostToDevice, g->copy_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(g->ev_res[n_used], g->copy_stream);
+    }
+    if (e != cudaSuccess) {
+        cudaStreamSynchronize(g->copy_stream);
+        set_err(err, errlen, "cuda: cannot upload Omni activations: %s", cudaGetErrorString(e));
+        return false;
+    }
+    bool encoded = true;
+    for (int p = 0; p < n_used && encoded; p++) {
+        const int start = p * per, rows = T - start < per ? T - start : per;
+        const size_t off = (size_t)start * OMNI_H;
+        e = cudaStreamWaitEvent(g->stream, g->ev_xn[p], 0);
+        g->residual_uploaded = g->ev_res[p];
+        g->wait_residual = true;
+        encoded = e == cudaSuccess && clef_omni_encode_moe(g, layer, (char *)g->stage_x + off * 2, (float *)g->stage_res + off, rows, 1, NULL, err, errlen);
+        g->wait_residual = false;
+        if (!encoded) break;
+        e = cudaEventRecord(g->ev_done[p], g->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(g->out_stream, g->ev_done[p], 0);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(x_host + off, (float *)g->stage_res + off, (size_t)rows * OMNI_H * 4, cudaMemcpyDeviceToHost, g->out_stream);
+        if (e != cudaSuccess) { encoded = false; set_err(err, errlen, "cuda: cannot download Omni residual: %s", cudaGetErrorString(e)); }
+    }
+    if (!encoded) {
+        if (e != cudaSuccess && err && !err[0]) set_err(err, errlen, "cuda: Omni host pass failed: %s", cudaGetErrorString(e));
+        cudaStreamSynchronize(g->copy_stream);
+        cudaStreamSynchronize(g->stream);
+        cudaStreamSynchronize(g->out_stream);
+        return false;
+    }
+    const bool done = clef_omni_complete(g, err, errlen);
+    if (cudaStreamSynchronize(g->out_stream) != cudaSuccess && done) {
+        set_err(err, errlen, "cuda: cannot download Omni residual");
+        return false;
+    }
+    return done;
 }
 
 bool clef_omni_stage_router(clef_gpu *g, int layer, const void *xn, int T, double *logits, char *err, size_t errlen) {

@@ -27,7 +27,6 @@
 
 namespace {
 
-constexpr unsigned FULL = 0xffffffffu;
 constexpr uint64_t SPIN_LIMIT_NS = 2000000000ull;      // 2 s: every legitimate wait is far shorter
 
 __device__ __forceinline__ uint64_t now_ns() {

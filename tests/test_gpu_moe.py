@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 import torch
 
+from cleffa_b200 import OmniError
 from oracle import omni_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -187,13 +188,19 @@ def test_config2_T4096_varlen_sampled(bound0, weights0):
     assert (np.diff(got["ids"].astype(np.int64), axis=-1) != 0).all()
 
 
-def test_forward_host_equals_device_path(bound0):
-    x = orc.make_activations(21, 300)
-    res = torch.randn(300, 2048, generator=torch.Generator().manual_seed(1))
+@pytest.mark.parametrize("T", [300, 1537, 3000])
+def test_forward_host_equals_device_path(bound0, T):
+    # above 1536 tokens the host call cuts the batch into pieces whose copies and kernels overlap
+    x = orc.make_activations(21, T)
+    res = torch.randn(T, 2048, generator=torch.Generator().manual_seed(1))
     dev = run_block(bound0, 0, x, residual=res)["out"]
-    host = res.clone()
-    bound0.forward_host(0, x, host)
-    assert torch.equal(host, dev)
+    for pinned in (False, True):
+        host = res.clone().pin_memory() if pinned else res.clone()
+        xin = x.pin_memory() if pinned else x
+        bound0.forward_host(0, xin, host, np.array([0, T // 3, T], dtype=np.int32))
+        assert torch.equal(host, dev)
+    with pytest.raises(OmniError, match="sequence bounds"):
+        bound0.forward_host(0, x, res.clone(), np.array([0, T + 1], dtype=np.int32))
 
 
 def test_three_layer_stack_teacher_forced(backend):
