@@ -795,7 +795,8 @@ bool clef_omni_stage_assign(clef_gpu *g, const int32_t *ids, int rows, int32_t *
 bool clef_omni_stage_experts(clef_gpu *g, int layer, const void *xn, const int32_t *ids, const float *weights,
                              float *x, int T, char *err, size_t errlen) {
     if (!check_pass(g, layer, true, err, errlen)) return false;
-    if (!xn || !ids || !weights || !x || T <= 0 || T > OMNI_CHUNK) {
+    if (!xn || !ids || !weights || !x || T <= 0 || T > OMNI_CHUNK ||
+        (((uintptr_t)xn | (uintptr_t)ids | (uintptr_t)weights | (uintptr_t)x) & 15)) {      /* vector loads: 16-byte alignment */
         set_err(err, errlen, "cuda: invalid Omni expert dispatch");
         return false;
     }

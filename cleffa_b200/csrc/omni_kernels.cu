@@ -272,9 +272,18 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4 *__restrict__ 
     dep_wait();
     dep_launch();
     const long t = blockIdx.x;
+    // the residual does not depend on the routing: its loads travel with the routing's
+    float4 *xp = reinterpret_cast<float4 *>(x + t * OMNI_H) + threadIdx.x * 2;
+    float4 a = xp[0], b = xp[1];
     int id[8], sl[8]; float w[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) { id[k] = ids[t * 8 + k]; sl[k] = slots[t * 8 + k]; w[k] = weights[t * 8 + k]; }
+    {
+        const int4 i0 = __ldg(reinterpret_cast<const int4 *>(ids + t * 8)), i1 = __ldg(reinterpret_cast<const int4 *>(ids + t * 8) + 1);
+        const int4 s0 = __ldg(reinterpret_cast<const int4 *>(slots + t * 8)), s1 = __ldg(reinterpret_cast<const int4 *>(slots + t * 8) + 1);
+        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(weights + t * 8)), w1 = __ldg(reinterpret_cast<const float4 *>(weights + t * 8) + 1);
+        id[0] = i0.x; id[1] = i0.y; id[2] = i0.z; id[3] = i0.w; id[4] = i1.x; id[5] = i1.y; id[6] = i1.z; id[7] = i1.w;
+        sl[0] = s0.x; sl[1] = s0.y; sl[2] = s0.z; sl[3] = s0.w; sl[4] = s1.x; sl[5] = s1.y; sl[6] = s1.z; sl[7] = s1.w;
+        w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+    }
     // stable insertion sort by expert id (ids of one token are distinct on a valid route)
 #pragma unroll
     for (int i = 1; i < 8; i++) {
@@ -291,8 +300,12 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4 *__restrict__ 
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
 #pragma unroll
+    uint4 q8[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) q8[k] = __ldcs(d + (long)sl[k] * (OMNI_H / 8) + threadIdx.x);   // each row is read once
+#pragma unroll
     for (int k = 0; k < 8; k++) {
-        const uint4 q = __ldg(d + (long)sl[k] * (OMNI_H / 8) + threadIdx.x);
+        const uint4 q = q8[k];
         const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int j = 0; j < 4; j++) {
@@ -300,8 +313,6 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4 *__restrict__ 
             acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(bf16_bits_to_float(u[j] >> 16), w[k]));
         }
     }
-    float4 *xp = reinterpret_cast<float4 *>(x + t * OMNI_H) + threadIdx.x * 2;
-    float4 a = xp[0], b = xp[1];
     a.x += acc[0]; a.y += acc[1]; a.z += acc[2]; a.w += acc[3];
     b.x += acc[4]; b.y += acc[5]; b.z += acc[6]; b.w += acc[7];
     xp[0] = a; xp[1] = b;
