@@ -102,7 +102,9 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
 
 /* One synchronous pass with HOST buffers: begin, copy xn (BF16) and x (FP32) to the device,
  * encode_moe, copy x back, complete.  This is the call a host engine makes when its
- * activations live in host memory. */
+ * activations live in host memory.  Above 1536 tokens (one GPU) the batch is processed in
+ * pieces of about a thousand tokens whose uploads, kernels and downloads overlap; the bits are
+ * those of one pass.  Page-locked host buffers are needed for the copies to overlap. */
 bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
                             const int32_t *seq_bounds, char *err, size_t errlen);
 
@@ -197,6 +199,8 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
  * context on the same GPU -- another micro-batch -- are not locked out while they run),
  * "fused_gather" 0/1 (default 1: the gate/up kernel fetches its token rows through the permutation
  * itself instead of reading a copy in expert order made by a separate kernel; same results),
+ * "fused_router" 0/1 (default 1: the router kernel counts the experts per segment of the counting sort,
+ * so no histogram kernel runs; same results),
  * "dependent_launch" 0/1 (default 1, process-wide: the kernels of a pass are launched so that each one's
  * prologue overlaps the tail of the one before),
  * "alloc_fail_at" N / "launch_fail_at" N (host-side fault injection, 0 = off). */

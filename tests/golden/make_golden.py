@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ from the reference's own Python code.
 
-Run once, in a container that has the reference checkout (default /root/reference):
+Run once, where a checkout of the reference project (zknpr/cleffa) is available:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <path to the checkout>
 
 What is stored (small .npz files, committed):
 
@@ -63,7 +63,7 @@ def hf_block(router, gate_up, down):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     ref = load_reference_fp64(Path(args.reference))
     out_dir = Path(__file__).resolve().parent
