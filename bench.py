@@ -244,6 +244,9 @@ def ours(args):
                        for shape in ((E, H), (E, 2 * F, H), (E, H, F)))
             b.bind_layer(l, *wl)
             stack.append(wl)
+        if args.norm:
+            for l in range(n_layers):
+                b.bind_norm(l, torch.ones(H), 1e-6)
     xn = x_host.cuda()
     x = torch.zeros(T_TOKENS, H, device="cuda")
     x0 = xn.float() if n_layers > 1 else None
@@ -255,8 +258,11 @@ def ours(args):
             b.begin()
             x.copy_(x0)                         # every step starts from the same N(0,1) residual stream
             for l in range(n_layers):
-                xn.copy_(x)                     # FP32 residual -> BF16 layer input (the norm's place)
-                b.encode_moe(l, xn, x, bounds)
+                if args.norm:
+                    b.encode_norm_moe(l, x, bounds)     # RMSNorm of the residual stream inside the library
+                else:
+                    xn.copy_(x)                 # FP32 residual -> BF16 layer input (the norm's place)
+                    b.encode_moe(l, xn, x, bounds)
             return
         if micro == 1:
             b.begin()
@@ -410,6 +416,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU (default: the headline 4096)")
     ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
     ap.add_argument("--reserve", type=int, default=0, help="SMs the expert kernels leave to the copy kernels with expert parallelism (0: the library default, 32)")
+    ap.add_argument("--norm", action="store_true", help="with --layers: each layer normalises the residual stream itself (RMSNorm, unit weights) instead of taking a BF16 copy")
     ap.add_argument("--kernels-only", action="store_true", help="run the warm-up and the timed steps and stop (for profiler captures; one GPU)")
     ap.add_argument("--option", action="append", default=[], help="library option name=value (clef_omni_set_option), repeatable")
     ap.add_argument("--overlap", action="store_true", help="expert parallelism: run the transfers under the expert kernels")

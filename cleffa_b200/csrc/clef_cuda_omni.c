@@ -50,6 +50,10 @@ struct clef_gpu {
     omni_arena *omni;
     omni_layer layer[MAX_LAYERS];
     int n_layer;
+    /* RMSNorm in front of the block (clef_omni_bind_norm / clef_omni_encode_norm_moe) */
+    float *norm_w[MAX_LAYERS];          /* device, FP32 [2048]; NULL = not bound */
+    float norm_eps[MAX_LAYERS];
+    void *xnorm;                        /* BF16 [CHUNK][2048]: the normalised rows of the chunk in flight */
     /* route capture */
     omni_route_row *trace;              /* device */
     int trace_first, trace_rows, trace_layers;
@@ -221,6 +225,8 @@ void clef_cuda_omni_close(clef_gpu *g) {
     clef_omni_ep_disconnect(g);
     clef_omni_free(g);
     for (int l = 0; l < MAX_LAYERS; l++) free_layer(&g->layer[l]);
+    for (int l = 0; l < MAX_LAYERS; l++) if (g->norm_w[l]) cudaFree(g->norm_w[l]);
+    if (g->xnorm) cudaFree(g->xnorm);
     if (g->trace) cudaFree(g->trace);
     if (g->stage_x) cudaFree(g->stage_x);
     if (g->stage_res) cudaFree(g->stage_res);
@@ -618,10 +624,11 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
 
 static void book_profile(clef_gpu *g) { if (g->profile) g->prof_passes++; }
 
-bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int T, int n_seq,
+/* xn == NULL: the rows are normalised here, chunk by chunk, from the residual x */
+static bool encode_chunks(clef_gpu *g, int layer, const void *xn, float *x, int T, int n_seq,
                           const int32_t *seq_bounds, char *err, size_t errlen) {
     if (!check_pass(g, layer, true, err, errlen)) return false;
-    if (!xn || !x || T <= 0 || n_seq < 1 || ((uintptr_t)xn & 15) || ((uintptr_t)x & 15)) {
+    if (!x || T <= 0 || n_seq < 1 || ((uintptr_t)xn & 15) || ((uintptr_t)x & 15)) {
         set_err(err, errlen, "cuda: invalid Omni layer dispatch");
         return false;
     }
@@ -644,10 +651,12 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
      * regardless of record boundaries; a token's arithmetic never depends on its chunk. */
     for (int start = 0; start < T; start += OMNI_CHUNK) {
         const int rows = T - start < OMNI_CHUNK ? T - start : OMNI_CHUNK;
-        const char *xn_c = (const char *)xn + (size_t)start * OMNI_H * 2;
+        const char *xn_c = xn ? (const char *)xn + (size_t)start * OMNI_H * 2 : (const char *)g->xnorm;
         stage_mark(g, 0);
         bool have_counts = false;
-        bool ok = run_router(g, L, xn_c, rows, &have_counts);
+        bool ok = xn || launched(g, "rmsnorm", omni_launch_rmsnorm(x + (size_t)start * OMNI_H, g->norm_w[layer], g->norm_eps[layer],
+                                                                   rows, g->xnorm, g->stream));
+        if (ok) ok = run_router(g, L, xn_c, rows, &have_counts);
         if (ok && g->trace && layer < g->trace_layers && start + rows > g->trace_first)
             ok = launched(g, "route capture", omni_launch_trace(s->logits, s->ids, s->weights, rows, start, g->trace_first,
                                                                 g->trace_rows, layer, g->trace, g->stream));
@@ -659,6 +668,49 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
         g->last_T = rows;
     }
     return true;
+}
+
+bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int T, int n_seq,
+                          const int32_t *seq_bounds, char *err, size_t errlen) {
+    if (!xn) { set_err(err, errlen, "cuda: invalid Omni layer dispatch"); return false; }
+    return encode_chunks(g, layer, xn, x, T, n_seq, seq_bounds, err, errlen);
+}
+
+bool clef_omni_bind_norm(clef_gpu *g, int layer, const float *weight, float eps, int where, char *err, size_t errlen) {
+    if (!g || layer < 0 || layer >= MAX_LAYERS || !weight || !(eps > 0.f) || !isfinite(eps) ||
+        (where != CLEF_OMNI_HOST && where != CLEF_OMNI_DEVICE)) {
+        set_err(err, errlen, "cuda: invalid Omni norm binding");
+        return false;
+    }
+    cudaSetDevice(g->device);
+    float *w = g->norm_w[layer] ? g->norm_w[layer] : dev_alloc(g, OMNI_H * 4);
+    void *xnorm = g->xnorm ? g->xnorm : dev_alloc(g, (size_t)OMNI_CHUNK * OMNI_H * 2);
+    bool ok = w && xnorm;
+    if (ok) {
+        cudaStreamSynchronize(g->stream);      /* a pass in flight may still read the old weights */
+        ok = cudaMemcpyAsync(w, weight, OMNI_H * 4, where == CLEF_OMNI_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
+                             g->stream) == cudaSuccess && cudaStreamSynchronize(g->stream) == cudaSuccess;
+    }
+    if (!ok) {
+        cudaGetLastError();
+        if (w && !g->norm_w[layer]) cudaFree(w);
+        if (xnorm && !g->xnorm) cudaFree(xnorm);
+        set_err(err, errlen, "cuda: cannot upload the Omni norm weights of layer %d (previous binding kept)", layer);
+        return false;
+    }
+    g->norm_w[layer] = w;
+    g->norm_eps[layer] = eps;
+    g->xnorm = xnorm;
+    return true;
+}
+
+bool clef_omni_encode_norm_moe(clef_gpu *g, int layer, float *x, int T, int n_seq, const int32_t *seq_bounds,
+                               char *err, size_t errlen) {
+    if (!g || layer < 0 || layer >= MAX_LAYERS || !g->norm_w[layer]) {
+        set_err(err, errlen, "cuda: invalid Omni layer dispatch (no norm weights bound)");
+        return false;
+    }
+    return encode_chunks(g, layer, NULL, x, T, n_seq, seq_bounds, err, errlen);
 }
 
 bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
@@ -824,6 +876,7 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
     else if (!strcmp(what, "status")) { src = s->status; have = 4; }
     else if (!strcmp(what, "rechecked")) { src = s->n_flag; have = 4; }
     else if (!strcmp(what, "n_ttiles")) { src = s->sort.n_ttiles; have = 4; }
+    else if (!strcmp(what, "xnorm") && g->xnorm) { src = g->xnorm; have = T * OMNI_H * 2; }
     else if (!strcmp(what, "router_stamps")) { src = s->stamps; have = (size_t)(OMNI_CHUNK / 128) * 64; }
     if (!src || !dst || bytes > have || !bytes) { set_err(err, errlen, "cuda: unknown or oversized Omni read: %s", what); return false; }
     cudaError_t e = cudaStreamSynchronize(g->stream);

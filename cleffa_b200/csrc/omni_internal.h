@@ -76,6 +76,8 @@ cudaError_t omni_launch_route_pairs(const float *hi, const float *lo, int rows, 
                                     uint32_t *status, cudaStream_t s);
 /* have_counts: st.segcount already holds the per-segment expert counts of ids (the router kernel wrote them) */
 cudaError_t omni_launch_assign(const int32_t *ids, int rows, omni_sort_state st, int have_counts, cudaStream_t s);
+/* xn[rows][2048] BF16 = RMSNorm of x[rows][2048] FP32 with FP32 weights w[2048] */
+cudaError_t omni_launch_rmsnorm(const float *x, const float *w, float eps, int rows, void *xn, cudaStream_t s);
 cudaError_t omni_launch_gather(const void *xn, const int32_t *rowmap, int rows8, void *xg, cudaStream_t s);
 cudaError_t omni_launch_combine(const void *d, const int32_t *ids, const float *weights, const int32_t *slots,
                                 float *x, int T, cudaStream_t s);

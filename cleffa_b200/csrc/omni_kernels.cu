@@ -263,6 +263,38 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint4 *__restrict__ x
     }
 }
 
+// ------------------------------------------------------------------ RMSNorm in front of the block
+// xn[t] = bf16( x[t] * rsqrt(mean(x[t]^2) + eps) * w )  (metal/clef.metal:190-204, `rmsnorm_f32`;
+// the product order (x * inv) * w is the reference's).  One block per token, eight elements per
+// thread: 8 KiB read, 4 KiB written per row.
+__global__ void __launch_bounds__(256) rmsnorm_bf16_kernel(const float4 *__restrict__ x, const float4 *__restrict__ w,
+                                                           float eps, uint4 *__restrict__ xn) {
+    __shared__ float part[8];
+    dep_wait();
+    dep_launch();
+    const long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float4 a = x[t * (OMNI_H / 4) + threadIdx.x * 2], b = x[t * (OMNI_H / 4) + threadIdx.x * 2 + 1];
+    const float4 wa = __ldg(w + threadIdx.x * 2), wb = __ldg(w + threadIdx.x * 2 + 1);
+    float ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(FULL, ss, s);
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += part[i];                 // same order in every thread
+    const float inv = 1.0f / sqrtf(tot / (float)OMNI_H + eps);
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(a.x, inv), wa.x), __fmul_rn(__fmul_rn(a.y, inv), wa.y));
+    const __nv_bfloat162 p1 = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(a.z, inv), wa.z), __fmul_rn(__fmul_rn(a.w, inv), wa.w));
+    const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(b.x, inv), wb.x), __fmul_rn(__fmul_rn(b.y, inv), wb.y));
+    const __nv_bfloat162 p3 = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(b.z, inv), wb.z), __fmul_rn(__fmul_rn(b.w, inv), wb.w));
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&p0); o.y = *reinterpret_cast<const uint32_t *>(&p1);
+    o.z = *reinterpret_cast<const uint32_t *>(&p2); o.w = *reinterpret_cast<const uint32_t *>(&p3);
+    xn[t * (OMNI_H / 8) + threadIdx.x] = o;
+}
+
 // ------------------------------------------------------------------ combine
 // x[t] += sum over the token's experts in ascending expert id of w * d[slot]
 // (clef.metal:2504-2521: fixed order, separate multiply and add, residual added once).
@@ -299,7 +331,6 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4 *__restrict__ 
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
-#pragma unroll
     uint4 q8[8];
 #pragma unroll
     for (int k = 0; k < 8; k++) q8[k] = __ldcs(d + (long)sl[k] * (OMNI_H / 8) + threadIdx.x);   // each row is read once
@@ -463,6 +494,10 @@ cudaError_t omni_launch_gather(const void *xn, const int32_t *rowmap, int rows8,
     int blocks = (rows8 + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     return omni_launch_chain(gather_kernel, dim3(blocks), dim3(256), 0, s, (const uint4 *)xn, rowmap, rows8, (uint4 *)xg);
+}
+
+cudaError_t omni_launch_rmsnorm(const float *x, const float *w, float eps, int rows, void *xn, cudaStream_t s) {
+    return omni_launch_chain(rmsnorm_bf16_kernel, dim3(rows), dim3(256), 0, s, (const float4 *)x, (const float4 *)w, eps, (uint4 *)xn);
 }
 
 cudaError_t omni_launch_combine(const void *d, const int32_t *ids, const float *weights, const int32_t *slots,

@@ -37,6 +37,7 @@ EXPORTS = [
     "clef_omni_set_option", "clef_omni_profile", "clef_omni_arena_bytes",
     "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
     "clef_omni_assign_noalloc", "clef_omni_ep_gate", "clef_omni_ep_sync",
+    "clef_omni_bind_norm", "clef_omni_encode_norm_moe", "clef_omni_bind_gguf", "clef_omni_gguf_check",
 ]
 NOALLOC_MAX_ROWS = 4096
 EP_HANDLES, EP_HANDLE_BYTES = 5, 64
@@ -76,6 +77,10 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_ep_gate": (C.c_bool, [vp, vp, vp]),
         "clef_omni_ep_sync": (C.c_bool, [vp, ci, cc, cz]),
         "clef_omni_assign_noalloc": (C.c_bool, [vp, ci, vp, vp, vp, vp, vp, vp, cc, cz]),
+        "clef_omni_bind_norm": (C.c_bool, [vp, ci, vp, C.c_float, ci, cc, cz]),
+        "clef_omni_encode_norm_moe": (C.c_bool, [vp, ci, vp, ci, ci, vp, cc, cz]),
+        "clef_omni_bind_gguf": (C.c_bool, [vp, cc, ci, cc, cz]),
+        "clef_omni_gguf_check": (C.c_bool, [cc, ci, ci, ci, ci, C.POINTER(C.c_float), cc, cz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -187,6 +192,29 @@ class OmniBackend:
         self._check(self.lib.clef_omni_encode_moe(self._g, layer, _ptr(xn), _ptr(x), T, len(seq_bounds) - 1, _ptr(seq_bounds),
                                                   self._err, _ERRLEN))
 
+    def bind_norm(self, layer: int, weight: torch.Tensor, eps: float = 1e-6):
+        """FP32 [2048] ffn_norm weights of the layer (host or CUDA tensor; the library copies them)."""
+        if tuple(weight.shape) != (H,) or weight.dtype != torch.float32:
+            raise ValueError("norm weights must be float32 [2048]")
+        weight = weight.contiguous()
+        self._check(self.lib.clef_omni_bind_norm(self._g, layer, _ptr(weight), float(eps),
+                                                 DEVICE if weight.is_cuda else HOST, self._err, _ERRLEN))
+
+    def encode_norm_moe(self, layer: int, x: torch.Tensor, seq_bounds=None):
+        """x[T][2048] (float32, CUDA) += MoE(RMSNorm(x)).  Asynchronous."""
+        T = x.shape[0]
+        if x.dtype != torch.float32 or tuple(x.shape) != (T, H) or not x.is_cuda:
+            raise ValueError("x must be a CUDA float32 [T,2048] tensor")
+        if seq_bounds is None:
+            seq_bounds = np.array([0, T], dtype=np.int32)
+        seq_bounds = np.ascontiguousarray(seq_bounds, dtype=np.int32)
+        self._check(self.lib.clef_omni_encode_norm_moe(self._g, layer, _ptr(x), T, len(seq_bounds) - 1, _ptr(seq_bounds),
+                                                       self._err, _ERRLEN))
+
+    def bind_gguf(self, path, n_layer: int):
+        """Bind layers 0..n_layer-1 (experts, router, ffn_norm) from a converted checkpoint file."""
+        self._check(self.lib.clef_omni_bind_gguf(self._g, str(path).encode(), n_layer, self._err, _ERRLEN))
+
     def forward_host(self, layer: int, xn_host: torch.Tensor, x_host: torch.Tensor, seq_bounds=None):
         """Synchronous pass on HOST tensors (x_host is updated in place)."""
         T = xn_host.shape[0]
@@ -234,6 +262,8 @@ class OmniBackend:
         if what in self._READ:
             dt, per = self._READ[what]
             out = np.empty((T, per) if what in ("ids", "weights", "logits") else (T * per,), dtype=dt)
+        elif what == "xnorm":                      # BF16 bit patterns
+            out = np.empty((T, H), np.uint16)
         elif what == "counts":
             out = np.empty(E, np.int32)
         elif what == "offsets":

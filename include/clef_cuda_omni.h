@@ -108,6 +108,29 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
 bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
                             const int32_t *seq_bounds, char *err, size_t errlen);
 
+/* ---- the steps either side of the block ------------------------------------------------- */
+
+/* RMSNorm weights of the layer's `ffn_norm` (FP32 [2048]; clef_engine.h:35-40, bound from
+ * `blk.N.ffn_norm.weight`, clef.c:236) and the epsilon of clef_config (clef.c:55).  where as in
+ * clef_omni_bind_layer; the library keeps its own device copy.  Atomic like the other binds. */
+bool clef_omni_bind_norm(clef_gpu *g, int layer, const float *weight, float eps, int where, char *err, size_t errlen);
+
+/* The reference's sequence `norm(ffn_norm)` + MoE section (clef_metal_omni.m:243 then 256-329) on
+ * the FP32 residual stream: xn = BF16(x * rsqrt(mean(x^2) + eps) * w) per token (clef.metal:190-204),
+ * then x += MoE(xn).  x is device FP32 [T][2048]; needs clef_omni_bind_norm for the layer. */
+bool clef_omni_encode_norm_moe(clef_gpu *g, int layer, float *x, int T, int n_seq, const int32_t *seq_bounds,
+                               char *err, size_t errlen);
+
+/* Binds layers 0..n_layer-1 from a converted checkpoint (GGUF v3 as tools/convert_omni.py:135-139
+ * writes it): router, gate/up and down expert tensors and the ffn_norm weights, with the type,
+ * rank and extent checks and messages of clef.c:194-246 (`bind_experts`, `bind_weights`).  The
+ * file is mapped, uploaded and unmapped; with expert parallelism connected, only this rank's
+ * experts are uploaded. */
+bool clef_omni_bind_gguf(clef_gpu *g, const char *path, int n_layer, char *err, size_t errlen);
+/* The same checks without a GPU, for any extents; returns the file's RMS epsilon in *rms_eps. */
+bool clef_omni_gguf_check(const char *path, int n_layer, int H, int ffn, int n_expert, float *rms_eps, char *err,
+                          size_t errlen);
+
 /* ---- expert parallelism over the GPUs of one node (no counterpart in the reference, which
  *      is single-device; defined by the 1/2/4/8-GPU configurations) -------------------- */
 
@@ -189,7 +212,8 @@ bool clef_omni_assign_noalloc(const int32_t *ids, int rows, int32_t *counts, int
 /* Copies an arena buffer of the last pass to host memory after waiting for the stream:
  * "ids" int32[T][8], "weights" f32[T][8], "logits" f32[T][128], "counts" int32[128],
  * "offsets" int32[129], "rowmap" int32[T*8], "slots" int32[T*8], "status" u32,
- * "rechecked" int32 (rows whose order was decided by the exact pass). */
+ * "rechecked" int32 (rows whose order was decided by the exact pass), "xnorm" bf16[T][2048]
+ * (the normalised rows clef_omni_encode_norm_moe fed to the block). */
 bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char *err, size_t errlen);
 /* Options: "debug_poison" 0/1 (CLEF_DEBUG_POISON), "router_exact" 0/1 (decide every row with
  * FP64 logits), "router_eps" (bound on the tensor-core logit error, x1e-9), "gemm" 0 =

@@ -18,6 +18,9 @@ What is restated, and from where (paths inside the reference project):
                         once.  Expert tensors use the converted layout
                         `gate_up [E][2F][H]` (gate rows first) and `down [E][H][F]`
                         (tools/convert_omni.py:135-139).
+* `rmsnorm`          -- ref/omni_fp64.py:31-32 (`x * rsqrt(mean(x^2) + eps) * weight`), the
+                        `ffn_norm` in front of the block (metal/clef.metal:190-204 is the
+                        reference's FP32 kernel for it).
 * `assign_padded`    -- the serial oracle inside tests/test_omni_assign.m:44-56 (counts,
                         32-row padded offsets, row map with -1 padding, slots).
 * `assign_canonical` -- the same stable counting sort without padding: the comparable form
@@ -158,6 +161,12 @@ def moe_block_f32(x, router, gate_up, down, bias=None):
 
 
 # --------------------------------------------------------------------------- permutation
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """FP64 RMSNorm over the last dimension (ref/omni_fp64.py:31-32)."""
+    x = x.double()
+    return x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * weight.double()
+
+
 def assign_padded(ids: np.ndarray, n_expert: int = E, pad: int = 32):
     """tests/test_omni_assign.m:44-56, word for word in behaviour: every expert run is padded
     to a multiple of `pad` rows, padding rows map to -1."""

@@ -14,6 +14,9 @@ What is stored (small .npz files, committed):
                     executes per layer (`Qwen3OmniMoeThinkerTextSparseMoeBlock`, eager
                     experts, FP32 math on the BF16-rounded weights), on the same inputs:
                     32 sampled rows, column sums over all rows and the router's ids.
+* rms_small.npz  -- inputs and output of the reference's `ref/omni_fp64.py: rms()` (the FP64
+                    RMSNorm in front of the block) on nine seeded rows, among them tiny, large
+                    and all-zero ones.
 * route_small.npz-- `route()` of the reference on small random FP64 problems (4 experts
                     top-2 and 16 experts top-4), inputs included.
 
@@ -64,10 +67,23 @@ def hf_block(router, gate_up, down):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project")
+    ap.add_argument("--only", choices=["rms"], help="regenerate one file only")
     args = ap.parse_args()
     ref = load_reference_fp64(Path(args.reference))
     out_dir = Path(__file__).resolve().parent
     torch.set_num_threads(max(1, torch.get_num_threads()))
+
+    # ---- RMSNorm in front of the block: the reference's own ref/omni_fp64.py `rms`
+    from types import SimpleNamespace
+    g = torch.Generator().manual_seed(23)
+    xr = torch.randn(9, 2048, generator=g, dtype=torch.float64)
+    xr[1] *= 1e-4; xr[2] *= 300.0; xr[3, 5:] = 0.0; xr[4] = 0.0        # tiny, large, one-hot-ish and all-zero rows
+    wr = 1.0 + 0.1 * torch.randn(2048, generator=g, dtype=torch.float64)
+    yr = ref.rms(xr, SimpleNamespace(variance_epsilon=1e-6, weight=wr))
+    np.savez_compressed(out_dir / "rms_small.npz", x=xr.numpy(), w=wr.numpy(), eps=np.float64(1e-6), y=yr.numpy())
+    print("rms: max |restatement - reference| =", float((orc.rmsnorm(xr, wr, 1e-6) - yr).abs().max()))
+    if args.only == "rms":
+        return
 
     # ---- configuration 1: T=512, seed 0
     router, gate_up, down = orc.make_weights(0)

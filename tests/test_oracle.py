@@ -164,3 +164,11 @@ def test_compare_routing_exemption():
     assert orc.compare_routing(got, ref, lg) == (0, 1)
     got[0, 7] = 8
     assert orc.compare_routing(got, ref, lg) == (1, 1)
+
+
+def test_rmsnorm_matches_reference_rms():
+    # ref/omni_fp64.py:31-32 on nine seeded rows (tiny, large, mostly-zero and all-zero among them)
+    g = np.load(GOLDEN / "rms_small.npz")
+    got = orc.rmsnorm(torch.from_numpy(g["x"]), torch.from_numpy(g["w"]), float(g["eps"]))
+    assert np.array_equal(got.numpy(), g["y"])
+    assert np.all(got.numpy()[4] == 0.0)            # all-zero row stays zero (eps keeps the rsqrt finite)
