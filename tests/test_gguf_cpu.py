@@ -99,3 +99,36 @@ def test_garbage_and_missing_files(tmp_path):
     # a string length that runs past the end
     (tmp_path / "str.gguf").write_bytes(b"GGUF" + (3).to_bytes(4, "little") + (0).to_bytes(8, "little") + (1).to_bytes(8, "little") + (1 << 50).to_bytes(8, "little") + b"\0" * 32)
     assert "truncated" in check(tmp_path / "str.gguf")[2]
+
+
+def test_loader_is_callable_from_a_c_host(good, tmp_path):
+    """The reference's host is C: a C program built against the header and the shared library
+    checks a file (no GPU needed for this entry point)."""
+    import subprocess
+    from pathlib import Path
+
+    from cleffa_b200.omni import _LIB_PATH
+
+    tmp, kv, tensors = good
+    write_gguf(tmp / "ok.gguf", kv, tensors)
+    src = tmp_path / "host.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include "clef_cuda_omni.h"
+int main(int argc, char **argv) {
+    char err[256] = "";
+    float eps = 0.f;
+    if (argc < 2) return 2;
+    if (!clef_omni_gguf_check(argv[1], 2, 64, 32, 4, &eps, err, sizeof err)) { printf("refused: %s\n", err); return 1; }
+    printf("ok eps=%g\n", eps);
+    return 0;
+}
+''')
+    root = Path(__file__).resolve().parents[1]
+    exe = tmp_path / "host"
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", str(root / "include"), str(src), "-o", str(exe),
+                    "-L", str(_LIB_PATH.parent), "-lclef_cuda_omni", f"-Wl,-rpath,{_LIB_PATH.parent}"], check=True)
+    out = subprocess.run([str(exe), str(tmp / "ok.gguf")], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.startswith("ok eps=1e-06"), out.stdout + out.stderr
+    out = subprocess.run([str(exe), str(tmp / "absent.gguf")], capture_output=True, text=True)
+    assert out.returncode == 1 and "cannot open" in out.stdout
