@@ -203,7 +203,7 @@ def test_forward_host_equals_device_path(bound0, T):
         bound0.forward_host(0, x, res.clone(), np.array([0, T + 1], dtype=np.int32))
 
 
-def test_three_layer_stack_teacher_forced(backend):
+def test_three_layer_stack_teacher_forced(backend, weights0):
     # configuration 3 in miniature: MoE sublayers with a residual add, independent weights per
     # layer.  Routing flips compound across layers, so every layer is checked on the input the
     # GPU actually fed it (its own residual, rounded to BF16), and the end is checked too.
@@ -222,4 +222,5 @@ def test_three_layer_stack_teacher_forced(backend):
                    slots=backend.read("slots", T), rowmap=backend.read("rowmap", T))
         check_against_oracle(got, xn.cpu(), ws[l])
         ref = ref + orc.experts(ref.to(torch.bfloat16), got["ids"].astype(np.int64), got["weights"].astype(np.float64), ws[l][1], ws[l][2])
+    backend.bind_layer(0, *weights0)                         # layer 0 is shared with the other tests (fixture bound0)
     assert orc.rel_l2(x.cpu(), ref) <= REL_L2_GATE

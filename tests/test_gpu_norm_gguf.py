@@ -25,8 +25,9 @@ def residual(seed, T):
 
 
 @pytest.mark.parametrize("T", [1, 333, 2500])
-def test_norm_in_front_of_the_block(bound0, T):
-    b = bound0
+def test_norm_in_front_of_the_block(backend, weights0, T):
+    b = backend
+    b.bind_layer(0, *weights0)
     x0, w = residual(5 + T, T)
     b.bind_norm(0, w, EPS)
     x = x0.cuda()
@@ -44,12 +45,8 @@ def test_norm_in_front_of_the_block(bound0, T):
     assert torch.equal(x, y)
     # 3. and the oracle's block on the rows the GPU used
     ids, wts = b.read("ids", T), b.read("weights", T)
-    ref = orc.experts(xn.cpu(), ids.astype(np.int64), wts.astype(np.float64), *bound_weights(b)[1:], residual=x0)
+    ref = orc.experts(xn.cpu(), ids.astype(np.int64), wts.astype(np.float64), weights0[1], weights0[2], residual=x0)
     assert orc.rel_l2(x.cpu(), ref) < 1e-2
-
-
-def bound_weights(b):
-    return orc.make_weights(0)
 
 
 def test_norm_needs_weights_and_valid_arguments(backend):
