@@ -1,7 +1,8 @@
-// HBM-bound stages of the Clef-Omni MoE block for sm_100a: routing selection (warp-level
-// top-k), exact re-evaluation of near-tied router rows, deterministic histogram + stable
-// counting sort, row gather, weighted combine, plus plain CUDA-core check kernels for the
-// two expert products.  The tensor-core kernels live in omni_sm100.cu.
+// HBM- and latency-bound stages of the Clef-Omni MoE block for sm_100a: exact re-evaluation of
+// near-tied router rows, deterministic stable counting sort, weighted combine, the RMSNorm in
+// front of the block, plus what the default path only uses for checks or caller-supplied
+// routing: warp-level top-k selection, the stand-alone histogram, the row gather and plain
+// CUDA-core kernels for the two expert products.  The tensor-core kernels live in omni_sm100.cu.
 //
 // Reference behaviour these kernels reproduce (paths inside the reference project):
 //   selection / weights     metal/clef.metal:2347-2394  (omni_route)
@@ -10,6 +11,7 @@
 //   gather                  metal/clef.metal:2445-2453  (omni_gather)
 //   combine                 metal/clef.metal:2494-2523  (omni_combine)
 //   route capture           metal/clef.metal:2526-2539  (omni_trace)
+//   norm before the block   metal/clef.metal:190-204    (rmsnorm_f32)
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>

@@ -2,9 +2,13 @@
 //   * router_sm100_kernel   x[T][2048] . W_r[128][2048]^T on tcgen05 with the FP32 accumulator in
 //                           TMEM, fused with bias, nonfinite check, top-8 selection, renormalised
 //                           weights and the near-tie flagging that feeds the exact pass
-//                           (reference: metal/clef.metal:2330-2394, omni_router + omni_route)
+//                           (reference: metal/clef.metal:2330-2394, omni_router + omni_route),
+//                           and with the per-segment expert counts of the counting sort
+//                           (metal/clef.metal:2396-2410, omni_assign_count)
 //   * expert_gemm_kernel<GATEUP>  per expert: h = silu(Xe Wg^T) * (Xe Wu^T), SwiGLU in the epilogue
-//                           (reference: metal/clef.metal:2455-2492, omni_expert_gemm + omni_swiglu)
+//                           (reference: metal/clef.metal:2455-2492, omni_expert_gemm + omni_swiglu);
+//                           on one GPU the kernel also fetches the expert's token rows through
+//                           the permutation itself (metal/clef.metal:2445-2453, omni_gather)
 //   * expert_gemm_kernel<DOWN>    per expert: d = He Wd^T            (clef.metal:2455-2482)
 //
 // Orientation of the expert products: the WEIGHT rows are the MMA M dimension (always a full
@@ -13,7 +17,8 @@
 // weight tile is streamed from HBM by exactly one CTA when the expert has <= 256 rows.
 //
 // Operands reach shared memory through per-CTA TMA loads (cp.async.bulk.tensor, 128-byte
-// swizzle); no cluster multicast is used anywhere.  Every wait on an mbarrier is bounded: when
+// swizzle), the gathered token rows through 16-byte cp.async into the same swizzled layout; no
+// cluster multicast is used anywhere.  Every wait on an mbarrier is bounded: when
 // it runs out the CTA raises OMNI_ST_TIMEOUT in the status word, drains what it issued, frees
 // its TMEM and returns.
 #include <cuda_bf16.h>
