@@ -52,3 +52,14 @@ def test_header_compiles_as_c_and_cxx(tmp_path):
         src.write_text('#include "clef_cuda_omni.h"\nint main(void) { return sizeof(clef_omni_config) == 20 ? 0 : 1; }\n')
         subprocess.run([comp, std, "-Wall", "-Werror", "-I", str(ROOT / "include"), str(src), "-o", str(tmp_path / "t")], check=True)
         subprocess.run([str(tmp_path / "t")], check=True)
+
+
+def test_open_without_a_gpu_fails_loudly():
+    """No CPU path exists behind the boundary: without a usable CUDA device the context cannot
+    be opened, and the message says why."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("this box has a GPU")
+    with pytest.raises(omni.OmniError, match="cuda: "):
+        omni.OmniBackend(0)
