@@ -214,7 +214,17 @@ template <int MODE> struct GemmSmem {
 };
 static_assert(GemmSmem<MODE_GATEUP>::TOTAL_BYTES <= 232448 && GemmSmem<MODE_DOWN>::TOTAL_BYTES <= 232448, "shared memory budget");
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+// silu(g) * u with silu(g) = g * sigmoid(g) = (g/2) * (1 + tanh(g/2)): one special-function
+// instruction per element instead of two (exp and reciprocal).  The epilogue holds tensor memory
+// while it computes this and is bound by the special-function unit (one warp instruction per 8
+// cycles), so the count of such instructions is what matters.  tanh.approx.f32 is accurate to
+// about 2^-11 absolute; the result is rounded to BF16 (2^-9 relative) right after.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    const float hg = 0.5f * g;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(hg));
+    return fmaf(hg, t, hg) * u;
+}
 
 // Work distribution.  The work list is expert-major: for one expert, every (weight tile m,
 // token tile j) pair is consecutive, so CTAs that run at the same time share either the token
