@@ -129,10 +129,10 @@ __device__ __forceinline__ void recheck_row(const __nv_bfloat16 *__restrict__ xn
     double val[4], approx[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) approx[j] = val[j] = (double)logits[row * OMNI_E + lane + 32 * j];
+    const XRow x = load_xrow(xn, row, lane);              // in flight while the threshold is found
     double top_v[8]; int top_id[8];
     warp_topn<8>(val, lane, top_v, top_id);               // every warp finds the same threshold
     const double floor_v = top_v[7] - 2.0 * (double)eps;
-    const XRow x = load_xrow(xn, row, lane);
     sync();
     int c = 0;
 #pragma unroll

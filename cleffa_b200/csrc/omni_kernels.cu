@@ -162,56 +162,68 @@ __global__ void __launch_bounds__(256) assign_hist_kernel(const int32_t *__restr
 // per-segment bases, writes counts/offsets and the token-tile list of the expert GEMMs.
 __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_state st) {
     __shared__ int part[8][OMNI_E];
-    __shared__ int cnt[OMNI_E], scan_a[OMNI_E], scan_b[OMNI_E];
+    __shared__ int warp_rows[4], warp_tiles[4];
     dep_wait();
     dep_launch();
-    const int e = threadIdx.x & (OMNI_E - 1), grp = threadIdx.x >> 7;
+    const int e = threadIdx.x & (OMNI_E - 1), grp = threadIdx.x >> 7, lane = threadIdx.x & 31;
     const int per = (nseg + 7) / 8;
     const int s0 = grp * per, s1 = min(nseg, s0 + per);
+    // up to 16 segments per thread (4096 tokens) stay in registers between the two sweeps
+    constexpr int KEEP = 16;
+    int c[KEEP];
     int sum = 0;
-    for (int s = s0; s < s1; s++) sum += st.segcount[(long)s * OMNI_E + e];
+#pragma unroll
+    for (int i = 0; i < KEEP; i++) {
+        c[i] = s0 + i < s1 ? st.segcount[(long)(s0 + i) * OMNI_E + e] : 0;
+        sum += c[i];
+    }
+    for (int s = s0 + KEEP; s < s1; s++) sum += st.segcount[(long)s * OMNI_E + e];
     part[grp][e] = sum;
     __syncthreads();
     int run = 0;
     for (int gq = 0; gq < grp; gq++) run += part[gq][e];
-    for (int s = s0; s < s1; s++) {
-        const int c = st.segcount[(long)s * OMNI_E + e];
-        st.segcount[(long)s * OMNI_E + e] = run;
-        run += c;
+#pragma unroll
+    for (int i = 0; i < KEEP; i++) {
+        if (s0 + i < s1) { st.segcount[(long)(s0 + i) * OMNI_E + e] = run; run += c[i]; }
     }
+    for (int s = s0 + KEEP; s < s1; s++) {
+        const int v = st.segcount[(long)s * OMNI_E + e];
+        st.segcount[(long)s * OMNI_E + e] = run;
+        run += v;
+    }
+    // inclusive scans over the 128 experts (rows and token tiles): shuffles inside each of the
+    // four warps of group 0, then the totals of the warps before
+    int total = 0, rows_incl = 0, tiles_incl = 0;
     if (grp == 0) {
-        int total = 0;
 #pragma unroll
         for (int gq = 0; gq < 8; gq++) total += part[gq][e];
-        cnt[e] = total;
-        scan_a[e] = total;                          // rows
-        scan_b[e] = (total + OMNI_TILE_N - 1) / OMNI_TILE_N;   // token tiles
+        rows_incl = total;
+        tiles_incl = (total + OMNI_TILE_N - 1) / OMNI_TILE_N;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int a = __shfl_up_sync(FULL, rows_incl, d), b = __shfl_up_sync(FULL, tiles_incl, d);
+            if (lane >= d) { rows_incl += a; tiles_incl += b; }
+        }
+        if (lane == 31) { warp_rows[e >> 5] = rows_incl; warp_tiles[e >> 5] = tiles_incl; }
     }
     __syncthreads();
-    // inclusive Hillis-Steele scans over the 128 experts
-    for (int d = 1; d < OMNI_E; d <<= 1) {
-        int a = 0, b = 0;
-        if (grp == 0 && e >= d) { a = scan_a[e - d]; b = scan_b[e - d]; }
-        __syncthreads();
-        if (grp == 0) { scan_a[e] += a; scan_b[e] += b; }
-        __syncthreads();
-    }
     if (grp == 0) {
-        const int n = cnt[e];
-        const int off = scan_a[e] - n;
+        for (int q = 0; q < (e >> 5); q++) { rows_incl += warp_rows[q]; tiles_incl += warp_tiles[q]; }
+        const int n = total;
+        const int off = rows_incl - n;
         st.counts[e] = n;
         st.offsets[e] = off;
-        if (e == OMNI_E - 1) st.offsets[OMNI_E] = scan_a[e];
+        if (e == OMNI_E - 1) st.offsets[OMNI_E] = rows_incl;
         // expert-major tile list
         const int nt = (n + OMNI_TILE_N - 1) / OMNI_TILE_N;
-        const int first = scan_b[e] - nt;
+        const int first = tiles_incl - nt;
         // an expert's rows are split into nt tiles of near-equal length: tiles that share a
         // weight tile then advance at the same pace and meet in L2
         const int base = nt ? n / nt : 0, extra = nt ? n % nt : 0;
         for (int j = 0; j < nt; j++)
             st.ttiles[first + j] = omni_ttile{e, off + j * base + min(j, extra), base + (j < extra), first | (nt << 16)};
         if (e < 8) st.sched[e] = 0;
-        if (e == 0) *st.n_ttiles = scan_b[OMNI_E - 1];
+        if (e == OMNI_E - 1) *st.n_ttiles = tiles_incl;
     }
 }
 
