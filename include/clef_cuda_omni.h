@@ -103,7 +103,7 @@ bool clef_omni_encode_moe(clef_gpu *g, int layer, const void *xn, float *x, int 
 /* One synchronous pass with HOST buffers: begin, copy xn (BF16) and x (FP32) to the device,
  * encode_moe, copy x back, complete.  This is the call a host engine makes when its
  * activations live in host memory.  Above 1536 tokens (one GPU) the batch is processed in
- * pieces of about a thousand tokens whose uploads, kernels and downloads overlap; the bits are
+ * pieces of about 1400 tokens whose uploads, kernels and downloads overlap; the bits are
  * those of one pass.  Page-locked host buffers are needed for the copies to overlap. */
 bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
                             const int32_t *seq_bounds, char *err, size_t errlen);
