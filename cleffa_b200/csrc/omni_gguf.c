@@ -9,7 +9,10 @@
  *   blk.N.ffn_router.weight         BF16  [H, E]            (ne[0] is the row length)
  *   blk.N.ffn_gate_up_exps.weight   BF16  [H, 2*ffn, E]     gate rows then up rows per expert
  *   blk.N.ffn_down_exps.weight      BF16  [ffn, H, E]
- *   clef.attention.layer_norm_rms_epsilon   F32 key
+ *   clef.attention.layer_norm_rms_epsilon   F32 key (must be 1e-6), and the keys that pin the
+ *   geometry: general.architecture, clef.block_count, clef.embedding_length,
+ *   clef.feed_forward_length, clef.moe.expert_count, clef.moe.expert_used_count,
+ *   clef.moe.normalize_topk (clef.c:27-36, 76-90)
  *
  * The reader is a plain restatement of the published container format: little-endian header
  * (magic "GGUF", version 3, tensor count, key/value count), key/value pairs, tensor infos
@@ -46,6 +49,10 @@ typedef struct {
     tensor_info *tensors;
     float rms_eps; bool have_eps;
     uint32_t alignment;
+    /* the configuration keys that fix the block's geometry (clef.c:34-36, 76-79), 0 = absent */
+    uint32_t cfg_H, cfg_ffn, cfg_experts, cfg_used, cfg_layers;
+    int normalize_topk;           /* -1 absent, else the stored bool */
+    bool arch_clef;
     char err[256];
 } gguf_view;
 
@@ -107,6 +114,7 @@ static bool view_open(gguf_view *v, const char *path) {
     memset(v, 0, sizeof *v);
     v->fd = -1;
     v->alignment = 32;
+    v->normalize_topk = -1;
     if (!path) return fail(v, "gguf: no path");
     v->fd = open(path, O_RDONLY);
     if (v->fd < 0) return fail(v, "gguf: cannot open %s", path);
@@ -124,6 +132,26 @@ static bool view_open(gguf_view *v, const char *path) {
     for (uint64_t i = 0; i < n_kv; i++) {
         const char *k; uint64_t kn; uint32_t type;
         if (!rd_str(v, &k, &kn) || !rd_u32(v, &type)) return false;
+        uint32_t *u32_dst = NULL;
+        if (type == T_U32) {
+            if (key_is(k, kn, "clef.embedding_length")) u32_dst = &v->cfg_H;
+            else if (key_is(k, kn, "clef.feed_forward_length")) u32_dst = &v->cfg_ffn;
+            else if (key_is(k, kn, "clef.moe.expert_count")) u32_dst = &v->cfg_experts;
+            else if (key_is(k, kn, "clef.moe.expert_used_count")) u32_dst = &v->cfg_used;
+            else if (key_is(k, kn, "clef.block_count")) u32_dst = &v->cfg_layers;
+        }
+        if (u32_dst) {
+            if (!need(v, 4)) return false;
+            memcpy(u32_dst, v->base + v->pos, 4);
+        } else if (type == T_BOOL && key_is(k, kn, "clef.moe.normalize_topk")) {
+            if (!need(v, 1)) return false;
+            v->normalize_topk = v->base[v->pos];
+        } else if (type == T_STRING && key_is(k, kn, "general.architecture")) {
+            uint64_t n;
+            if (!need(v, 8)) return false;
+            memcpy(&n, v->base + v->pos, 8);
+            v->arch_clef = n == 4 && v->size - v->pos >= 12 && !memcmp(v->base + v->pos + 8, "clef", 4);
+        }
         if (type == T_F32 && key_is(k, kn, "clef.attention.layer_norm_rms_epsilon")) {
             if (!need(v, 4)) return false;
             memcpy(&v->rms_eps, v->base + v->pos, 4);
@@ -199,6 +227,27 @@ static bool layer_find(gguf_view *v, int l, uint64_t H, uint64_t ffn, uint64_t E
     return true;
 }
 
+/* The reference treats the metadata as untrusted and pins the geometry before it touches a
+ * tensor (clef.c:16-24 `cfg_u32`, clef.c:27-32 the architecture, clef.c:55-57 the epsilon,
+ * clef.c:76-90 the Omni geometry and routing configuration); same order and messages here for
+ * the keys the block depends on.  top_k = 0 accepts any count from 1 to the expert count. */
+static bool config_ok(gguf_view *v, int n_layer, uint64_t H, uint64_t ffn, uint64_t E, uint64_t top_k) {
+    if (!v->arch_clef) return fail(v, "model: not a clef GGUF (convert with tools/convert.py)");
+    const struct { const char *key; uint32_t value; } need_u32[] = {
+        {"clef.block_count", v->cfg_layers}, {"clef.embedding_length", v->cfg_H}, {"clef.feed_forward_length", v->cfg_ffn},
+    };
+    for (size_t i = 0; i < sizeof need_u32 / sizeof need_u32[0]; i++)
+        if (need_u32[i].value == 0 || need_u32[i].value > (1u << 24)) return fail(v, "model: missing or invalid %s", need_u32[i].key);
+    if (!v->have_eps) return fail(v, "model: missing rms eps / rope base");
+    if (v->cfg_experts == 0 || v->cfg_experts > (1u << 24)) return fail(v, "model: missing or invalid clef.moe.expert_count");
+    if (v->cfg_used == 0 || v->cfg_used > (1u << 24)) return fail(v, "model: missing or invalid clef.moe.expert_used_count");
+    if (v->cfg_H != H || v->cfg_ffn != ffn || v->cfg_experts != E || v->cfg_used > v->cfg_experts ||
+        (top_k && v->cfg_used != top_k) || v->rms_eps != 1e-6f || v->normalize_topk != 1)
+        return fail(v, "model: unsupported Omni decoder/head geometry or routing configuration");
+    if (n_layer < 1 || (uint64_t)n_layer > v->cfg_layers) return fail(v, "model: the checkpoint has %u layers", v->cfg_layers);
+    return true;
+}
+
 static void copy_err(const gguf_view *v, char *err, size_t errlen) {
     if (err && errlen) snprintf(err, errlen, "%s", v->err);
 }
@@ -208,11 +257,11 @@ bool clef_omni_gguf_check(const char *path, int n_layer, int H, int ffn, int n_e
     gguf_view v;
     bool ok = view_open(&v, path);
     if (ok && (n_layer < 1 || H < 1 || ffn < 1 || n_expert < 1)) ok = fail(&v, "model: invalid Omni dimensions");
+    if (ok) ok = config_ok(&v, n_layer, (uint64_t)H, (uint64_t)ffn, (uint64_t)n_expert, 0);
     for (int l = 0; ok && l < n_layer; l++) {
         layer_tensors t;
         ok = layer_find(&v, l, (uint64_t)H, (uint64_t)ffn, (uint64_t)n_expert, &t);
     }
-    if (ok && !v.have_eps) ok = fail(&v, "model: missing rms eps / rope base");     /* clef.c:55-57 */
     if (ok && rms_eps) *rms_eps = v.rms_eps;
     if (!ok) copy_err(&v, err, errlen);
     view_close(&v);
@@ -223,7 +272,7 @@ bool clef_omni_bind_gguf(clef_gpu *g, const char *path, int n_layer, char *err, 
     gguf_view v;
     bool ok = view_open(&v, path);
     if (ok && (!g || n_layer < 1)) ok = fail(&v, "cuda: invalid Omni expert tensor binding");
-    if (ok && !v.have_eps) ok = fail(&v, "model: missing rms eps / rope base");
+    if (ok) ok = config_ok(&v, n_layer, 2048, 768, 128, 8);
     if (!ok) { copy_err(&v, err, errlen); view_close(&v); return false; }
     for (int l = 0; ok && l < n_layer; l++) {
         layer_tensors t;

@@ -123,7 +123,9 @@ bool clef_omni_encode_norm_moe(clef_gpu *g, int layer, float *x, int T, int n_se
 
 /* Binds layers 0..n_layer-1 from a converted checkpoint (GGUF v3 as tools/convert_omni.py:135-139
  * writes it): router, gate/up and down expert tensors and the ffn_norm weights, with the type,
- * rank and extent checks and messages of clef.c:194-246 (`bind_experts`, `bind_weights`).  The
+ * rank and extent checks and messages of clef.c:194-246 (`bind_experts`, `bind_weights`), after the
+ * metadata checks of clef.c:27-90 for the keys the block depends on (architecture, layer count,
+ * width, intermediate size, expert counts, renormalised top-k, epsilon).  The
  * file is mapped, uploaded and unmapped; with expert parallelism connected, only this rank's
  * experts are uploaded. */
 bool clef_omni_bind_gguf(clef_gpu *g, const char *path, int n_layer, char *err, size_t errlen);

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 F32, F16, BF16 = 0, 1, 30
-T_U32, T_F32, T_STRING, T_ARRAY, T_I32 = 4, 6, 8, 9, 5
+T_U32, T_F32, T_BOOL, T_STRING, T_ARRAY, T_I32 = 4, 6, 7, 8, 9, 5
 
 
 def _s(b: str | bytes) -> bytes:
@@ -24,6 +24,8 @@ def _s(b: str | bytes) -> bytes:
 
 
 def _kv(key, value) -> bytes:
+    if isinstance(value, bool):
+        return _s(key) + struct.pack("<IB", T_BOOL, int(value))
     if isinstance(value, float):
         return _s(key) + struct.pack("<If", T_F32, value)
     if isinstance(value, int):
@@ -81,3 +83,12 @@ def omni_layers(weights_per_layer, norms, H, ffn, E):
         out[f"blk.{l}.ffn_gate_up_exps.weight"] = (BF16, gate_up)
         out[f"blk.{l}.ffn_down_exps.weight"] = (BF16, down)
     return out
+
+
+def omni_kv(H, ffn, E, used, n_layer, eps=1e-6):
+    """The metadata keys that pin the block's geometry (clef.c:27-36, 55, 76-79), plus a few of
+    other types so that the reader's value skipping is exercised."""
+    return {"general.architecture": "clef", "clef.block_count": n_layer, "clef.embedding_length": H,
+            "clef.feed_forward_length": ffn, "clef.moe.expert_count": E, "clef.moe.expert_used_count": used,
+            "clef.moe.normalize_topk": True, "clef.attention.layer_norm_rms_epsilon": eps,
+            "tokenizer.tokens": ["a", "bc", ""], "clef.rope.mrope_section": [24, 20, 20]}

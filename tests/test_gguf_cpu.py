@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from cleffa_b200.omni import load_library
-from tests.gguf_writer import BF16, F32, omni_layers, write_gguf
+from tests.gguf_writer import BF16, F32, omni_kv, omni_layers, write_gguf
 
 H, FFN, E = 64, 32, 4
 EPS_KEY = "clef.attention.layer_norm_rms_epsilon"
@@ -32,7 +32,7 @@ def check(path, n_layer=2, dims=(H, FFN, E)):
 def good(tmp_path):
     layers = [layer(1), layer(2)]
     tensors = omni_layers([w for w, _ in layers], [n for _, n in layers], H, FFN, E)
-    kv = {"general.architecture": "clef", EPS_KEY: 1e-6, "tokenizer.tokens": ["a", "bc", ""], "clef.sections": [1, 2, 3]}
+    kv = omni_kv(H, FFN, E, used=2, n_layer=2)
     return tmp_path, kv, tensors
 
 
@@ -52,12 +52,20 @@ def test_well_formed_file_passes(good):
     ("extent", "missing or invalid tensor blk.1.ffn_router.weight"),
     ("norm_type", "missing or invalid tensor blk.0.ffn_norm.weight"),
     ("no_eps", "missing rms eps"),
-    ("layers", "blk.2.ffn_norm.weight"),
+    ("eps_value", "unsupported Omni decoder/head geometry or routing configuration"),
+    ("not_clef", "not a clef GGUF"),
+    ("no_expert_count", "missing or invalid clef.moe.expert_count"),
+    ("no_width", "missing or invalid clef.embedding_length"),
+    ("used_gt_experts", "unsupported Omni decoder/head geometry or routing configuration"),
+    ("no_renorm", "unsupported Omni decoder/head geometry or routing configuration"),
+    ("renorm_off", "unsupported Omni decoder/head geometry or routing configuration"),
+    ("layers", "the checkpoint has 2 layers"),
+    ("missing_layer", "blk.2.ffn_norm.weight"),
     ("magic", "bad magic"),
     ("version", "unsupported version"),
     ("truncated", "past the end of the file"),
     ("misaligned", "not aligned"),
-    ("dims", "blk.0.ffn_norm.weight"),
+    ("dims", "unsupported Omni decoder/head geometry or routing configuration"),
 ])
 def test_malformed_files_are_refused(good, case, message):
     tmp, kv, tensors = good
@@ -72,8 +80,24 @@ def test_malformed_files_are_refused(good, case, message):
         tensors["blk.0.ffn_norm.weight"] = (BF16, tensors["blk.0.ffn_norm.weight"][1].to(torch.bfloat16))
     elif case == "no_eps":
         del kv[EPS_KEY]
+    elif case == "eps_value":
+        kv[EPS_KEY] = 1e-5
+    elif case == "not_clef":
+        kv["general.architecture"] = "llama"
+    elif case == "no_expert_count":
+        del kv["clef.moe.expert_count"]
+    elif case == "no_width":
+        del kv["clef.embedding_length"]
+    elif case == "used_gt_experts":
+        kv["clef.moe.expert_used_count"] = E + 1
+    elif case == "no_renorm":
+        del kv["clef.moe.normalize_topk"]
+    elif case == "renorm_off":
+        kv["clef.moe.normalize_topk"] = False
     elif case == "layers":
         n_layer = 3
+    elif case == "missing_layer":
+        n_layer, kv["clef.block_count"] = 3, 3
     elif case == "magic":
         args["magic"] = b"GGML"
     elif case == "version":

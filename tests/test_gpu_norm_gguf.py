@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from cleffa_b200 import OmniError
-from gguf_writer import BF16, F32, omni_layers, write_gguf
+from gguf_writer import BF16, F32, omni_kv, omni_layers, write_gguf
 from oracle import omni_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -73,8 +73,7 @@ def test_bind_from_checkpoint_file(backend, weights0, tmp_path):
     binding the tensors directly, norm weights included."""
     x0, w = residual(77, 300)
     path = tmp_path / "layer.gguf"
-    write_gguf(path, {"clef.attention.layer_norm_rms_epsilon": EPS, "general.architecture": "clef"},
-               omni_layers([weights0], [w], 2048, 768, 128))
+    write_gguf(path, omni_kv(2048, 768, 128, used=8, n_layer=1, eps=EPS), omni_layers([weights0], [w], 2048, 768, 128))
     b = backend
     b.bind_layer(1, *weights0); b.bind_norm(1, w, EPS)
     want = x0.cuda()
@@ -87,7 +86,7 @@ def test_bind_from_checkpoint_file(backend, weights0, tmp_path):
     b.bind_layer(0, *weights0)                             # what the session fixture promises
     # a file with the wrong extents is refused and the binding stays
     bad = tmp_path / "bad.gguf"
-    write_gguf(bad, {"clef.attention.layer_norm_rms_epsilon": EPS},
+    write_gguf(bad, omni_kv(2048, 768, 128, used=8, n_layer=1, eps=EPS),
                {"blk.0.ffn_norm.weight": (F32, w), "blk.0.ffn_router.weight": (BF16, weights0[0][:64].contiguous())})
     with pytest.raises(OmniError, match="missing or invalid tensor blk.0.ffn_router.weight"):
         b.bind_gguf(bad, 1)
