@@ -1,6 +1,6 @@
 // Programmatic dependent launch for the kernels of one MoE pass.
 //
-// The pass is a chain of eight kernels in one stream.  Launched the plain way, each kernel starts
+// The pass is a chain of seven kernels in one stream.  Launched the plain way, each kernel starts
 // only after the previous one has drained and its memory is flushed, and pays its launch latency
 // and prologue (barrier setup, tensor-memory allocation, descriptor prefetch) after that.  With
 // the stream-serialization attribute below, a kernel's blocks may become resident as soon as
