@@ -369,7 +369,7 @@ def ours(args):
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s",
                     "h2d_bytes_per_step": T_TOKENS * H * 2 + T_TOKENS * H * 4, "d2h_bytes_per_step": T_TOKENS * H * 4},
-            "gpu_launches": (KERNELS_PER_PASS * n_layers if world == 1 else KERNELS_PER_PASS_EP * micro) * args.steps,
+            "gpu_launches": ((KERNELS_PER_PASS + (1 if args.norm else 0)) * n_layers if world == 1 else KERNELS_PER_PASS_EP * micro) * args.steps,
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "expert_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
