@@ -78,6 +78,14 @@ def router_dot(x, w_bf16_bits):
     return out
 
 
+def rmsnorm(x, w, eps=1e-6):
+    x = np.ascontiguousarray(x, dtype=np.float64)
+    w = np.ascontiguousarray(w, dtype=np.float64)
+    out = np.zeros_like(x)
+    _lib().oracle_rmsnorm(_p(x, C.c_double), _p(w, C.c_double), C.c_double(eps), x.shape[0], x.shape[1], _p(out, C.c_double))
+    return out
+
+
 def moe_rows(x, residual, ids, weights, gate_up_bits, down_bits, top=8):
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, hn = x.shape

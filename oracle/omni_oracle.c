@@ -9,6 +9,8 @@
  *   oracle_router_dot        tests/test_omni_router.m:42 (FP64 dot of activations and BF16 weights)
  *   oracle_moe_rows          tests/test_omni_moe.m:104-113 (FP64 expert products and combine
  *                            in selection order, residual added once)
+ *   oracle_rmsnorm           metal/clef.metal:190-204 / ref/omni_fp64.py:31-32, in FP64
+ *                            (the ffn_norm in front of the block)
  *
  * Build: make -C oracle   (produces oracle/_build/libomni_oracle.so)
  */
@@ -107,6 +109,17 @@ void oracle_router_dot(const float *x, const uint16_t *w, int rows, int n_expert
         double s = 0;
         for (int k = 0; k < K; k++) s += (double)x[(size_t)t * K + k] * bf16_to_float(w[(size_t)e * K + k]);
         logits[(size_t)t * n_expert + e] = s;
+    }
+}
+
+/* y[t][i] = x[t][i] * (1 / sqrt(mean_i x[t][i]^2 + eps)) * w[i] */
+void oracle_rmsnorm(const double *x, const double *w, double eps, int rows, int Hn, double *y) {
+    for (int t = 0; t < rows; t++) {
+        const double *xr = x + (size_t)t * Hn;
+        double ss = 0;
+        for (int i = 0; i < Hn; i++) ss += xr[i] * xr[i];
+        const double inv = 1.0 / sqrt(ss / Hn + eps);
+        for (int i = 0; i < Hn; i++) y[(size_t)t * Hn + i] = xr[i] * inv * w[i];
     }
 }
 

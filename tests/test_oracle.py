@@ -172,3 +172,12 @@ def test_rmsnorm_matches_reference_rms():
     got = orc.rmsnorm(torch.from_numpy(g["x"]), torch.from_numpy(g["w"]), float(g["eps"]))
     assert np.array_equal(got.numpy(), g["y"])
     assert np.all(got.numpy()[4] == 0.0)            # all-zero row stays zero (eps keeps the rsqrt finite)
+
+
+def test_rmsnorm_c_restatement_agrees():
+    # summation order differs from torch's (serial here), so agreement is to rounding, not bitwise
+    g = np.load(GOLDEN / "rms_small.npz")
+    got = c_oracle.rmsnorm(g["x"], g["w"], float(g["eps"]))
+    scale = np.abs(g["y"]).max(axis=1, keepdims=True) + 1e-300
+    assert (np.abs(got - g["y"]) / scale).max() < 1e-14
+    assert np.all(got[4] == 0.0)
