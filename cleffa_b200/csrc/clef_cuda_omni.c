@@ -32,7 +32,8 @@ typedef struct {
 
 /* The scratch arena (clef_omni_gpu in the reference, clef_metal_omni.m:18-23). */
 typedef struct {
-    float *logits;                      /* [CHUNK][128] approximate router logits */
+    float *logits;                      /* [CHUNK][128] router logits: tensor-core values, exact (hi) where the exact pass ran */
+    float *logits_low;                  /* [CHUNK][128] remainder of the exact logits (hi + low); zero elsewhere; kept for route capture */
     int32_t *ids; float *weights;       /* [CHUNK][8] */
     int32_t *flag_rows, *n_flag;        /* rows handed to the exact pass */
     uint32_t *status, *sink;
@@ -85,7 +86,11 @@ struct clef_gpu {
         int rank, world;
         bool ipc;                        /* peers opened through CUDA IPC (else direct pointers) */
         omni_ep_peers peers;
-        uint32_t epoch;
+        uint32_t epoch;                  /* last barrier epoch this rank launched */
+        uint32_t sync_count;             /* successful clef_omni_ep_sync calls, as agreed between the ranks */
+        bool need_sync;                  /* a pass failed: the ranks may be out of step until the next sync */
+        uint64_t wait_ns;                /* bound on every in-pass wait for other ranks; 0 = 2 s */
+        uint32_t *sync_result;           /* device [2] */
         void *dret; int32_t *rowinfo, *counts, *send_base, *n_local_rows; uint32_t *flags;
         void *opened[OMNI_EP_MAX][OMNI_EP_BUFFERS];
         cudaEvent_t gate_wait, gate_record;   /* optional host-supplied events around the dispatch phase */
@@ -183,7 +188,14 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
         free(g);
         return false;
     }
-    for (int p = 0; p < PROF_SLOTS; p++) for (int i = 0; i < N_STAGE_EVENTS; i++) cudaEventCreate(&g->ev[p][i]);
+    for (int p = 0; p < PROF_SLOTS && e == cudaSuccess; p++)
+        for (int i = 0; i < N_STAGE_EVENTS && e == cudaSuccess; i++) e = cudaEventCreate(&g->ev[p][i]);
+    if (e != cudaSuccess) {
+        set_err(err, errlen, "cuda: cannot create the stage events: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        clef_cuda_omni_close(g);
+        return false;
+    }
     const char *v;
     if ((v = getenv("CLEF_DEBUG_POISON")) && *v == '1') g->debug_poison = true;
     if ((v = getenv("CLEF_PROFILE")) && *v == '1') g->profile = true;
@@ -204,7 +216,7 @@ static void free_layer(omni_layer *L) {
 
 static void free_arena(omni_arena *s) {
     if (!s) return;
-    void *all[] = {s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status, s->sink, s->sort.counts,
+    void *all[] = {s->logits, s->logits_low, s->ids, s->weights, s->flag_rows, s->n_flag, s->status, s->sink, s->sort.counts,
                    s->sort.offsets, s->sort.rowmap, s->sort.slots, s->sort.segcount, s->sort.ttiles, s->sort.n_ttiles, s->sort.sched,
                    s->xg, s->h, s->d, s->stamps};
     for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
@@ -254,6 +266,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
     if (!s) { set_err(err, errlen, "cuda: cannot allocate Omni state"); return false; }
     struct { void **p; size_t bytes; } want[] = {
         {(void **)&s->logits, (size_t)OMNI_CHUNK * OMNI_E * 4},
+        {(void **)&s->logits_low, (size_t)OMNI_CHUNK * OMNI_E * 4},
         {(void **)&s->ids, (size_t)OMNI_CHUNK * OMNI_TOP * 4},
         {(void **)&s->weights, (size_t)OMNI_CHUNK * OMNI_TOP * 4},
         {(void **)&s->flag_rows, (size_t)OMNI_CHUNK * 4},
@@ -333,6 +346,7 @@ bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen) {
     if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni pass failed: %s", cudaGetErrorString(e)); return false; }
     if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
     if (status & OMNI_ST_TIMEOUT) {
+        if (g->ep.world > 1) g->ep.need_sync = true;
         set_err(err, errlen, "cuda: a bounded device wait ran out in an Omni expert kernel (%s, status 0x%x)",
                 status & OMNI_ST_TIMEOUT_BARRIER ? "barrier between ranks" :
                 status & OMNI_ST_TIMEOUT_ARRIVAL ? "rows from other ranks did not arrive" : "pipeline barrier", status);
@@ -340,6 +354,11 @@ bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen) {
     }
     if (status & OMNI_ST_EP_OVERFLOW) { set_err(err, errlen, "cuda: more expert rows were routed to this rank than its Omni arena holds"); return false; }
     if (status & OMNI_ST_BAD_ID) { set_err(err, errlen, "cuda: expert id outside [0,128) reached the Omni permutation"); return false; }
+    if (status & OMNI_ST_ROUTER_EPS) {
+        set_err(err, errlen, "cuda: router accumulation error exceeded CLEF_OMNI_ROUTER_EPS (%g): raise it or set CLEF_OMNI_ROUTER_EXACT=1",
+                (double)g->router_eps);
+        return false;
+    }
     if (status) { set_err(err, errlen, "cuda: nonfinite Omni attention or router values"); return false; }
     g->trace_valid = g->trace != NULL;
     return true;
@@ -385,6 +404,37 @@ bool clef_omni_trace_reserve(clef_gpu *g, int T, int layers, int rows, bool enab
     return true;
 }
 
+/* A captured row is usable when every logit pair is finite and every selected id and weight
+ * is in range; the file is only created once all rows passed (clef_metal_omni.m:105-113). */
+static const char *route_row_defect(const omni_route_row *r) {
+    for (int e = 0; e < OMNI_E; e++)
+        if (!isfinite(r->logits[e]) || !isfinite(r->low[e])) return "nonfinite captured Omni router logits";
+    for (int k = 0; k < OMNI_TOP; k++)
+        if (r->ids[k] < 0 || r->ids[k] >= OMNI_E || !isfinite(r->weights[k])) return "invalid captured Omni routes";
+    return NULL;
+}
+
+/* One JSON line: {"layer","token","logits":[128 x hi+low, %.17g],"ids":[8],"weights":[8 x %.9g],
+ * "margin": 8th - 9th highest logit} -- the schema tests/compare_omni_routes.py:37-64 reads. */
+static void route_row_print(FILE *f, int layer, int token, const omni_route_row *r) {
+    double v[OMNI_E], best[OMNI_TOP + 1];
+    bool used[OMNI_E] = {false};
+    for (int e = 0; e < OMNI_E; e++) v[e] = (double)r->logits[e] + (double)r->low[e];
+    for (int k = 0; k <= OMNI_TOP; k++) {            /* the nine highest values by repeated selection */
+        int at = -1;
+        for (int e = 0; e < OMNI_E; e++) if (!used[e] && (at < 0 || v[e] > v[at])) at = e;
+        used[at] = true;
+        best[k] = v[at];
+    }
+    fprintf(f, "{\"layer\":%d,\"token\":%d,\"logits\":[", layer, token);
+    for (int e = 0; e < OMNI_E; e++) fprintf(f, e ? ",%.17g" : "%.17g", v[e]);
+    fputs("],\"ids\":[", f);
+    for (int k = 0; k < OMNI_TOP; k++) fprintf(f, k ? ",%d" : "%d", r->ids[k]);
+    fputs("],\"weights\":[", f);
+    for (int k = 0; k < OMNI_TOP; k++) fprintf(f, k ? ",%.9g" : "%.9g", r->weights[k]);
+    fprintf(f, "],\"margin\":%.17g}\n", best[OMNI_TOP - 1] - best[OMNI_TOP]);
+}
+
 bool clef_gpu_dump_routes(clef_gpu *g, const char *path, char *err, size_t errlen) {
     if (!g || !g->omni || !g->trace || !g->trace_rows || !g->trace_valid) {
         set_err(err, errlen, "no captured Omni routes");
@@ -394,44 +444,22 @@ bool clef_gpu_dump_routes(clef_gpu *g, const char *path, char *err, size_t errle
     const size_t n = (size_t)g->trace_layers * g->trace_rows;
     omni_route_row *rows = malloc(n * sizeof *rows);
     if (!rows) { set_err(err, errlen, "cannot allocate Omni route dump"); return false; }
+    const char *defect = NULL;
     if (cudaMemcpy(rows, g->trace, n * sizeof *rows, cudaMemcpyDeviceToHost) != cudaSuccess) {
         cudaGetLastError();
-        free(rows);
-        set_err(err, errlen, "cannot read captured Omni routes");
-        return false;
+        defect = "cannot read captured Omni routes";
     }
-    /* Validate before creating output (clef_metal_omni.m:105-113). */
-    for (size_t i = 0; i < n; i++) {
-        for (int j = 0; j < OMNI_E; j++) if (!isfinite(rows[i].logits[j]) || !isfinite(rows[i].low[j])) {
-            free(rows); set_err(err, errlen, "nonfinite captured Omni router logits"); return false;
-        }
-        for (int j = 0; j < OMNI_TOP; j++) if (rows[i].ids[j] < 0 || rows[i].ids[j] >= OMNI_E || !isfinite(rows[i].weights[j])) {
-            free(rows); set_err(err, errlen, "invalid captured Omni routes"); return false;
-        }
-    }
+    for (size_t i = 0; i < n && !defect; i++) defect = route_row_defect(rows + i);
+    if (defect) { free(rows); set_err(err, errlen, "%s", defect); return false; }
     FILE *f = fopen(path, "w");
     if (!f) { free(rows); set_err(err, errlen, "cannot open Omni route dump: %s", path); return false; }
-    for (int l = 0; l < g->trace_layers; l++) for (int t = 0; t < g->trace_rows; t++) {
-        const omni_route_row *r = rows + (size_t)l * g->trace_rows + t;
-        double top[OMNI_TOP + 1];
-        for (int j = 0; j <= OMNI_TOP; j++) top[j] = -INFINITY;
-        for (int e = 0; e < OMNI_E; e++) {
-            double v = (double)r->logits[e] + r->low[e];
-            for (int j = 0; j <= OMNI_TOP; j++) if (v > top[j]) { double old = top[j]; top[j] = v; v = old; }
-        }
-        fprintf(f, "{\"layer\":%d,\"token\":%d,\"logits\":[", l, g->trace_first + t);
-        for (int j = 0; j < OMNI_E; j++) fprintf(f, "%s%.17g", j ? "," : "", (double)r->logits[j] + r->low[j]);
-        fputs("],\"ids\":[", f);
-        for (int j = 0; j < OMNI_TOP; j++) fprintf(f, "%s%d", j ? "," : "", r->ids[j]);
-        fputs("],\"weights\":[", f);
-        for (int j = 0; j < OMNI_TOP; j++) fprintf(f, "%s%.9g", j ? "," : "", r->weights[j]);
-        fprintf(f, "],\"margin\":%.17g}\n", top[OMNI_TOP - 1] - top[OMNI_TOP]);
-    }
-    bool ok = !ferror(f);
-    if (fclose(f)) ok = false;
+    for (size_t i = 0; i < n; i++)
+        route_row_print(f, (int)(i / (size_t)g->trace_rows), g->trace_first + (int)(i % (size_t)g->trace_rows), rows + i);
+    const bool wrote = !ferror(f);
+    const bool closed = fclose(f) == 0;
     free(rows);
-    if (!ok) set_err(err, errlen, "cannot write Omni route dump: %s", path);
-    return ok;
+    if (!wrote || !closed) { set_err(err, errlen, "cannot write Omni route dump: %s", path); return false; }
+    return true;
 }
 
 /* ---------------------------------------------------------------- weights */
@@ -507,6 +535,9 @@ static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int row
     bool fused = false;
     *have_counts = false;
     if (!launched(g, "flag reset", cudaMemsetAsync(s->n_flag, 0, 4, g->stream))) return false;
+    /* the remainders of the exact logits are only read by route capture */
+    float *low = g->trace ? s->logits_low : NULL;
+    if (low && !launched(g, "capture reset", cudaMemsetAsync(low, 0, (size_t)rows * OMNI_E * 4, g->stream))) return false;
     if (g->router_impl == 0) {
         CUtensorMap tm_x;
         if (!make_map(g, &tm_x, xn, (uint64_t)rows, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
@@ -525,7 +556,7 @@ static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int row
         if (!launched(g, "route", omni_launch_select(s->logits, rows, g->router_eps, g->router_exact, s->ids, s->weights,
                                                      s->flag_rows, s->n_flag, s->status, g->stream))) return false;
     }
-    if (!launched(g, "router exact pass", omni_launch_recheck(fused ? s->sort.segcount : NULL, xn, L->router, L->bias, s->logits, s->flag_rows,
+    if (!launched(g, "router exact pass", omni_launch_recheck(fused ? s->sort.segcount : NULL, xn, L->router, L->bias, s->logits, low, s->flag_rows,
                                                               s->n_flag, rows, g->router_eps, s->ids, s->weights, s->status, g->stream))) return false;
     *have_counts = fused;
     return true;
@@ -583,11 +614,11 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
     /* with overlap the persistent expert kernels leave some SMs to the copy kernels */
     const int n_gemm = g->n_sm - (g->reserve_sms > 0 ? g->reserve_sms : overlap ? 16 : 0);
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, have_counts, g->stream))) return false;
-    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds, g->stream))) return false;
+    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds, g->ep.wait_ns, g->stream))) return false;
     if (!overlap) {
         if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->stream, g->ep.gate_wait, 0))) return false;
         if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, 0, g->n_sm, g->stream))) return false;
-        if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
+        if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->ep.wait_ns, g->stream))) return false;
         if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
         stage_mark(g, 2);
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, n_gemm == g->n_sm, n_gemm, g->stream))) return false;
@@ -615,7 +646,7 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
         if (!launched(g, "return join", cudaEventRecord(g->ep.ev_returned, g->ep.side))) return false;
         if (!launched(g, "return join", cudaStreamWaitEvent(g->stream, g->ep.ev_returned, 0))) return false;
     }
-    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, 0, g->stream))) return false;
+    if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->ep.wait_ns, g->stream))) return false;
     if (g->wait_residual && !launched(g, "residual upload join", cudaStreamWaitEvent(g->stream, g->residual_uploaded, 0))) return false;
     if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
     stage_mark(g, 5);
@@ -641,6 +672,10 @@ static bool encode_chunks(clef_gpu *g, int layer, const void *xn, float *x, int 
         return false;
     }
     if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    if (g->ep.world > 1 && g->ep.need_sync) {
+        set_err(err, errlen, "cuda: an expert-parallel Omni pass failed on this rank; realign the ranks with clef_omni_ep_sync first");
+        return false;
+    }
     if (g->ep.world > 1 && T > OMNI_CHUNK) {
         set_err(err, errlen, "cuda: expert-parallel Omni passes take at most %d tokens per rank", OMNI_CHUNK);
         return false;
@@ -658,12 +693,16 @@ static bool encode_chunks(clef_gpu *g, int layer, const void *xn, float *x, int 
                                                                    rows, g->xnorm, g->stream));
         if (ok) ok = run_router(g, L, xn_c, rows, &have_counts);
         if (ok && g->trace && layer < g->trace_layers && start + rows > g->trace_first)
-            ok = launched(g, "route capture", omni_launch_trace(s->logits, s->ids, s->weights, rows, start, g->trace_first,
+            ok = launched(g, "route capture", omni_launch_trace(s->logits, s->logits_low, s->ids, s->weights, rows, start, g->trace_first,
                                                                 g->trace_rows, layer, g->trace, g->stream));
         stage_mark(g, 1);
         if (ok) ok = g->ep.world > 1 ? run_experts_ep(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows, have_counts)
                                      : run_experts(g, L, xn_c, s->ids, s->weights, x + (size_t)start * OMNI_H, rows, have_counts);
-        if (!ok) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+        if (!ok) {
+            if (g->ep.world > 1) g->ep.need_sync = true;     /* this rank launched fewer barriers than its peers */
+            set_err(err, errlen, "%s", g->fail_msg);
+            return false;
+        }
         book_profile(g);
         g->last_T = rows;
     }
@@ -715,6 +754,7 @@ bool clef_omni_encode_norm_moe(clef_gpu *g, int layer, float *x, int T, int n_se
 
 bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *x_host, int T, int n_seq,
                             const int32_t *seq_bounds, char *err, size_t errlen) {
+    if (err && errlen) err[0] = 0;
     if (!check_pass(g, layer, true, err, errlen)) return false;
     if (!xn_host || !x_host || T <= 0) { set_err(err, errlen, "cuda: invalid Omni layer dispatch"); return false; }
     if ((size_t)T > g->stage_cap) {
@@ -897,6 +937,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "ep_overlap")) g->ep_overlap = value != 0;
+    else if (!strcmp(name, "ep_wait_ms")) { if (value < 0) return false; g->ep.wait_ns = (uint64_t)value * 1000000ull; }
     else if (!strcmp(name, "dependent_launch")) omni_set_dependent_launch(value != 0);
     else if (!strcmp(name, "fused_router")) g->fused_router = value != 0;
     else if (!strcmp(name, "fused_gather")) g->fused_gather = value != 0;
@@ -935,7 +976,8 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
     int32_t *n_local = dev_alloc(g, 256);
     int32_t *need = dev_alloc(g, (size_t)OMNI_E * 4);
     int32_t *ret_bounds = dev_alloc(g, 256);
-    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && ret_bounds;
+    uint32_t *sync_result = dev_alloc(g, 256);
+    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && ret_bounds && sync_result;
     if (ok && !g->ep.side) ok = cudaStreamCreateWithFlags(&g->ep.side, cudaStreamNonBlocking) == cudaSuccess &&
                                 cudaEventCreateWithFlags(&g->ep.ev_planned, cudaEventDisableTiming) == cudaSuccess &&
                                 cudaEventCreateWithFlags(&g->ep.ev_dispatched, cudaEventDisableTiming) == cudaSuccess &&
@@ -949,13 +991,14 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
                  cudaStreamSynchronize(g->stream) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
-        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, ret_bounds};
+        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, ret_bounds, sync_result};
         for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
         set_err(err, errlen, "cuda: cannot allocate Omni expert-parallel buffers (previous buffers kept)");
         return false;
     }
     g->ep.dret = dret; g->ep.rowinfo = rowinfo; g->ep.counts = counts; g->ep.flags = flags;
     g->ep.send_base = send_base; g->ep.n_local_rows = n_local; g->ep.need = need; g->ep.ret_bounds = ret_bounds;
+    g->ep.sync_result = sync_result;
     return true;
 }
 
@@ -1023,7 +1066,7 @@ bool clef_omni_ep_connect(clef_gpu *g, int rank, int world, const clef_omni_ipc_
         }
         ep_set_peer(&pe, r, buf);
     }
-    g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = true; g->ep.epoch = 0;
+    g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = true; g->ep.epoch = 0; g->ep.sync_count = 0; g->ep.need_sync = false;
     return true;
 }
 
@@ -1053,25 +1096,33 @@ bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *cons
         ep_set_peer(&pe, r, buf);
     }
     cudaSetDevice(g->device);
-    g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = false; g->ep.epoch = 0;
+    g->ep.peers = pe; g->ep.rank = rank; g->ep.world = world; g->ep.ipc = false; g->ep.epoch = 0; g->ep.sync_count = 0; g->ep.need_sync = false;
     return true;
 }
 
 bool clef_omni_ep_sync(clef_gpu *g, int timeout_ms, char *err, size_t errlen) {
     if (!g || !g->omni || g->ep.world < 2) { set_err(err, errlen, "cuda: Omni expert parallelism is not connected"); return false; }
     cudaSetDevice(g->device);
-    uint32_t status = 0;
-    const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
-    cudaError_t e = cudaMemsetAsync(g->omni->status, 0, 4, g->stream);
-    if (e == cudaSuccess) e = omni_launch_ep_barrier(&g->ep.peers, ++g->ep.epoch, g->omni->status, limit, g->stream);
+    uint32_t status = 0, agreed[2] = {0, 0};
+    const int ms = timeout_ms > 0 ? timeout_ms : 2000;
+    /* the attempt publishes sync_count + 1; only success keeps it (omni_ep.cu: ep_sync_kernel) */
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(g->omni->status, 0, 4, g->stream);
+    if (e == cudaSuccess) e = omni_launch_ep_sync(&g->ep.peers, g->ep.sync_count + 1, g->ep.epoch, g->omni->status, g->ep.sync_result,
+                                                  (uint64_t)ms * 1000000ull, g->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
     if (e == cudaSuccess) e = cudaMemcpy(&status, g->omni->status, 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && !status) e = cudaMemcpy(agreed, g->ep.sync_result, 8, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { set_err(err, errlen, "cuda: Omni rank barrier failed: %s", cudaGetErrorString(e)); return false; }
     if (status) {
         cudaMemset(g->omni->status, 0, 4);
-        set_err(err, errlen, "cuda: not every Omni rank reached the barrier within %d ms", timeout_ms > 0 ? timeout_ms : 2000);
+        set_err(err, errlen, "cuda: not every Omni rank reached the barrier within %d ms", ms);
         return false;
     }
+    g->ep.sync_count = agreed[0];
+    g->ep.epoch = agreed[1];
+    g->ep.need_sync = false;
+    g->failed = false;
     return true;
 }
 
@@ -1094,7 +1145,8 @@ void clef_omni_ep_disconnect(clef_gpu *g) {
     if (g->ep.ev_dispatched) cudaEventDestroy(g->ep.ev_dispatched);
     if (g->ep.ev_returned) cudaEventDestroy(g->ep.ev_returned);
     for (int i = 0; i < OMNI_EP_RET_GROUPS; i++) if (g->ep.ev_down[i]) cudaEventDestroy(g->ep.ev_down[i]);
-    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds};
+    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds,
+                   g->ep.sync_result};
     for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
     memset(&g->ep, 0, sizeof g->ep);
     cudaGetLastError();

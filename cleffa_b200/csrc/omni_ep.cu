@@ -16,7 +16,7 @@
 //            kernel finds it through `slots`.
 //
 // Cross-GPU ordering uses one monotonically increasing epoch per barrier and system-scope
-// release/acquire on flag words; every spin is bounded (1 s) and reports OMNI_ST_TIMEOUT
+// release/acquire on flag words; every spin is bounded (2 s unless the host sets another limit) and reports OMNI_ST_TIMEOUT
 // through the status word instead of hanging.  No TMA or multicast touches peer memory: remote
 // rows land in local HBM first and the GEMM kernels read them from there.
 #include <cuda_bf16.h>
@@ -72,10 +72,45 @@ __global__ void __launch_bounds__(128) ep_barrier_kernel(omni_ep_peers pe, uint3
     flag_barrier(pe, epoch, status, limit_ns ? limit_ns : SPIN_LIMIT_NS);
 }
 
+// Realignment of the ranks (clef_omni_ep_sync).  The barrier epochs are host counters that
+// advance with every barrier a rank launches, so a rank whose pass failed on the host part-way
+// is behind its peers from then on.  This barrier does not use them: every rank publishes the
+// number of successful syncs it has seen plus one (`count`) and its current epoch, waits until
+// every peer's count has reached its own, and then all adopt the largest epoch and the largest
+// count they read.  A rank that waited alone keeps its old count on the host, so that its next
+// attempt publishes the same number again and meets the others there.
+__global__ void __launch_bounds__(32) ep_sync_kernel(omni_ep_peers pe, uint32_t count, uint32_t epoch, uint32_t *status,
+                                                     uint32_t *result, uint64_t limit_ns) {
+    const int t = threadIdx.x;
+    __threadfence_system();
+    if (t < pe.world) {
+        st_release_sys(pe.flags[t] + OMNI_EP_SYNC_WORD + OMNI_EP_MAX + pe.rank, epoch);
+        st_release_sys(pe.flags[t] + OMNI_EP_SYNC_WORD + pe.rank, count);
+    }
+    uint32_t c = count, e = epoch;
+    bool ok = true;
+    if (t < pe.world) {
+        const uint32_t *mine = pe.flags[pe.rank] + OMNI_EP_SYNC_WORD;
+        const uint64_t t0 = now_ns();
+        while ((int32_t)((c = ld_acquire_sys(mine + t)) - count) < 0) {
+            if (now_ns() - t0 > limit_ns) { atomicOr(status, OMNI_ST_TIMEOUT | OMNI_ST_TIMEOUT_BARRIER); ok = false; break; }
+        }
+        e = ld_acquire_sys(mine + OMNI_EP_MAX + t);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const uint32_t oc = __shfl_xor_sync(0xffffffffu, c, s), oe = __shfl_xor_sync(0xffffffffu, e, s);
+        if ((int32_t)(oc - c) > 0) c = oc;
+        if ((int32_t)(oe - e) > 0) e = oe;
+    }
+    if (t == 0 && ok) { result[0] = c; result[1] = e; }
+}
+
 // Publish my counts, barrier, then plan.  One block of 128 threads, thread e = expert e.
 __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint32_t epoch, omni_sort_state st,
                                                          int32_t *send_base, int32_t *n_local_rows, int32_t *need,
-                                                         int32_t *ret_bounds) {
+                                                         int32_t *ret_bounds, uint64_t limit_ns) {
     __shared__ int tot[OMNI_E], scan[OMNI_E], tiles[OMNI_E];
     const int e = threadIdx.x;
     const int G = pe.world, EL = OMNI_E / G;
@@ -83,7 +118,7 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
     for (int p = 0; p < G; p++) pe.counts[p][pe.rank * OMNI_E + e] = mine;
     // arrival counters of this rank's experts start at zero; peers add to them only after the barrier
     pe.flags[pe.rank][OMNI_EP_READY_WORD + e] = 0;
-    flag_barrier(pe, epoch, st.status);
+    flag_barrier(pe, epoch, st.status, limit_ns);
     // table[s][e] = rows rank s routes to expert e
     const int32_t *table = pe.counts[pe.rank];
     int total = 0, before_me = 0;
@@ -94,6 +129,14 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
     }
     tot[e] = total;
     __syncthreads();
+    // Every rank holds the same table, so every rank can see an owner whose buffers would not
+    // hold what is routed to it: the senders skip those rows, the owner returns nothing, and
+    // each rank's own status word says so (its combine would otherwise read rows of an earlier pass).
+    if (e < G) {
+        int to_owner = 0;
+        for (int o = e * EL; o < (e + 1) * EL; o++) to_owner += tot[o];
+        if (to_owner > OMNI_ROWS) atomicOr(st.status, OMNI_ST_EP_OVERFLOW);
+    }
     // base of expert e inside its owner's buffer: totals of the owner's earlier experts
     const int owner = e / EL, first = owner * EL;
     int base = 0;
@@ -210,14 +253,20 @@ __global__ void __launch_bounds__(256) ep_return_kernel(omni_ep_peers pe, const 
 extern "C" {
 
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, cudaStream_t s) {
-    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, ret_bounds);
+                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, uint64_t limit_ns, cudaStream_t s) {
+    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, ret_bounds, limit_ns ? limit_ns : SPIN_LIMIT_NS);
     return cudaGetLastError();
 }
 
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
                                    cudaStream_t s) {
     ep_barrier_kernel<<<1, 128, 0, s>>>(*pe, epoch, status, limit_ns);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_ep_sync(const omni_ep_peers *pe, uint32_t count, uint32_t epoch, uint32_t *status, uint32_t *result,
+                                uint64_t limit_ns, cudaStream_t s) {
+    ep_sync_kernel<<<1, 32, 0, s>>>(*pe, count, epoch, status, result, limit_ns ? limit_ns : SPIN_LIMIT_NS);
     return cudaGetLastError();
 }
 

@@ -115,39 +115,63 @@ __device__ __forceinline__ double exact_dot(const XRow &x, const __nv_bfloat16 *
 }
 
 // Re-evaluates one flagged row with four warps (128 threads): exact logits for every expert
-// that can still reach the top eight (approximate logit within 2*eps of the approximate 8th),
-// spread over the warps, then the final order by warp 0.  `sync` is a barrier over exactly
-// these 128 threads; `exact_s` is their scratch of 128 doubles.  With `segcount` given (expert
-// counts per 256-assignment segment, taken from the ids being replaced), the counts follow
-// the ids that change.
+// that can still reach the top eight (approximate logit within twice the row's error bound of
+// the approximate 8th) and for the approximate 9th, spread over the warps, then the final order
+// by warp 0.  `sync` is a barrier over exactly these 128 threads; `exact_s` is their scratch of
+// 128 doubles.  With `segcount` given (expert counts per 256-assignment segment, taken from the
+// ids being replaced), the counts follow the ids that change.
+//
+// What the pass learns is written back: every logit it evaluated is replaced by its exact value
+// as a float pair (hi into `logits`, the remainder into `low` when given), so that a capture of
+// the row shows logits that agree with the ids chosen from them (clef_metal_omni.m:118-130
+// prints hi+lo).  And the assumed error bound is checked on the way: an approximate logit
+// further than the bound from its exact value raises OMNI_ST_ROUTER_EPS.
 template <typename Sync>
 __device__ __forceinline__ void recheck_row(const __nv_bfloat16 *__restrict__ xn, const __nv_bfloat16 *__restrict__ w,
-                                            const float *__restrict__ bias, const float *__restrict__ logits, long row,
-                                            float eps, int32_t *__restrict__ ids, float *__restrict__ weights,
-                                            int32_t *__restrict__ segcount, double *exact_s, int lane, int warp, Sync sync) {
+                                            const float *__restrict__ bias, float *__restrict__ logits,
+                                            float *__restrict__ low, long row, float eps, int32_t *__restrict__ ids,
+                                            float *__restrict__ weights, int32_t *__restrict__ segcount,
+                                            uint32_t *__restrict__ status, double *exact_s, int lane, int warp, Sync sync) {
     exact_s[warp * 32 + lane] = -CUDART_INF;
     double val[4], approx[4];
+    float max_abs = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; j++) approx[j] = val[j] = (double)logits[row * OMNI_E + lane + 32 * j];
+    for (int j = 0; j < 4; j++) {
+        const float f = logits[row * OMNI_E + lane + 32 * j];
+        approx[j] = val[j] = (double)f;
+        max_abs = fmaxf(max_abs, fabsf(f));
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) max_abs = fmaxf(max_abs, __shfl_xor_sync(FULL, max_abs, s));
+    const double bound = (double)omni_row_eps(eps, max_abs);
     const XRow x = load_xrow(xn, row, lane);              // in flight while the threshold is found
-    double top_v[8]; int top_id[8];
-    warp_topn<8>(val, lane, top_v, top_id);               // every warp finds the same threshold
-    const double floor_v = top_v[7] - 2.0 * (double)eps;
+    double top_v[9]; int top_id[9];
+    warp_topn<9>(val, lane, top_v, top_id);               // every warp finds the same threshold
+    const double floor_v = fmin(top_v[7] - 2.0 * bound, top_v[8]);
     sync();
     int c = 0;
+    bool off = false;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         unsigned m = __ballot_sync(FULL, approx[j] >= floor_v);
         while (m) {
             const int src = __ffs(m) - 1;
             m &= m - 1;
+            const double a = __shfl_sync(FULL, approx[j], src);
             if ((c++ & 3) != warp) continue;              // candidates round-robin over the warps
             const int e = src + 32 * j;
             double v = exact_dot(x, w + (long)e * OMNI_H, lane);
             if (bias) v += (double)bias[e];
-            if (lane == 0) exact_s[e] = v;
+            off |= fabs(v - a) > bound;
+            if (lane == 0) {
+                exact_s[e] = v;
+                const float hi = (float)v;
+                logits[row * OMNI_E + e] = hi;
+                if (low) low[row * OMNI_E + e] = (float)(v - (double)hi);
+            }
         }
     }
+    if (off && lane == 0) atomicOr(status, OMNI_ST_ROUTER_EPS);
     sync();
     if (warp == 0) {
         double exact[4];

@@ -24,7 +24,22 @@ enum {
 /* status word bits (clef_omni_complete) */
 enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_ST_EP_OVERFLOW = 32u,
        /* which bounded wait ran out (set together with OMNI_ST_TIMEOUT) */
-       OMNI_ST_TIMEOUT_BARRIER = 64u, OMNI_ST_TIMEOUT_ARRIVAL = 128u };
+       OMNI_ST_TIMEOUT_BARRIER = 64u, OMNI_ST_TIMEOUT_ARRIVAL = 128u,
+       /* the exact pass found a tensor-core logit further from its exact value than the bound the
+        * near-tie test assumes: rows that were not re-decided may carry a wrong order */
+       OMNI_ST_ROUTER_EPS = 256u };
+
+/* Bound assumed on |tensor-core logit - exact logit| for one row: `eps` for rows whose largest
+ * |logit| is at most OMNI_EPS_REF_SCALE, growing in proportion beyond that (the FP32 accumulation
+ * error of a 2048-term sum scales with the magnitude of its partial sums). */
+#define OMNI_EPS_REF_SCALE 4.0f
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+static inline float omni_row_eps(float eps, float max_abs_logit) {
+    const float s = max_abs_logit * (1.0f / OMNI_EPS_REF_SCALE);
+    return s > 1.0f ? eps * s : eps;
+}
 
 /* One token tile of one expert: rows [row0, row0+len) of the permuted buffers. */
 /* group = index of the expert's first tile | (its tile count << 16) */
@@ -54,7 +69,9 @@ typedef struct {
     uint32_t *flags[OMNI_EP_MAX];   /* [EP_MAX] barrier epochs, written by the peers; from word
                                        OMNI_EP_READY_WORD on: rows arrived per local expert       */
 } omni_ep_peers;
-enum { OMNI_EP_READY_WORD = 64, OMNI_EP_FLAG_WORDS = 64 + 128 };
+/* flag words: [0, EP_MAX) barrier epochs; [SYNC_WORD, +EP_MAX) sync counts, then EP_MAX epochs
+ * published for realignment; from READY_WORD on, rows arrived per local expert group */
+enum { OMNI_EP_SYNC_WORD = 16, OMNI_EP_READY_WORD = 64, OMNI_EP_FLAG_WORDS = 64 + 128 };
 /* local experts are announced as "arrived" in groups of this many (four groups per rank) */
 #ifdef __CUDACC__
 __host__ __device__
@@ -67,8 +84,10 @@ cudaError_t omni_launch_router_simple(const void *xn, const void *router, const 
                                       float *logits, cudaStream_t s);
 cudaError_t omni_launch_select(const float *logits, int T, float eps, int exact_all, int32_t *ids, float *weights,
                                int32_t *flag_rows, int32_t *n_flag, uint32_t *status, cudaStream_t s);
-cudaError_t omni_launch_recheck(int32_t *segcount, const void *xn, const void *router, const float *bias, const float *logits,
-                                const int32_t *flag_rows, const int32_t *n_flag, int T, float eps,
+/* logits: the approximate values on entry; on return every logit the exact pass evaluated holds
+ * (float)exact, and low (may be NULL) the remainder (float)(exact - hi) */
+cudaError_t omni_launch_recheck(int32_t *segcount, const void *xn, const void *router, const float *bias, float *logits,
+                                float *low, const int32_t *flag_rows, const int32_t *n_flag, int T, float eps,
                                 int32_t *ids, float *weights, uint32_t *status, cudaStream_t s);
 cudaError_t omni_launch_router_exact(const void *xn, const void *router, const float *bias, int T,
                                      double *logits, cudaStream_t s);
@@ -87,7 +106,7 @@ cudaError_t omni_launch_down_simple(const void *h, const void *down, const int32
                                     cudaStream_t s);
 cudaError_t omni_launch_fill_u32(void *p, uint32_t v, size_t words, cudaStream_t s);
 cudaError_t omni_launch_touch(const void *p, uint32_t *sink, cudaStream_t s);
-cudaError_t omni_launch_trace(const float *logits, const int32_t *ids, const float *weights, int rows, int start,
+cudaError_t omni_launch_trace(const float *logits, const float *low, const int32_t *ids, const float *weights, int rows, int start,
                               int first, int captured, int layer, void *trace, cudaStream_t s);
 
 /* the sort with its scratch in a static device array (no allocation); *max_rows = its limit */
@@ -125,9 +144,12 @@ int omni_dependent_launch_enabled(void);
 
 /* ---- expert parallel (omni_ep.cu) ---- */
 /* ret_bounds: [2][RET_GROUPS+1] tile bounds, then row bounds, of the groups the down product is launched in */
+/* limit_ns = 0 (here and below): the default bound of 2 s on the wait for the other ranks */
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, cudaStream_t s);
-/* limit_ns = 0: the default bound */
+                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, uint64_t limit_ns, cudaStream_t s);
+/* realignment barrier: result[0] = agreed sync count, result[1] = agreed epoch (written on success only) */
+cudaError_t omni_launch_ep_sync(const omni_ep_peers *pe, uint32_t count, uint32_t epoch, uint32_t *status, uint32_t *result,
+                                uint64_t limit_ns, cudaStream_t s);
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
                                    cudaStream_t s);
 cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,

@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(128) router_simple_kernel(const __nv_bfloat16 
 
 // ------------------------------------------------------------------ selection from stored logits
 // One warp per token.  Rows whose ranked logits are closer than 2*eps anywhere in the first
-// nine (or every row when exact_all) are appended to flag_rows for the exact pass.
+// nine (or every row when exact_all) are appended to flag_rows for the exact pass; eps is the
+// row's error bound (omni_row_eps).
 __global__ void __launch_bounds__(256) select_kernel(const float *__restrict__ logits, int T, float eps, int exact_all,
                                                      int32_t *__restrict__ ids, float *__restrict__ weights,
                                                      int32_t *__restrict__ flag_rows, int32_t *__restrict__ n_flag,
@@ -60,18 +61,23 @@ __global__ void __launch_bounds__(256) select_kernel(const float *__restrict__ l
     if (row >= T) return;
     double val[4];
     bool bad = false;
+    float max_abs = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const float f = logits[row * OMNI_E + lane + 32 * j];
         bad |= !isfinite(f);
         val[j] = (double)f;
+        max_abs = fmaxf(max_abs, fabsf(f));
     }
     if (__any_sync(FULL, bad)) { write_fallback(lane, ids, weights, row, status); return; }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) max_abs = fmaxf(max_abs, __shfl_xor_sync(FULL, max_abs, s));
+    const double bound = (double)omni_row_eps(eps, max_abs);
     double top_v[9]; int top_id[9];
     warp_topn<9>(val, lane, top_v, top_id);
     bool close = exact_all != 0;
 #pragma unroll
-    for (int k = 0; k < 8; k++) close |= (top_v[k] - top_v[k + 1]) < 2.0 * (double)eps;
+    for (int k = 0; k < 8; k++) close |= (top_v[k] - top_v[k + 1]) < 2.0 * bound;
     write_selection(top_v, top_id, lane, ids, weights, row);
     if (close && lane == 0) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
 }
@@ -79,11 +85,11 @@ __global__ void __launch_bounds__(256) select_kernel(const float *__restrict__ l
 // One block (four warps) per flagged row.
 __global__ void __launch_bounds__(128) recheck_kernel(const __nv_bfloat16 *__restrict__ xn,
                                                       const __nv_bfloat16 *__restrict__ w,
-                                                      const float *__restrict__ bias, const float *__restrict__ logits,
-                                                      const int32_t *__restrict__ flag_rows,
+                                                      const float *__restrict__ bias, float *__restrict__ logits,
+                                                      float *__restrict__ low, const int32_t *__restrict__ flag_rows,
                                                       const int32_t *__restrict__ n_flag, int T, float eps,
                                                       int32_t *__restrict__ ids, float *__restrict__ weights,
-                                                      int32_t *__restrict__ segcount) {
+                                                      int32_t *__restrict__ segcount, uint32_t *__restrict__ status) {
     __shared__ double exact_s[OMNI_E];
     dep_wait();
     dep_launch();
@@ -91,7 +97,7 @@ __global__ void __launch_bounds__(128) recheck_kernel(const __nv_bfloat16 *__res
     int n = *n_flag;
     if (n > T) n = T;
     for (int f = blockIdx.x; f < n; f += gridDim.x)
-        recheck_row(xn, w, bias, logits, flag_rows[f], eps, ids, weights, segcount, exact_s, lane, warp, [] { __syncthreads(); });
+        recheck_row(xn, w, bias, logits, low, flag_rows[f], eps, ids, weights, segcount, status, exact_s, lane, warp, [] { __syncthreads(); });
 }
 
 // Exact logits for every (token, expert): tests only (tests/test_omni_router.m).
@@ -434,10 +440,11 @@ __global__ void touch_kernel(const uint32_t *p, uint32_t *sink) {
     if (p[0] == 0x7fc00001u && sink) *sink = 1;    // read-only touch (clef_metal_omni.m:138-147)
 }
 
-// Layer-major capture rows: logits[128], low[128] (zero here), ids[8], weights[8] = 1088 bytes.
+// Layer-major capture rows: logits[128], low[128], ids[8], weights[8] = 1088 bytes.  `low` is the
+// remainder of the logits the exact pass evaluated and zero for the others.
 struct TraceRow { float logits[OMNI_E], low[OMNI_E]; int32_t ids[OMNI_TOP]; float weights[OMNI_TOP]; };
 
-__global__ void trace_kernel(const float *__restrict__ logits, const int32_t *__restrict__ ids,
+__global__ void trace_kernel(const float *__restrict__ logits, const float *__restrict__ low, const int32_t *__restrict__ ids,
                              const float *__restrict__ weights, int rows, int start, int first, int captured, int layer,
                              TraceRow *__restrict__ out) {
     const int p = blockIdx.x;                 // chunk-local row
@@ -446,7 +453,7 @@ __global__ void trace_kernel(const float *__restrict__ logits, const int32_t *__
     TraceRow &r = out[(long)layer * captured + row];
     const int e = threadIdx.x;
     r.logits[e] = logits[(long)p * OMNI_E + e];
-    r.low[e] = 0.f;
+    r.low[e] = low[(long)p * OMNI_E + e];
     if (e < 8) { r.ids[e] = ids[(long)p * 8 + e]; r.weights[e] = weights[(long)p * 8 + e]; }
 }
 
@@ -472,13 +479,12 @@ cudaError_t omni_launch_select(const float *logits, int T, float eps, int exact_
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_recheck(int32_t *segcount, const void *xn, const void *router, const float *bias, const float *logits,
-                                const int32_t *flag_rows, const int32_t *n_flag, int T, float eps, int32_t *ids,
+cudaError_t omni_launch_recheck(int32_t *segcount, const void *xn, const void *router, const float *bias, float *logits,
+                                float *low, const int32_t *flag_rows, const int32_t *n_flag, int T, float eps, int32_t *ids,
                                 float *weights, uint32_t *status, cudaStream_t s) {
-    (void)status;
     int blocks = T < 148 * 8 ? T : 148 * 8;
     return omni_launch_chain(recheck_kernel, dim3(blocks), dim3(128), 0, s, (const __nv_bfloat16 *)xn, (const __nv_bfloat16 *)router, bias, logits,
-                             flag_rows, n_flag, T, eps, ids, weights, segcount);
+                             low, flag_rows, n_flag, T, eps, ids, weights, segcount, status);
 }
 
 cudaError_t omni_launch_router_exact(const void *xn, const void *router, const float *bias, int T, double *logits,
@@ -547,9 +553,9 @@ cudaError_t omni_launch_touch(const void *p, uint32_t *sink, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-cudaError_t omni_launch_trace(const float *logits, const int32_t *ids, const float *weights, int rows, int start,
+cudaError_t omni_launch_trace(const float *logits, const float *low, const int32_t *ids, const float *weights, int rows, int start,
                               int first, int captured, int layer, void *trace, cudaStream_t s) {
-    trace_kernel<<<rows, OMNI_E, 0, s>>>(logits, ids, weights, rows, start, first, captured, layer, (TraceRow *)trace);
+    trace_kernel<<<rows, OMNI_E, 0, s>>>(logits, low, ids, weights, rows, start, first, captured, layer, (TraceRow *)trace);
     return cudaGetLastError();
 }
 
@@ -588,7 +594,9 @@ cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, i
     }
     NoAllocScratch *sc = g_noalloc_ptr[dev];
     if (!status) {
-        // the shared status word keeps whatever the previous call left: start it at zero
+        // No word of the caller's to report into: the bad-id bit then lands in the shared scratch
+        // word, which no entry point reads back, and the id is sorted as id & 127 (documented in
+        // the header).  The word keeps whatever the previous call left: start it at zero.
         e = cudaMemsetAsync(&sc->status, 0, sizeof(uint32_t), s);
         if (e != cudaSuccess) return e;
         status = &sc->status;

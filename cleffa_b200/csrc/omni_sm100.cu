@@ -777,9 +777,11 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     float *col = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
                     const int et = threadIdx.x - 128;
                     uint32_t key[OMNI_E];
+                    float max_abs = 0.f;
 #pragma unroll
                     for (int i = 0; i < OMNI_E; i++) {
                         col[i * 128 + et] = v[i];
+                        max_abs = fmaxf(max_abs, fabsf(v[i]));
                         const uint32_t u = __float_as_uint(v[i]);
                         const uint32_t ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
                         key[i] = (ord & ~127u) | (uint32_t)(127 - i);
@@ -792,8 +794,9 @@ router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     float tv[9]; int ti[9];
 #pragma unroll
                     for (int r = 0; r < 9; r++) { ti[r] = 127 - (int)(key[r] & 127u); tv[r] = col[ti[r] * 128 + et]; }
-                    // near-tie threshold: the assumed accumulation error plus what the borrowed key bits can hide
-                    const float thr = 2.f * eps + fmaxf(fabsf(tv[0]), fabsf(tv[8])) * 6.1035156e-5f;   // 2^-14
+                    // near-tie threshold: the row's assumed accumulation error (it grows with the
+                    // row's largest |logit|) plus what the borrowed key bits can hide
+                    const float thr = 2.f * omni_row_eps(eps, max_abs) + fmaxf(fabsf(tv[0]), fabsf(tv[8])) * 6.1035156e-5f;   // 2^-14
                     bool close = exact_all != 0;
 #pragma unroll
                     for (int k = 0; k < 8; k++) close |= (tv[k] - tv[k + 1]) < thr;

@@ -44,7 +44,8 @@ enum { CLEF_OMNI_H = 2048, CLEF_OMNI_F = 768, CLEF_OMNI_E = 128, CLEF_OMNI_TOP =
 
 /* Counterpart of clef_gpu_open (clef_engine.h:165; clef_metal.m:113) for this path: selects
  * `device`, adopts `stream` (a cudaStream_t; NULL creates a private non-blocking stream)
- * and reads the CLEF_* debug environment. */
+ * and reads the CLEF_* debug environment (CLEF_DEBUG_POISON, CLEF_PROFILE, CLEF_OMNI_ROUTER_EXACT,
+ * CLEF_OMNI_ROUTER_EPS, CLEF_DEBUG_OMNI_ALLOC_FAIL, CLEF_DEBUG_OMNI_LAUNCH_FAIL). */
 bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, size_t errlen);
 /* Counterpart of clef_gpu_close (clef_metal.m:241-247): frees arena, trace and owned weights. */
 void clef_cuda_omni_close(clef_gpu *g);
@@ -54,6 +55,15 @@ void clef_cuda_omni_close(clef_gpu *g);
  * made and leaves the previous state ("... (previous buffers kept)").  The arena size does
  * not depend on T. */
 bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err, size_t errlen);
+#ifdef CLEF_ENGINE_H
+/* For a caller that holds the reference's own clef_config (clef_engine.h:18-33, included before
+ * this header): the call of clef_metal.m:1148 with the same arguments. */
+static inline bool clef_omni_reserve_config(clef_gpu *g, const clef_config *c, int T, char *err, size_t errlen) {
+    clef_omni_config o = {0, 0, 0, 0, 0};
+    if (c) { o.n_layer = c->n_layer; o.H = c->H; o.ffn = c->ffn; o.n_expert = c->n_expert; o.n_expert_used = c->n_expert_used; }
+    return clef_omni_reserve(g, c ? &o : (const clef_omni_config *)0, T, err, errlen);
+}
+#endif
 /* clef_omni_free (clef_metal_omni.m:71-74). */
 void clef_omni_free(clef_gpu *g);
 /* clef_omni_begin (clef_metal_omni.m:149-159): clears the status word; with debug poison on,
@@ -63,7 +73,10 @@ void clef_omni_begin(clef_gpu *g);
  * nonzero status word as an error.  Bit 0: nonfinite router values (clef.metal:2364).
  * Bit 3: an expert id outside [0,128) reached the permutation.  Bit 4: a bounded device-side
  * wait ran out.  Bit 5: more rows were routed to one rank than its buffers hold (expert
- * parallel only).  A failed launch or stream error is reported here too. */
+ * parallel only).  Bit 8: the exact router pass met a tensor-core logit further from its exact
+ * value than the assumed bound (CLEF_OMNI_ROUTER_EPS, scaled by the row's largest |logit| / 4
+ * when that exceeds 1), so rows it did not re-decide cannot be trusted.  A failed launch or
+ * stream error is reported here too. */
 bool clef_omni_complete(clef_gpu *g, char *err, size_t errlen);
 /* clef_omni_keepalive (clef_metal_omni.m:138-147): read-only touch of every arena buffer. */
 void clef_omni_keepalive(clef_gpu *g);
@@ -73,7 +86,10 @@ void clef_omni_keepalive(clef_gpu *g);
  * of every layer. */
 bool clef_omni_trace_reserve(clef_gpu *g, int T, int layers, int rows, bool enabled, char *err, size_t errlen);
 /* clef_gpu_dump_routes (clef_metal_omni.m:98-136): validates, then writes one JSON line per
- * (layer, token): logits[128] (%.17g), ids[8], weights[8] (%.9g), margin = 8th - 9th logit. */
+ * (layer, token): logits[128] (%.17g), ids[8], weights[8] (%.9g), margin = 8th - 9th logit.
+ * A logit is printed as hi + low: the tensor-core value with low = 0, or, for every logit the
+ * exact pass evaluated, its FP64 value as a float pair -- so the ids of a row always follow from
+ * the row's printed logits (tests/test_omni_routes.py:28-30). */
 bool clef_gpu_dump_routes(clef_gpu *g, const char *path, char *err, size_t errlen);
 
 /* ---- weights ---------------------------------------------------------------------- */
@@ -154,11 +170,17 @@ bool clef_omni_ep_connect(clef_gpu *g, int rank, int world, const clef_omni_ipc_
 /* same, for contexts that live in one process: peers[r] is rank r's context */
 bool clef_omni_ep_connect_local(clef_gpu *g, int rank, int world, clef_gpu *const *peers, char *err, size_t errlen);
 void clef_omni_ep_disconnect(clef_gpu *g);
-/* One barrier across the ranks on the context's stream, waited for on the host.  Every rank
- * calls it once after all ranks have connected (it also makes the first, slow touch of the
- * peers' memory happen here and not in the first pass) and may call it again to realign ranks.
- * Inside a pass every wait on another rank is bounded by 2 s; ranks that start a pass further
- * apart than that fail the pass with status bit 4. */
+/* One barrier across the ranks on the context's stream, waited for on the host (timeout_ms <= 0:
+ * 2 s).  Every rank calls it once after all ranks have connected (it also makes the first, slow
+ * touch of the peers' memory happen here and not in the first pass).  It is also how ranks get
+ * back in step: the ranks agree on a common barrier epoch here, whatever each one's was.  A
+ * pass that fails on one rank (a refused launch, a wait on the others that ran out) leaves that
+ * rank's context refusing further passes until this call has succeeded on every rank; a rank
+ * that waited alone may simply call again.  Inside a pass every wait on another rank is bounded
+ * (2 s, or option "ep_wait_ms"); ranks that start a pass further apart than that fail the pass
+ * with status bit 4.  Capacity: a pass is refused (status bit 5, on every rank) when more than
+ * 131072 expert rows from all ranks together are routed to the experts of one rank -- with
+ * evenly spread routing that is 16384 tokens per rank, with skewed routing fewer. */
 bool clef_omni_ep_sync(clef_gpu *g, int timeout_ms, char *err, size_t errlen);
 /* Overlap of transfers and expert products is the host's choice: drive two (or more) contexts
  * per GPU on separate streams, each with a share of the rank's tokens (micro-batches), all
@@ -198,8 +220,9 @@ bool clef_omni_stage_experts(clef_gpu *g, int layer, const void *xn, const int32
  * library image, so every GPU that loads the library carries it until the process exits.
  *   - at most CLEF_OMNI_NOALLOC_MAX_ROWS tokens per call; more is refused with a message;
  *   - ids, counts[128], offsets[129], rowmap[rows*8], slots[rows*8] are device pointers on the
- *     current device; status (device, one word, may be NULL) receives bit 3 when an expert id
- *     is out of range, as in clef_omni_complete; the caller clears it;
+ *     current device; status (device, one word) receives bit 3 when an expert id is out of
+ *     range, as in clef_omni_complete; the caller clears it.  status may be NULL, but then
+ *     nothing reports such an id: it is sorted as id & 127 and the call still returns true;
  *   - work is enqueued on `stream` (a cudaStream_t, NULL = default stream); nothing is waited for;
  *   - the first call on each device looks up the array's device address (one
  *     cudaGetSymbolAddress); make that first call outside any stream capture;
@@ -221,7 +244,8 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
  * FP64 logits), "router_eps" (bound on the tensor-core logit error, x1e-9), "gemm" 0 =
  * tcgen05 kernels, 1 = plain CUDA-core check kernels, "router" likewise, "profile" 0/1,
  * "ep_overlap" 0/1 (expert parallelism: run the transfers under the expert kernels instead of
- * between them; same results), "reserve_sms" N (the persistent expert kernels use all SMs but N, so that kernels of another
+ * between them; same results; must be the same on every rank, as it changes the number of barriers per pass),
+ * "ep_wait_ms" N (bound on each in-pass wait for other ranks, 0 = 2000), "reserve_sms" N (the persistent expert kernels use all SMs but N, so that kernels of another
  * context on the same GPU -- another micro-batch -- are not locked out while they run),
  * "fused_gather" 0/1 (default 1: the gate/up kernel fetches its token rows through the permutation
  * itself instead of reading a copy in expert order made by a separate kernel; same results),

@@ -1,4 +1,4 @@
-"""Host-side model of the expert-parallel bookkeeping (what omni_ep.cu computes on the device).
+"""Host-side model of the expert-parallel bookkeeping (what omni_ep.cu computes on the device); test infrastructure for test_ep_cpu.py.
 
 Experts are sharded in contiguous ranges of E/world per rank.  Every rank sorts its own
 assignments by expert (stable), then from the table of per-rank per-expert counts each rank

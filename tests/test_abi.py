@@ -14,6 +14,7 @@ ROOT = Path(__file__).resolve().parents[1]
 def declared_functions():
     text = (ROOT / "include" / "clef_cuda_omni.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"#ifdef CLEF_ENGINE_H.*?#endif", "", text, flags=re.S)    # inline adapter for the reference's clef_config
     return sorted(set(re.findall(r"\b(clef_[a-z0-9_]+)\s*\(", text)))
 
 
@@ -63,3 +64,32 @@ def test_open_without_a_gpu_fails_loudly():
         pytest.skip("this box has a GPU")
     with pytest.raises(omni.OmniError, match="cuda: "):
         omni.OmniBackend(0)
+
+
+def reference_dir():
+    import os
+    for cand in (os.environ.get("CLEF_REFERENCE_DIR"), "/root/reference"):
+        if cand and (Path(cand) / "clef_engine.h").exists():
+            return Path(cand)
+    return None
+
+
+@pytest.mark.skipif(reference_dir() is None, reason="no checkout of the reference engine (set CLEF_REFERENCE_DIR)")
+def test_integration_stub_builds_against_the_reference_headers(tmp_path, lib):
+    """tests/integration_stub.c is the binding INTEGRATION.md shows.  It is compiled with the
+    reference's own clef_engine.h in front of this repository's header, so clef_config,
+    clef_layer_w and gguf_tensor (clef_engine.h:18-40, clef_gguf.h:31-39) are the real types,
+    and linked against the library so every call resolves."""
+    import subprocess
+    stub = ROOT / "tests" / "integration_stub.c"
+    md = (ROOT / "INTEGRATION.md").read_text()
+    body = stub.read_text().split("*/", 1)[1].strip()
+    assert body in md, "INTEGRATION.md must show the stub that is compiled here"
+    main = tmp_path / "main.c"
+    main.write_text('#include <stdbool.h>\n#include <stddef.h>\nvoid cuda_backend_close(void);\n'
+                    'int main(int argc, char **argv) { (void)argv; if (argc > 99) cuda_backend_close(); return 0; }\n')
+    exe = tmp_path / "stub"
+    libdir = omni_build.LIB.parent
+    subprocess.run(["gcc", "-std=c11", "-D_GNU_SOURCE", "-Wall", "-Wextra", "-Werror", "-I", str(reference_dir()), "-I", str(ROOT / "include"),
+                    str(stub), str(main), "-L", str(libdir), "-lclef_cuda_omni", f"-Wl,-rpath,{libdir}", "-o", str(exe)], check=True)
+    subprocess.run([str(exe)], check=True)

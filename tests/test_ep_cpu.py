@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from cleffa_b200 import ep
+import ep_model as ep
 
 E, K, H = 128, 8, 16
 

@@ -42,7 +42,7 @@ def test_every_failing_allocation_leaves_the_previous_state():
                 n += 1
                 continue
             break
-        assert n == 20                        # 19 arena buffers
+        assert n == 21                        # 20 arena buffers
         b.set_option("alloc_fail_at", 0)
         assert b.arena_bytes() > 0
 
@@ -69,6 +69,18 @@ def test_failed_launch_surfaces_at_complete_and_next_pass_is_identical(bound0):
         assert torch.equal(run(), good)
 
 
+def check_route_rows(lines, first_token):
+    """The reference's own checks on a route dump (tests/test_omni_routes.py:21-31)."""
+    for i, row in enumerate(lines):
+        assert (row["layer"], row["token"]) == (0, first_token + i)
+        assert len(row["logits"]) == 128 and len(set(row["ids"])) == 8
+        assert all(math.isfinite(v) for v in row["logits"] + row["weights"])
+        assert abs(sum(row["weights"]) - 1) < 1e-6
+        order = sorted(range(128), key=lambda e: (-row["logits"][e], e))
+        assert row["ids"] == order[:8], (row["token"], row["ids"], order[:9])
+        assert row["margin"] == row["logits"][order[7]] - row["logits"][order[8]]
+
+
 def test_trace_reserve_and_dump(bound0, tmp_path):
     b = bound0
     T, rows = 300, 3
@@ -89,19 +101,76 @@ def test_trace_reserve_and_dump(bound0, tmp_path):
     lines = [json.loads(s) for s in path.read_text().splitlines()]
     assert len(lines) == rows
     ids = b.read("ids", T)
-    for i, row in enumerate(lines):          # tests/test_omni_routes.py:21-31
-        assert (row["layer"], row["token"]) == (0, T - rows + i)
-        assert len(row["logits"]) == 128 and len(set(row["ids"])) == 8
-        assert all(math.isfinite(v) for v in row["logits"] + row["weights"])
-        assert abs(sum(row["weights"]) - 1) < 1e-6
-        order = sorted(range(128), key=lambda e: (-row["logits"][e], e))
+    check_route_rows(lines, T - rows)
+    for i, row in enumerate(lines):
         assert row["ids"] == ids[T - rows + i].tolist()
-        assert abs(row["margin"] - (row["logits"][order[7]] - row["logits"][order[8]])) < 1e-5
     with pytest.raises(OmniError, match="cannot open"):
         b.dump_routes(tmp_path)               # a directory is not writable as a file
     b.trace_reserve(T, 1, rows, enabled=False)
     with pytest.raises(OmniError, match="no captured Omni routes"):
         b.dump_routes(path)
+
+
+@pytest.mark.parametrize("exact", [0, 1])
+def test_dumped_ids_follow_from_dumped_logits(bound0, weights0, tmp_path, exact):
+    """Rows the exact pass re-decided carry ids chosen from FP64 logits; the dump must show
+    logits (hi + low) from which exactly those ids follow, for every row of a capture large
+    enough to hold hundreds of re-decided rows (tests/test_omni_routes.py:28-30)."""
+    b = bound0
+    T = 2500
+    b.trace_reserve(T, 1, 0)                  # 0 = every row
+    b.set_option("router_exact", exact)
+    try:
+        x = orc.make_activations(43, T)
+        out = torch.zeros(T, 2048, device="cuda")
+        b.begin(); b.encode_moe(0, x.cuda(), out); b.complete()
+        assert int(b.read("rechecked")[0]) >= (T if exact else 100)
+        path = tmp_path / "routes.jsonl"
+        b.dump_routes(path)
+        lines = [json.loads(s) for s in path.read_text().splitlines()]
+        assert len(lines) == T
+        check_route_rows(lines, 0)
+        # and the dumped logits are the oracle's: exact rows to FP64 rounding of the float pair,
+        # the others to the tensor-core accumulation error
+        logits, _, ids_ref, _ = orc.route(x, weights0[0])
+        got = np.array([r["logits"] for r in lines])
+        assert np.abs(got - logits.numpy()).max() < (1e-9 if exact else 5e-4 / 4)
+        bad, _ = orc.compare_routing(np.array([r["ids"] for r in lines], np.int32), ids_ref.numpy(), logits)
+        assert bad == 0
+    finally:
+        b.set_option("router_exact", 0)
+        b.trace_reserve(T, 1, 0, enabled=False)
+
+
+def test_router_error_bound_is_checked_not_assumed(bound0, weights0):
+    """The near-tie test trusts a bound on the tensor-core accumulation error.  The exact pass
+    compares every logit it evaluates with the approximate one and fails the pass when the
+    bound does not hold; it never lets wrong ids through silently."""
+    b = bound0
+    T = 1024
+    x = orc.make_activations(47, T)
+    out = torch.zeros(T, 2048, device="cuda")
+    # a bound far below the real error (1e-8): the pass must be refused
+    b.set_option("router_eps", 10)
+    try:
+        b.begin(); b.encode_moe(0, x.cuda(), out)
+        with pytest.raises(OmniError, match="router accumulation error exceeded"):
+            b.complete()
+    finally:
+        b.set_option("router_eps", 500000)    # 5e-4, the default
+    # activations 64 times larger (logits and their error grow alike): the default bound scales
+    # with the row's largest |logit|, so the ids are still the oracle's -- or the pass says so
+    x64 = (x.float() * 64).to(torch.bfloat16)
+    out.zero_()
+    b.begin(); b.encode_moe(0, x64.cuda(), out)
+    try:
+        b.complete()
+    except OmniError as e:
+        assert "router accumulation error exceeded" in str(e)
+        return
+    logits, _, ids_ref, _ = orc.route(x64, weights0[0])
+    bad, _ = orc.compare_routing(b.read("ids", T), ids_ref.numpy(), logits)
+    assert bad == 0
 
 
 def test_failed_pass_does_not_publish_a_trace(bound0, tmp_path):

@@ -188,6 +188,44 @@ def test_config2_T4096_varlen_sampled(bound0, weights0):
     assert (np.diff(got["ids"].astype(np.int64), axis=-1) != 0).all()
 
 
+def permutation_properties(got, T):
+    assert got["counts"].sum() == T * 8 and np.array_equal(np.sort(got["slots"]), np.arange(T * 8))
+    assert np.array_equal(got["rowmap"][got["slots"]], np.arange(T * 8) // 8)
+    assert (np.diff(np.sort(got["ids"].astype(np.int64), axis=-1), axis=-1) != 0).all()
+
+
+def test_config3_T16384_single_sequence_sampled(bound0, weights0):
+    """One layer of configuration 3 (T=16384, one sequence, seed 2): every expert has about 1024
+    rows = four 256-row token tiles, so the multi-tile work items (a weight tile shared by
+    several token tiles, tile lists longer than the SM count) are what runs.  Ids and the
+    permutation are checked in full, 192 sampled output rows against the FP64 oracle."""
+    T = 16384
+    x = orc.make_activations(2, T)
+    got = run_block(bound0, 0, x)
+    assert got["counts"].min() > 3 * 256            # at least four token tiles for every expert
+    tokens = np.sort(np.random.default_rng(2).choice(T, 192, replace=False))
+    print(check_against_oracle(got, x, weights0, tokens=tokens))
+    permutation_properties(got, T)
+
+
+def test_config4_T8192_zipf_skew_sampled(backend, weights0):
+    """Configuration 4 (T=8192, seed 3, Zipf(1.2) bias on the router logits): the hottest expert
+    takes about ten times the mean, i.e. tens of token tiles for one expert, while others get
+    a handful of rows.  The sample takes half of its rows from the hottest expert's tokens."""
+    T = 8192
+    bias = torch.from_numpy(orc.zipf_bias(3))
+    backend.bind_layer(1, *weights0, bias=bias)
+    x = orc.make_activations(3, T)
+    got = run_block(backend, 1, x)
+    hot = int(got["counts"].argmax())
+    assert got["counts"][hot] >= 8 * 256 and got["counts"][hot] > 5 * got["counts"].mean()
+    rng = np.random.default_rng(3)
+    hot_tokens = np.where((got["ids"] == hot).any(-1))[0]
+    tokens = np.unique(np.concatenate([rng.choice(hot_tokens, 96, replace=False), rng.choice(T, 96, replace=False)]))
+    print(check_against_oracle(got, x, weights0, bias=bias.numpy(), tokens=tokens), "hottest", got["counts"][hot])
+    permutation_properties(got, T)
+
+
 @pytest.mark.parametrize("T", [300, 1537, 3000])
 def test_forward_host_equals_device_path(bound0, T):
     # above 1536 tokens the host call cuts the batch into pieces whose copies and kernels overlap

@@ -58,3 +58,28 @@ def test_out_of_range_id_is_reported_in_the_caller_status_word():
     ids[3, 2] = 500
     _, status = run_noalloc(ids)
     assert status & 8
+
+
+def test_without_a_status_word_on_a_side_stream():
+    """status=NULL is allowed: the sort then runs as usual, but nothing can report an expert id
+    outside [0,128) -- such an id is sorted as id & 127.  Valid ids give the same bits as with a
+    status word, on whichever stream the caller names."""
+    ids = random_ids(513, 5)
+    want, status = run_noalloc(ids)
+    assert status == 0
+    side = torch.cuda.Stream()
+    out = [torch.full((n,), -7, dtype=torch.int32, device="cuda") for n in (128, 129, 513 * 8, 513 * 8)]
+    side.wait_stream(torch.cuda.current_stream())
+    omni.assign_noalloc(ids, *out, status=None, stream=side.cuda_stream)
+    side.synchronize()
+    for g, w in zip(out, want):
+        assert np.array_equal(g.cpu().numpy(), w)
+    # an out-of-range id without a status word: masked, sorted, unreported (documented)
+    ids[7, 1] = 128 + 5
+    masked = ids.clone()
+    masked[7, 1] = 5
+    a, _ = run_noalloc(masked)
+    omni.assign_noalloc(ids, *out, status=None, stream=side.cuda_stream)
+    side.synchronize()
+    for g, w in zip(out, a):
+        assert np.array_equal(g.cpu().numpy(), w)
