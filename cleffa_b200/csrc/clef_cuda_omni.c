@@ -28,6 +28,7 @@ typedef struct {
     float *bias;                        /* device, FP32 [128] or NULL */
     bool owned, bound;
     CUtensorMap tm_router, tm_gate_up, tm_down;
+    CUtensorMap tm_gate_up3;            /* {K, gate|up, row} view of gate_up: a box interleaves gate and up rows */
 } omni_layer;
 
 /* The scratch arena (clef_omni_gpu in the reference, clef_metal_omni.m:18-23). */
@@ -63,6 +64,8 @@ struct clef_gpu {
     bool debug_poison, router_exact, profile, debug_stamps, ep_overlap;
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
+    int expert_kernel;                  /* tcgen05 expert products: 2 = pairs of CTAs (cta_group::2), 1 = the same kernel on
+                                           single CTAs, 0 = the earlier single-CTA kernels (two accumulators for gate/up) */
     int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
     int fused_router;                   /* the router kernel counts experts per sort segment (no histogram kernel) */
     int fused_gather;                   /* gate/up fetches its token rows through rowmap (no gather kernel) */
@@ -146,6 +149,19 @@ static bool make_map(clef_gpu *g, CUtensorMap *map, const void *base, uint64_t r
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+/* The gate/up matrix of the bound experts, [n_expert][gate rows 0..767 ; up rows 0..767][2048], as a
+ * three-dimensional tensor {K, 2, row}: coordinate (k, 0, e*1536 + f) with box {64, 2, 64} brings
+ * gate row f+i and up row f+i (i < 64) of expert e into consecutive shared-memory rows 2i, 2i+1. */
+static bool make_gate_up3(clef_gpu *g, CUtensorMap *map, const void *base, uint64_t n_expert) {
+    const cuuint64_t dims[3] = {OMNI_H, 2, n_expert * 2 * OMNI_F - OMNI_F};
+    const cuuint64_t strides[2] = {(cuuint64_t)OMNI_F * OMNI_H * 2, (cuuint64_t)OMNI_H * 2};
+    const cuuint32_t box[3] = {64, 2, 64};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return g->encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void *)base, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 /* ---------------------------------------------------------------- lifecycle */
 bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, size_t errlen) {
     if (!out) { set_err(err, errlen, "cuda: null context pointer"); return false; }
@@ -182,6 +198,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
         g->own_stream = true;
     }
     e = omni_sm100_configure();
+    if (e == cudaSuccess) e = omni_expert_configure();
     if (e != cudaSuccess) {
         set_err(err, errlen, "cuda: cannot configure sm_100a kernels: %s", cudaGetErrorString(e));
         if (g->own_stream) cudaStreamDestroy(g->stream);
@@ -503,7 +520,8 @@ bool clef_omni_bind_layer(clef_gpu *g, int layer, const void *router, const void
     }
     if (!make_map(g, &next.tm_router, next.router, OMNI_E, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
         !make_map(g, &next.tm_gate_up, next.gate_up, (uint64_t)EL * 2 * OMNI_F, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
-        !make_map(g, &next.tm_down, next.down, (uint64_t)EL * OMNI_H, OMNI_F, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+        !make_map(g, &next.tm_down, next.down, (uint64_t)EL * OMNI_H, OMNI_F, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
+        !make_gate_up3(g, &next.tm_gate_up3, next.gate_up, (uint64_t)EL)) {
         free_layer(&next);
         set_err(err, errlen, "cuda: cannot describe Omni expert tensors of layer %d", layer);
         return false;
@@ -573,7 +591,14 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     const bool fused = g->gemm_impl == 0 && g->fused_gather;
     if (!fused && !launched(g, "gather", omni_launch_gather(xn, s->sort.rowmap, rows8, s->xg, g->stream))) return false;
     stage_mark(g, 2);
-    if (g->gemm_impl == 0) {
+    if (g->gemm_impl == 0 && g->expert_kernel > 0) {
+        const int ctas = g->expert_kernel;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
+                                                                    fused ? s->sort.rowmap : NULL, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
+        stage_mark(g, 3);
+        if (!launched(g, "down experts", omni_launch_down_pair(ctas, &L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, NULL, NULL, g->reserve_sms == 0,
+                                                               g->n_sm - g->reserve_sms, g->stream))) return false;
+    } else if (g->gemm_impl == 0) {
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
                                                                      fused ? s->sort.rowmap : NULL, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
@@ -934,6 +959,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "router_eps")) { if (value <= 0) return false; g->router_eps = (float)((double)value * 1e-9); }
     else if (!strcmp(name, "gemm")) { if (value < 0 || value > 1) return false; g->gemm_impl = (int)value; }
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
+    else if (!strcmp(name, "expert_kernel")) { if (value < 0 || value > 2) return false; g->expert_kernel = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "ep_overlap")) g->ep_overlap = value != 0;

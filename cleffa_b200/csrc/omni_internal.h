@@ -138,6 +138,23 @@ cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *t
                                    void *d, const int32_t *tile_bounds, int group, int early_dependents, int n_sm,
                                    cudaStream_t s);
 
+/* ---- expert products on pairs of SMs (omni_expert.cu) ---- */
+cudaError_t omni_expert_configure(void);  /* opt-in shared-memory sizes; call once per device */
+/* ctas: 2 = clusters of two CTAs driving tcgen05.mma.cta_group::2, 1 = the same code on single CTAs.
+ * tm_w3: three-dimensional map of the gate/up matrix {K, gate|up, row} with box {64, 2, 64}: gate
+ * and up rows of the same intermediate column arrive interleaved.  Other arguments as in
+ * omni_launch_gateup_sm100. */
+cudaError_t omni_launch_gateup_pair(int ctas, const CUtensorMap *tm_w3, const CUtensorMap *tm_x4, const omni_sort_state st,
+                                    void *h, const uint32_t *ready, const int32_t *need, int group_size,
+                                    const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
+                                    cudaStream_t s);
+/* rowinfo/ret (may be NULL): expert parallelism -- result row i is written to row
+ * (rowinfo[i] & 0xfffff) of ret[rowinfo[i] >> 20] (the buffer of the rank the token came from)
+ * instead of row i of d */
+cudaError_t omni_launch_down_pair(int ctas, const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
+                                  void *d, const int32_t *tile_bounds, int group, const int32_t *rowinfo, void *const *ret,
+                                  int early_dependents, int n_sm, cudaStream_t s);
+
 /* Programmatic dependent launch of the pass's kernel chain (process-wide, default on) */
 void omni_set_dependent_launch(int on);
 int omni_dependent_launch_enabled(void);

@@ -14,6 +14,7 @@ from oracle import omni_oracle as orc
 
 pytestmark = pytest.mark.gpu
 REL_L2_GATE = 1e-2
+EXPERT_KERNEL_DEFAULT = 0
 WEIGHT_TOL_FAST = 2e-5      # tensor-core logits (FP32 accumulate); rows decided by the exact pass reach 2e-7
 
 
@@ -96,6 +97,30 @@ def test_launch_variants_give_the_same_bits(bound0, T):
     finally:
         for name in opts:
             b.set_option(name, 1)
+
+
+@pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("T", [1, 37, 300, 2500, 4096])
+def test_expert_kernel_variants_give_the_same_bits(bound0, T, ctas):
+    """The expert products exist as two schedules of the same arithmetic: single CTAs with one
+    accumulator per gate and up tile, and CTA pairs (or single CTAs, ctas=1) on interleaved
+    gate/up rows with the output staged through shared memory.  Every element is the same K-ordered
+    FP32 sum either way, so the block's output must be the same bytes, with the token rows
+    gathered by the kernel or read from the permuted copy."""
+    b = bound0
+    x = orc.make_activations(23, T)
+    try:
+        b.set_option("expert_kernel", 0)
+        base = run_block(b, 0, x)
+        for gather in (1, 0):
+            b.set_option("fused_gather", gather)
+            b.set_option("expert_kernel", ctas)
+            other = run_block(b, 0, x)
+            for key in ("ids", "slots", "counts", "out"):
+                assert np.array_equal(base[key], other[key]), (key, gather)
+    finally:
+        b.set_option("fused_gather", 1)
+        b.set_option("expert_kernel", EXPERT_KERNEL_DEFAULT)
 
 
 def test_golden_ids_of_config1(bound0):
