@@ -45,7 +45,7 @@ GATEUP_FLOP_PER_TOKEN = 2 * H * (2 * F) * TOP          # 50,331,648
 EXPERT_FLOP_PER_TOKEN = GATEUP_FLOP_PER_TOKEN + 2 * F * H * TOP   # 75,497,472
 WEIGHT_BYTES = (E * H + E * 2 * F * H + E * H * F) * 2
 KERNELS_PER_PASS = 7     # router (counts the sort segments), exact pass, scan, scatter, gate/up (gathers its rows), down, combine
-KERNELS_PER_PASS_EP = 12 # ... plus plan, dispatch, return and two barriers
+KERNELS_PER_PASS_EP = 9  # ... plus plan and one barrier; the expert kernels dispatch and return the rows themselves
 METRIC = "MoE-layer prefill tokens/sec at T=4096"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at T=4096, from the ncu
 # capture summarised in profiles/ncu_full_router_experts_combine_T4096.md
@@ -234,20 +234,15 @@ def ours(args):
     bounds = np.array([0, T], np.int32) if (single_seq or args.strong) else workloads.varlen_bounds(SEED, T)
     res_host = torch.zeros(T, H).pin_memory()
 
-    # Dedicated streams: the library launches on them and the timing events are recorded on the
-    # main one (the legacy default stream has handle 0, which the C-ABI reads as "create your own").
-    # With expert parallelism the tokens of a rank may be split into `micro` independent
-    # micro-batches, each driven through its own library context and stream.
-    micro = max(1, args.micro if args.micro else 1)
+    # A dedicated stream: the library launches on it and the timing events are recorded on it
+    # (the legacy default stream has handle 0, which the C-ABI reads as "create your own").
     main_stream = torch.cuda.Stream()
     torch.cuda.set_stream(main_stream)
-    streams = [main_stream] + [torch.cuda.Stream() for _ in range(micro - 1)]
-    bs = [OmniBackend(local, stream=st.cuda_stream) for st in streams]
-    for b in bs:
-        b.reserve(T, n_layer=n_layers)
-        for kv in args.option:                           # library options, name=value (for A/B runs)
-            name, _, val = kv.partition("=")
-            b.set_option(name, int(val))
+    b = OmniBackend(local, stream=main_stream.cuda_stream)
+    b.reserve(T, n_layer=n_layers)
+    for kv in args.option:                               # library options, name=value (for A/B runs)
+        name, _, val = kv.partition("=")
+        b.set_option(name, int(val))
 
     def layer_weights(l):
         """Layer 0: the seeded host weights.  Further layers: generated on the device from a seed
@@ -260,44 +255,26 @@ def ours(args):
 
     if world > 1:
         # expert parallel: 128/world experts per GPU; every rank maps every rank's exchange buffers
-        for b in bs:
-            handles = [None] * world
-            dist.all_gather_object(handles, b.ep_export())
-            b.ep_connect(rank, world, b"".join(handles))
+        handles = [None] * world
+        dist.all_gather_object(handles, b.ep_export())
+        b.ep_connect(rank, world, b"".join(handles))
         for l in range(n_layers):
             r_, gu_, dn_ = layer_weights(l)
-            dev_w = (r_.cuda(), gu_[rank * el:(rank + 1) * el].cuda().contiguous(), dn_[rank * el:(rank + 1) * el].cuda().contiguous())
+            b.bind_layer(l, r_.cuda(), gu_[rank * el:(rank + 1) * el].cuda().contiguous(), dn_[rank * el:(rank + 1) * el].cuda().contiguous(),
+                         bias=bias.cuda() if bias is not None else None)
             del r_, gu_, dn_
-            for b in bs:
-                b.bind_layer(l, *dev_w, bias=bias.cuda() if bias is not None else None)   # one device copy of the slice, shared
         dist.barrier()                                   # every rank has mapped every rank
-        for b in bs:
-            b.ep_sync(30000)                             # first touch of the peers' memory happens here
-        for bi in bs:
-            if args.reserve:
-                bi.set_option("reserve_sms", args.reserve)
-            if args.overlap:
-                bi.set_option("ep_overlap", 1)
-        if micro > 1 and not args.no_gate:
-            # stagger the micro-batches: context i starts its dispatch when context i-1 finished its own
-            gates = [torch.cuda.Event() for _ in range(micro)]
-            for ev, st in zip(gates, streams):
-                ev.record(st)                            # gives every event a handle; the first waits pass
-            torch.cuda.synchronize()
-            for i, bi in enumerate(bs):
-                bi.ep_gate(gates[(i - 1) % micro].cuda_event, gates[i].cuda_event)
+        b.ep_sync(30000)                                 # first touch of the peers' memory happens here
     else:
-        bs[0].bind_layer(0, router, gate_up, down, bias=bias)
+        b.bind_layer(0, router, gate_up, down, bias=bias)
         for l in range(1, n_layers):
-            bs[0].bind_layer(l, *layer_weights(l))
-    b = bs[0]
+            b.bind_layer(l, *layer_weights(l))
     if args.norm:
         for l in range(n_layers):
             b.bind_norm(l, torch.ones(H), 1e-6)
     xn = x_host.cuda()
     x = torch.zeros(T, H, device="cuda")
     x0 = xn.float() if n_layers > 1 else None
-    cuts = [T * i // micro for i in range(micro + 1)]
     torch.cuda.synchronize()
 
     def step():
@@ -311,13 +288,8 @@ def ours(args):
                     xn.copy_(x)                 # FP32 residual -> BF16 layer input (the norm's place)
                     b.encode_moe(l, xn, x, bounds)
             return
-        if micro == 1:
-            b.begin()
-            b.encode_moe(0, xn, x, bounds)
-            return
-        for i, bi in enumerate(bs):
-            bi.begin()
-            bi.encode_moe(0, xn[cuts[i]:cuts[i + 1]], x[cuts[i]:cuts[i + 1]])
+        b.begin()
+        b.encode_moe(0, xn, x, bounds)
 
     def barrier():
         if world > 1:
@@ -335,8 +307,7 @@ def ours(args):
     barrier()
     for _ in range(max(3, args.warmup)):
         step()
-    for bi in bs:
-        bi.complete()
+    b.complete()
 
     def timed_region():
         """EXACTLY `steps` steps between two events on the launching stream, bracketed by a
@@ -344,18 +315,11 @@ def ours(args):
         barrier()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(main_stream)
-        for st in streams[1:]:
-            st.wait_event(start)
         for _ in range(args.steps):
             step()
-        for st in streams[1:]:
-            done = torch.cuda.Event()
-            done.record(st)
-            main_stream.wait_event(done)
         stop.record(main_stream)
         barrier()
-        for bi in bs:
-            bi.complete()
+        b.complete()
         ms = start.elapsed_time(stop)
         return agree(ms, dist.ReduceOp.MAX) if world > 1 else ms
 
@@ -374,8 +338,7 @@ def ours(args):
     if args.kernels_only and world == 1:
         # for captures under a profiler: the warm-up and the timed steps, nothing else
         print(json.dumps({"kernels_only": True, "ms_per_step": elapsed_ms / args.steps, "tokens": T, "n_gpus": world}))
-        for bi in bs:
-            bi.close()
+        b.close()
         return
 
     # ---- a further region of the same K steps with an event recorded between the stages of every
@@ -430,9 +393,9 @@ def ours(args):
         if world == 1:
             par = "single GPU"
         else:
-            par = (f"expert parallel ep{world}, tokens data-parallel, rows exchanged by peer stores over NVLink, "
-                   f"{micro} micro-batch(es) per rank")
-        launches = (KERNELS_PER_PASS + (1 if args.norm else 0)) * n_layers if world == 1 else KERNELS_PER_PASS_EP * micro * n_layers
+            par = (f"expert parallel ep{world}, tokens data-parallel, rows exchanged by peer stores over NVLink "
+                   f"from inside the expert kernels")
+        launches = (KERNELS_PER_PASS + (1 if args.norm else 0)) * n_layers if world == 1 else KERNELS_PER_PASS_EP * n_layers
         line = {
             "metric": METRIC if (T_TOKENS == 4096 and n_layers == 1 and not zipf) else
                       f"MoE-layer prefill tokens/sec at T={T_TOKENS}" + (f" through {n_layers} layers" if n_layers > 1 else ""),
@@ -474,11 +437,9 @@ def ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
-        for bi in bs:
-            bi.ep_disconnect()
+        b.ep_disconnect()
         dist.barrier()
-    for bi in bs:
-        bi.close()
+    b.close()
     if world > 1:
         dist.destroy_process_group()
     if ep_equal is not None and not ep_equal:
@@ -544,14 +505,10 @@ def main():
     ap.add_argument("--max-regions", type=int, default=400)
     ap.add_argument("--sweep", action="store_true", help="BASELINE configuration 5: latency table over small batch sizes, one GPU")
     ap.add_argument("--sweep-tokens", type=int, nargs="+", default=[1, 8, 32, 64, 128, 256])
-    ap.add_argument("--no-gate", action="store_true", help="do not stagger the micro-batches")
-    ap.add_argument("--reserve", type=int, default=0, help="SMs the expert kernels leave to the copy kernels with expert parallelism (0: the library default, 16 with --overlap)")
     ap.add_argument("--norm", action="store_true", help="with --layers: each layer normalises the residual stream itself (RMSNorm, unit weights) instead of taking a BF16 copy")
     ap.add_argument("--kernels-only", action="store_true", help="run the warm-up and the timed steps and stop (for profiler captures; one GPU)")
     ap.add_argument("--option", action="append", default=[], help="library option name=value (clef_omni_set_option), repeatable")
-    ap.add_argument("--overlap", action="store_true", help="expert parallelism: run the transfers under the expert kernels")
     ap.add_argument("--layers", type=int, default=1, help="stack of MoE sublayers with residual adds (BASELINE configuration 3 uses 48 at --tokens 16384)")
-    ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank, each on its own context and stream (default 1)")
     args = ap.parse_args()
     T_TOKENS = args.tokens
     SEED = args.seed if args.seed is not None else (3 if args.bias == "zipf" else 2 if args.layers > 1 else 1)

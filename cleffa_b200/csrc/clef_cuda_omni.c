@@ -61,7 +61,8 @@ struct clef_gpu {
     int trace_first, trace_rows, trace_layers;
     bool trace_valid;
     /* options */
-    bool debug_poison, router_exact, profile, debug_stamps, ep_overlap;
+    bool debug_poison, router_exact, profile, debug_stamps;
+    int ep_fused;                       /* expert parallelism: the expert kernels move the rows themselves (default 1) */
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
     int expert_kernel;                  /* tcgen05 expert products: 2 = pairs of CTAs (cta_group::2), 1 = the same kernel on
@@ -96,11 +97,7 @@ struct clef_gpu {
         uint32_t *sync_result;           /* device [2] */
         void *dret; int32_t *rowinfo, *counts, *send_base, *n_local_rows; uint32_t *flags;
         void *opened[OMNI_EP_MAX][OMNI_EP_BUFFERS];
-        cudaEvent_t gate_wait, gate_record;   /* optional host-supplied events around the dispatch phase */
-        cudaStream_t side;                    /* dispatch runs here, under the gate/up kernel */
-        cudaEvent_t ev_planned, ev_dispatched, ev_down[OMNI_EP_RET_GROUPS], ev_returned;
         int32_t *need;                        /* [128] rows each group of local experts must receive */
-        int32_t *ret_bounds;                  /* [2][RET_GROUPS+1] tile and row bounds of the down/return groups */
     } ep;
     CUresult (*encode_tiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -182,6 +179,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     g->router_eps = 5e-4f;
     g->fused_gather = 1;
     g->fused_router = 1;
+    g->ep_fused = 1;
     void *fn = NULL;
     enum cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -594,9 +592,10 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     if (g->gemm_impl == 0 && g->expert_kernel > 0) {
         const int ctas = g->expert_kernel;
         if (!launched(g, "gate/up experts", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
-                                                                    fused ? s->sort.rowmap : NULL, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
+                                                                    fused ? s->sort.rowmap : NULL, NULL, NULL, NULL, g->reserve_sms == 0,
+                                                                    g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_pair(ctas, &L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, NULL, NULL, g->reserve_sms == 0,
+        if (!launched(g, "down experts", omni_launch_down_pair(ctas, &L->tm_down, s->tm_h, s->sort, s->d, NULL, NULL, g->reserve_sms == 0,
                                                                g->n_sm - g->reserve_sms, g->stream))) return false;
     } else if (g->gemm_impl == 0) {
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
@@ -616,61 +615,41 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
 }
 
 /* Expert-parallel variant of run_experts: rows travel to the ranks that own their experts and
- * back by peer stores (omni_ep.cu).
+ * back by peer stores, inside the two expert kernels (omni_expert.cu, omni_ep_dev.cuh).
  *
- * Default (ep_overlap = 0): the phases follow one another on the context's stream -- plan
- * (+barrier), dispatch, barrier, gate/up, down, return, barrier, combine.
+ * Default (ep_fused = 1): plan (+ barrier: every rank knows every rank's counts), then the gate/up
+ * kernel, whose spare warps send this rank's token rows to the owners group by group while its
+ * token producers wait per group of experts until that group's rows have arrived from every
+ * rank; then the down kernel, whose epilogue writes every result row piece straight into the
+ * buffer of the rank the token came from; one barrier; combine.  No copy kernel runs and the
+ * transfers travel under the products.
  *
- * ep_overlap = 1 (optional): dispatch goes to a side stream and the gate/up kernel starts at
- * once, its token producer waiting per group of experts until that group's rows have arrived
- * from every rank; the down product runs in RET_GROUPS launches and each group's results travel
- * back on the side stream under the next group's product.  A copy kernel cannot share an SM with
- * a resident expert-product CTA (which holds nearly all of its shared memory), so the expert
- * kernels then leave reserve_sms SMs (default 16) to the copies.  Same bits as the default;
- * measured 5 % faster on 8 GPUs at 4096 tokens per rank (0.733 against 0.768 ms per pass): the
- * copies are slower on few SMs and the products slower on fewer, which eats most of the overlap. */
+ * ep_fused = 0 (for comparison, same bits): a copy kernel dispatches all rows and a barrier
+ * follows before the gate/up kernel starts; the way back is the same as above. */
 static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, const int32_t *ids, const float *weights,
                            float *x, int rows, bool have_counts) {
     omni_arena *s = g->omni;
     const int rows8 = rows * OMNI_TOP;
     const omni_ep_peers *pe = &g->ep.peers;
-    const bool overlap = g->ep_overlap;
-    const int32_t *row_bounds = g->ep.ret_bounds + OMNI_EP_RET_GROUPS + 1;
-    /* with overlap the persistent expert kernels leave some SMs to the copy kernels */
-    const int n_gemm = g->n_sm - (g->reserve_sms > 0 ? g->reserve_sms : overlap ? 16 : 0);
+    const int ctas = g->expert_kernel == 1 ? 1 : 2;
+    const int n_gemm = g->n_sm - g->reserve_sms;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, have_counts, g->stream))) return false;
-    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds, g->ep.wait_ns, g->stream))) return false;
-    if (!overlap) {
-        if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->stream, g->ep.gate_wait, 0))) return false;
+    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.wait_ns, g->stream))) return false;
+    if (g->ep_fused) {
+        stage_mark(g, 2);
+        if (!launched(g, "gate/up experts + dispatch", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
+                                                                               g->ep.need, omni_ep_group_size(pe->world), NULL, NULL, pe, xn, g->ep.send_base,
+                                                                               g->reserve_sms == 0, n_gemm, g->stream))) return false;
+    } else {
         if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, 0, g->n_sm, g->stream))) return false;
         if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->ep.wait_ns, g->stream))) return false;
-        if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->stream))) return false;
         stage_mark(g, 2);
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, n_gemm == g->n_sm, n_gemm, g->stream))) return false;
-        stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, n_gemm == g->n_sm, n_gemm, g->stream))) return false;
-        stage_mark(g, 4);
-        if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, row_bounds, 0, OMNI_EP_RET_GROUPS, g->n_sm, g->stream))) return false;
-    } else {
-        if (g->ep.gate_wait && !launched(g, "dispatch gate", cudaStreamWaitEvent(g->ep.side, g->ep.gate_wait, 0))) return false;
-        if (!launched(g, "dispatch fork", cudaEventRecord(g->ep.ev_planned, g->stream))) return false;
-        if (!launched(g, "dispatch fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_planned, 0))) return false;
-        if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, 1, g->n_sm, g->ep.side))) return false;
-        if (g->ep.gate_record && !launched(g, "dispatch gate", cudaEventRecord(g->ep.gate_record, g->ep.side))) return false;
-        stage_mark(g, 2);
-        if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
-                                                                     g->ep.need, omni_ep_group_size(pe->world), NULL, NULL, 0, n_gemm, g->stream))) return false;
-        stage_mark(g, 3);
-        for (int rg = 0; rg < OMNI_EP_RET_GROUPS; rg++) {
-            if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, g->ep.ret_bounds, rg, 0, n_gemm, g->stream))) return false;
-            if (!launched(g, "return fork", cudaEventRecord(g->ep.ev_down[rg], g->stream))) return false;
-            if (!launched(g, "return fork", cudaStreamWaitEvent(g->ep.side, g->ep.ev_down[rg], 0))) return false;
-            if (!launched(g, "expert-parallel return", omni_launch_ep_return(pe, s->d, g->ep.rowinfo, row_bounds, rg, rg + 1, g->n_sm, g->ep.side))) return false;
-        }
-        stage_mark(g, 4);
-        if (!launched(g, "return join", cudaEventRecord(g->ep.ev_returned, g->ep.side))) return false;
-        if (!launched(g, "return join", cudaStreamWaitEvent(g->stream, g->ep.ev_returned, 0))) return false;
+        if (!launched(g, "gate/up experts", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, NULL, NULL, NULL,
+                                                                    g->reserve_sms == 0, n_gemm, g->stream))) return false;
     }
+    stage_mark(g, 3);
+    if (!launched(g, "down experts + return", omni_launch_down_pair(ctas, &L->tm_down, s->tm_h, s->sort, s->d, pe, g->ep.rowinfo, g->reserve_sms == 0, n_gemm, g->stream))) return false;
+    stage_mark(g, 4);
     if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->ep.wait_ns, g->stream))) return false;
     if (g->wait_residual && !launched(g, "residual upload join", cudaStreamWaitEvent(g->stream, g->residual_uploaded, 0))) return false;
     if (!launched(g, "combine", omni_launch_combine(g->ep.dret, ids, weights, s->sort.slots, x, rows, g->stream))) return false;
@@ -962,7 +941,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "expert_kernel")) { if (value < 0 || value > 2) return false; g->expert_kernel = (int)value; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
-    else if (!strcmp(name, "ep_overlap")) g->ep_overlap = value != 0;
+    else if (!strcmp(name, "ep_fused")) g->ep_fused = value != 0;
     else if (!strcmp(name, "ep_wait_ms")) { if (value < 0) return false; g->ep.wait_ns = (uint64_t)value * 1000000ull; }
     else if (!strcmp(name, "dependent_launch")) omni_set_dependent_launch(value != 0);
     else if (!strcmp(name, "fused_router")) g->fused_router = value != 0;
@@ -1001,15 +980,8 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
     int32_t *send_base = dev_alloc(g, (size_t)OMNI_E * 4);
     int32_t *n_local = dev_alloc(g, 256);
     int32_t *need = dev_alloc(g, (size_t)OMNI_E * 4);
-    int32_t *ret_bounds = dev_alloc(g, 256);
     uint32_t *sync_result = dev_alloc(g, 256);
-    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && ret_bounds && sync_result;
-    if (ok && !g->ep.side) ok = cudaStreamCreateWithFlags(&g->ep.side, cudaStreamNonBlocking) == cudaSuccess &&
-                                cudaEventCreateWithFlags(&g->ep.ev_planned, cudaEventDisableTiming) == cudaSuccess &&
-                                cudaEventCreateWithFlags(&g->ep.ev_dispatched, cudaEventDisableTiming) == cudaSuccess &&
-                                cudaEventCreateWithFlags(&g->ep.ev_returned, cudaEventDisableTiming) == cudaSuccess;
-    for (int i = 0; i < OMNI_EP_RET_GROUPS && ok; i++)
-        if (!g->ep.ev_down[i]) ok = cudaEventCreateWithFlags(&g->ep.ev_down[i], cudaEventDisableTiming) == cudaSuccess;
+    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && sync_result;
     if (ok) ok = cudaMemsetAsync(flags, 0, (size_t)OMNI_EP_FLAG_WORDS * 4, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(need, 0, (size_t)OMNI_E * 4, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(counts, 0, (size_t)OMNI_EP_MAX * OMNI_E * 4, g->stream) == cudaSuccess &&
@@ -1017,13 +989,13 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
                  cudaStreamSynchronize(g->stream) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
-        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, ret_bounds, sync_result};
+        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, sync_result};
         for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
         set_err(err, errlen, "cuda: cannot allocate Omni expert-parallel buffers (previous buffers kept)");
         return false;
     }
     g->ep.dret = dret; g->ep.rowinfo = rowinfo; g->ep.counts = counts; g->ep.flags = flags;
-    g->ep.send_base = send_base; g->ep.n_local_rows = n_local; g->ep.need = need; g->ep.ret_bounds = ret_bounds;
+    g->ep.send_base = send_base; g->ep.n_local_rows = n_local; g->ep.need = need;
     g->ep.sync_result = sync_result;
     return true;
 }
@@ -1152,13 +1124,6 @@ bool clef_omni_ep_sync(clef_gpu *g, int timeout_ms, char *err, size_t errlen) {
     return true;
 }
 
-bool clef_omni_ep_gate(clef_gpu *g, void *wait_event, void *record_event) {
-    if (!g) return false;
-    g->ep.gate_wait = (cudaEvent_t)wait_event;
-    g->ep.gate_record = (cudaEvent_t)record_event;
-    return true;
-}
-
 void clef_omni_ep_disconnect(clef_gpu *g) {
     if (!g) return;
     cudaSetDevice(g->device);
@@ -1166,13 +1131,7 @@ void clef_omni_ep_disconnect(clef_gpu *g) {
     if (g->ep.ipc)
         for (int r = 0; r < OMNI_EP_MAX; r++) for (int i = 0; i < OMNI_EP_BUFFERS; i++)
             if (g->ep.opened[r][i]) { cudaIpcCloseMemHandle(g->ep.opened[r][i]); g->ep.opened[r][i] = NULL; }
-    if (g->ep.side) { cudaStreamSynchronize(g->ep.side); cudaStreamDestroy(g->ep.side); }
-    if (g->ep.ev_planned) cudaEventDestroy(g->ep.ev_planned);
-    if (g->ep.ev_dispatched) cudaEventDestroy(g->ep.ev_dispatched);
-    if (g->ep.ev_returned) cudaEventDestroy(g->ep.ev_returned);
-    for (int i = 0; i < OMNI_EP_RET_GROUPS; i++) if (g->ep.ev_down[i]) cudaEventDestroy(g->ep.ev_down[i]);
-    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.ret_bounds,
-                   g->ep.sync_result};
+    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.sync_result};
     for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
     memset(&g->ep, 0, sizeof g->ep);
     cudaGetLastError();

@@ -24,30 +24,9 @@
 #include <stdint.h>
 
 #include "omni_internal.h"
+#include "omni_ep_dev.cuh"
 
 namespace {
-
-constexpr uint64_t SPIN_LIMIT_NS = 2000000000ull;      // 2 s: every legitimate wait is far shorter
-
-__device__ __forceinline__ uint64_t now_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Adds to a counter in (possibly another GPU's) memory; every store this warp made before the
-// preceding __syncwarp is visible to whoever acquires the new value.
-__device__ __forceinline__ void red_release_sys_add(uint32_t *p, uint32_t v) {
-    __threadfence_system();
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 // One block.  Every rank tells every peer "I reached epoch E", then waits until all peers
 // said so.  Writes made by earlier kernels of this stream are ordered before the flag by the
@@ -110,7 +89,7 @@ __global__ void __launch_bounds__(32) ep_sync_kernel(omni_ep_peers pe, uint32_t 
 // Publish my counts, barrier, then plan.  One block of 128 threads, thread e = expert e.
 __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint32_t epoch, omni_sort_state st,
                                                          int32_t *send_base, int32_t *n_local_rows, int32_t *need,
-                                                         int32_t *ret_bounds, uint64_t limit_ns) {
+                                                         uint64_t limit_ns) {
     __shared__ int tot[OMNI_E], scan[OMNI_E], tiles[OMNI_E];
     const int e = threadIdx.x;
     const int G = pe.world, EL = OMNI_E / G;
@@ -157,12 +136,6 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
             const int hi = min((grp + 1) * gsz, EL);
             need[grp] = (hi < EL ? scan[hi] : rows) - scan[grp * gsz];
         }
-        // the down product and the way back run in RET_GROUPS groups of local experts
-        for (int rg = 0; rg <= OMNI_EP_RET_GROUPS; rg++) {
-            const int le0 = min(EL, (EL * rg + OMNI_EP_RET_GROUPS - 1) / OMNI_EP_RET_GROUPS);
-            ret_bounds[rg] = le0 < EL ? tiles[le0] : t;
-            ret_bounds[OMNI_EP_RET_GROUPS + 1 + rg] = le0 < EL ? scan[le0] : rows;
-        }
         *n_local_rows = rows;
         *st.n_ttiles = rows <= OMNI_ROWS ? t : 0;
         for (int i = 0; i < 8; i++) st.sched[i] = 0;
@@ -177,75 +150,13 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
     }
 }
 
-// One warp per permuted row of this rank: 4 KiB to the owner's buffer + its origin tag.
-// Blocks are dealt round-robin to destination ranks, starting with the next rank, so that at
-// every moment each rank writes to all owners at once and no owner is the target of everyone
-// (walking the rows in expert order would make all ranks hit owner 0 first, then owner 1, ...:
-// measured 2.6x slower on 8 GPUs).  An owner's experts are sent in ascending groups; after each
-// group the block adds the number of rows it delivered to the owner's arrival counter of that
-// group (one system-scope release per block and group), which is what the owner's gate/up
-// kernel waits on before it reads those rows.
 template <bool SIGNAL>
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(omni_ep_peers pe, const uint4 *__restrict__ xn,
                                                           const int32_t *__restrict__ rowmap,
                                                           const int32_t *__restrict__ offsets,
                                                           const int32_t *__restrict__ send_base) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // without SIGNAL (phases separated by a barrier) the owner's experts form one group and nothing is announced
-    const int G = pe.world, EL = OMNI_E / G, gsz = SIGNAL ? omni_ep_group_size(G) : EL;
-    const int owner = (int)((blockIdx.x % G + pe.rank + 1) % G);
-    const int sub = blockIdx.x / G, nsub = (gridDim.x - (blockIdx.x % G) + G - 1) / G;   // blocks serving this owner
-    uint4 *xg = reinterpret_cast<uint4 *>(pe.xg[owner]);
-    int32_t *info = pe.rowinfo[owner];
-    uint32_t *arrived = pe.flags[owner] + OMNI_EP_READY_WORD;        // the owner's per-group arrival counters
-    int e = owner * EL;
-    for (int grp = 0; grp * gsz < EL; grp++) {
-        const int lo = offsets[owner * EL + grp * gsz], hi = offsets[owner * EL + min((grp + 1) * gsz, EL)];
-        for (int r = lo + sub * 8 + warp; r < hi; r += nsub * 8) {
-            while (offsets[e + 1] <= r) e++;                        // rows ascend: the expert only moves forward
-            const long dst = (long)send_base[e] + (r - offsets[e]);
-            if (dst >= OMNI_ROWS) continue;                         // owner overflow: flagged by its plan kernel
-            const uint4 *src = xn + (long)rowmap[r] * (OMNI_H / 8);
-            uint4 *out = xg + dst * (OMNI_H / 8);
-            uint4 v[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __ldg(src + lane + 32 * i);
-#pragma unroll
-            for (int i = 0; i < 8; i++) out[lane + 32 * i] = v[i];
-            if (lane == 0) info[dst] = (pe.rank << 20) | r;
-        }
-        if (!SIGNAL) break;
-        __threadfence_system();          // every thread: its own row stores are out before the count is published
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            // rows of [lo, hi) that fell to this block: positions j with (j / 8) % nsub == sub
-            const int n = hi - lo, full = n / (nsub * 8), rem = n % (nsub * 8);
-            const int mine = full * 8 + max(0, min(8, rem - sub * 8));
-            if (mine) red_release_sys_add(arrived + grp, (uint32_t)mine);
-        }
-    }
-}
-
-// One warp per local expert-major row: result row back to the source rank's permuted position.
-__global__ void __launch_bounds__(256) ep_return_kernel(omni_ep_peers pe, const uint4 *__restrict__ d,
-                                                        const int32_t *__restrict__ rowinfo,
-                                                        const int32_t *__restrict__ row_bounds, int group, int group_end) {
-    const int lane = threadIdx.x & 31;
-    const int warps = gridDim.x * 8;
-    const int first = row_bounds[group];
-    int n = row_bounds[group_end];
-    if (n > OMNI_ROWS) n = 0;
-    for (int r = first + blockIdx.x * 8 + (threadIdx.x >> 5); r < n; r += warps) {
-        const int info = rowinfo[r];
-        const int src_rank = info >> 20, src_row = info & 0xfffff;
-        const uint4 *src = d + (long)r * (OMNI_H / 8);
-        uint4 *out = reinterpret_cast<uint4 *>(pe.dret[src_rank]) + (long)src_row * (OMNI_H / 8);
-        uint4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = src[lane + 32 * i];
-#pragma unroll
-        for (int i = 0; i < 8; i++) out[lane + 32 * i] = v[i];
-    }
+    ep_dispatch_rows<SIGNAL>(pe, xn, rowmap, offsets, send_base, (int)blockIdx.x, (int)gridDim.x, threadIdx.x >> 5, 8,
+                             threadIdx.x & 31, threadIdx.x == 0, [] { __syncthreads(); });
 }
 
 }  // namespace
@@ -253,8 +164,8 @@ __global__ void __launch_bounds__(256) ep_return_kernel(omni_ep_peers pe, const 
 extern "C" {
 
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, uint64_t limit_ns, cudaStream_t s) {
-    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, ret_bounds, limit_ns ? limit_ns : SPIN_LIMIT_NS);
+                                int32_t *n_local_rows, int32_t *need, uint64_t limit_ns, cudaStream_t s) {
+    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, limit_ns ? limit_ns : SPIN_LIMIT_NS);
     return cudaGetLastError();
 }
 
@@ -280,12 +191,6 @@ cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, con
     if (blocks < pe->world) blocks = pe->world;
     if (signal) ep_dispatch_kernel<true><<<blocks, 256, 0, s>>>(*pe, (const uint4 *)xn, rowmap, offsets, send_base);
     else ep_dispatch_kernel<false><<<blocks, 256, 0, s>>>(*pe, (const uint4 *)xn, rowmap, offsets, send_base);
-    return cudaGetLastError();
-}
-
-cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
-                                  const int32_t *row_bounds, int group, int group_end, int n_sm, cudaStream_t s) {
-    ep_return_kernel<<<n_sm, 256, 0, s>>>(*pe, (const uint4 *)d, rowinfo, row_bounds, group, group_end);
     return cudaGetLastError();
 }
 

@@ -31,6 +31,7 @@
 #include <stdint.h>
 
 #include "omni_internal.h"
+#include "omni_ep_dev.cuh"
 #include "omni_pdl.cuh"
 #include "omni_ptx.cuh"
 
@@ -55,6 +56,13 @@ __device__ __forceinline__ void cluster_sync_all() {
 // arrive on a barrier that may live in the peer CTA (shared::cluster address)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same with the default ordering (release at CTA scope): for arrivals that only say "done"
+// -- a stage was consumed, copies into this CTA's own shared memory have landed -- and publish no
+// data written through the generic proxy into another CTA.  A cluster-scope release costs
+// hundreds of nanoseconds and these arrivals sit on the per-stage critical path.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -84,23 +92,29 @@ struct Abort {
     }
 };
 
-template <int CTAS>
+// Bounded wait on a barrier of this CTA.  False: the limit ran out or someone in the pair gave up.
+// CLUSTER: acquire at cluster scope, for the one hand-over whose data another CTA wrote with
+// ordinary stores (the item ring); everything else is signalled by the asynchronous units.
+template <bool CLUSTER>
 __device__ __noinline__ bool xwait_slow(uint32_t bar, uint32_t parity, const Abort &ab) {
     const uint64_t t0 = globaltimer_ns();
     for (;;) {
         for (int i = 0; i < 256; i++)
-            if (CTAS == 2 ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+            if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if (*ab.flag) return false;
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { ab.raise(OMNI_ST_TIMEOUT); return false; }
     }
 }
-// Bounded wait on a barrier of this CTA.  False: the limit ran out or someone in the pair gave up.
-template <int CTAS>
-__device__ __forceinline__ bool xwait(uint32_t bar, uint32_t parity, const Abort &ab) {
+template <bool CLUSTER>
+__device__ __forceinline__ bool xwait_impl(uint32_t bar, uint32_t parity, const Abort &ab) {
     for (int i = 0; i < 64; i++)
-        if (CTAS == 2 ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    return xwait_slow<CTAS>(bar, parity, ab);
+        if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    return xwait_slow<CLUSTER>(bar, parity, ab);
 }
+template <int CTAS>
+__device__ __forceinline__ bool xwait(uint32_t bar, uint32_t parity, const Abort &ab) { return xwait_impl<false>(bar, parity, ab); }
+template <int CTAS>
+__device__ __forceinline__ bool xwait_item(uint32_t bar, uint32_t parity, const Abort &ab) { return xwait_impl<CTAS == 2>(bar, parity, ab); }
 
 // TMA loads whose completion is signalled on a barrier of the pair's first CTA.  Each CTA
 // issues its own loads into its own shared memory: nothing here is a multicast.
@@ -193,6 +207,7 @@ static_assert(XCfg<X_GATEUP, 1>::TOTAL_BYTES <= 232448 && XCfg<X_DOWN, 1>::TOTAL
               XCfg<X_GATEUP, 2>::TOTAL_BYTES <= 232448 && XCfg<X_DOWN, 2>::TOTAL_BYTES <= 232448, "shared memory budget");
 
 constexpr int X_THREADS = 384;      // warp 0 scheduler + weight loads, 1 MMA, 2 TMEM (2+3 gather), 3 token loads, 4..11 epilogue
+constexpr int X_COPY_THREADS = 128; // with COPY: warps 12..15 move this rank's token rows to the other ranks
 constexpr int X_EPI_WARPS = 8;
 constexpr int X_GATHER_THREADS = 64;
 constexpr int X_RING = 4;
@@ -209,14 +224,17 @@ struct XArgs {
     const uint32_t *ready;
     const int32_t *need;
     int group_size;
-    const int32_t *tile_bounds;         // optional: this launch covers tiles [tile_bounds[g], tile_bounds[g+1])
-    int tile_group;
     // gate/up on one GPU: token row i of the permuted order is row gather_rows[i] of gather_src
     const __nv_bfloat16 *gather_src;
     const int32_t *gather_rows;
-    // down with expert parallelism: row i goes to rank (rowinfo[i] >> 20), row (rowinfo[i] & 0xfffff) of ret[rank]
+    // expert parallelism (pe.world > 1).  Down: result row i goes to row (rowinfo[i] & 0xfffff) of
+    // pe.dret[rowinfo[i] >> 20], the buffer of the rank the token came from.  Gate/up with copy
+    // warps: the spare warps send this rank's token rows (row rowmap[r] of disp_src for permuted
+    // row r) to the owners of their experts while the other warps compute.
+    omni_ep_peers pe;
     const int32_t *rowinfo;
-    __nv_bfloat16 *ret[OMNI_EP_MAX];
+    const uint4 *disp_src;
+    const int32_t *disp_rowmap, *disp_offsets, *disp_send_base;
     int early_dependents;
 };
 
@@ -237,9 +255,9 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // (token tile, weight block) claimed one at a time from a device counter by the first CTA of the
 // pair, which hands each decoded item to the consumers of BOTH CTAs through a small ring that
 // exists in each CTA's shared memory.
-template <int MODE, int CTAS>
-__global__ void __launch_bounds__(X_THREADS, 1)
-expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ XTokMaps tm_tok, const XArgs a) {
+template <int MODE, int CTAS, bool COPY>
+__global__ void __launch_bounds__(X_THREADS + (COPY ? X_COPY_THREADS : 0), 1)
+expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ XTokMaps tm_tok, const __grid_constant__ XArgs a) {
     using C = XCfg<MODE, CTAS>;
     using M = XMode<MODE>;
     constexpr int KSTAGES = M::KTOT / BK;
@@ -281,7 +299,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const Abort ab{abort_flag, PAIR ? mapa_u32(misc_u32 + 4, rank ^ 1u) : 0u, a.status};
     // a barrier of the pair's first CTA, as an address every CTA of the pair may signal
     auto lead = [&](uint32_t bar) { return PAIR ? mapa_u32(bar, 0) : bar; };
-    auto arrive_lead = [&](uint32_t bar) { if (PAIR) mbar_arrive_cluster(mapa_u32(bar, 0)); else mbar_arrive(bar); };
+    auto arrive_lead = [&](uint32_t bar) { if (PAIR) mbar_arrive_remote(mapa_u32(bar, 0)); else mbar_arrive(bar); };
 
     if (threadIdx.x == 0) {
         const int tp = gathering ? 2 : 1;                       // arrivals of a CTA's token producer per item
@@ -311,8 +329,8 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int work_lo = a.tile_bounds ? a.tile_bounds[a.tile_group] * MI : 0;
-    const int n_work = a.tile_bounds ? min(a.tile_bounds[a.tile_group + 1], *a.n_ttiles) * MI : *a.n_ttiles * MI;
+    const int work_lo = 0;
+    const int n_work = *a.n_ttiles * MI;
 
     // weight tile of CTA `rank` for block m of an expert, K slab ks
     auto load_weights = [&](uint32_t dst, int expert, int m, int ks, uint32_t bar, uint64_t pol) {
@@ -388,7 +406,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const uint64_t pol_w = l2_policy_evict_first();
         bool ok = true;
         while (ok) {
-            ok = xwait<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
+            ok = xwait_item<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
             if (!ok) break;
             const int expert = ring[wr.stage].expert, len = ring[wr.stage].len, m = ring[wr.stage].m;
             arrive_lead(iempty_bar(wr.stage));
@@ -419,7 +437,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         PipeState p, pend, wr;
         int off[NR], off_next[NR];
         auto next_item = [&](int (&o)[NR]) -> int {
-            if (!xwait<CTAS>(ifull_bar(wr.stage), wr.phase, ab)) return -1;
+            if (!xwait_item<CTAS>(ifull_bar(wr.stage), wr.phase, ab)) return -1;
             const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len;
             __syncwarp();
             if (lane == 0) arrive_lead(iempty_bar(wr.stage));
@@ -474,7 +492,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         int ready_group = -1;
         bool ok = true;
         while (ok) {
-            ok = xwait<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
+            ok = xwait_item<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
             if (!ok) break;
             const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, expert = ring[wr.stage].expert;
             arrive_lead(iempty_bar(wr.stage));
@@ -518,7 +536,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         PipeState pw, pt, wr;
         bool ok = true;
         for (int it = 0; ok; it++) {
-            ok = xwait<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
+            ok = xwait_item<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
             if (!ok) break;
             const int len = ring[wr.stage].len;
             mbar_arrive(iempty_bar(wr.stage));
@@ -555,7 +573,17 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const uint64_t t0 = globaltimer_ns();
             while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
         }
-    } else if (warp >= 4) {
+    } else if (COPY && warp >= 12) {
+        // ---------------------------------------------------------- dispatch of this rank's token rows
+        // (expert parallelism): plain peer stores into the owners' buffers, group by group, each
+        // group announced on the owner's arrival counter -- which the token producers above,
+        // here and on the other ranks, wait for.  Virtual block = the copy warps of one CTA.
+        const int nvb = (int)gridDim.x - (int)gridDim.x % a.pe.world;
+        if ((int)blockIdx.x < nvb)
+            ep_dispatch_rows<true>(a.pe, a.disp_src, a.disp_rowmap, a.disp_offsets, a.disp_send_base, (int)blockIdx.x, nvb,
+                                   warp - 12, X_COPY_THREADS / 32, lane, threadIdx.x == X_THREADS,
+                                   [] { named_bar_sync(3, X_COPY_THREADS); });
+    } else if (warp >= 4 && warp < 12) {
         // ---------------------------------------------------------- epilogue: TMEM -> registers -> shared -> HBM
         // Each half stages its token rows in its own 128 rows of the shared-memory tile (which rows
         // of an item fall to which half changes from item to item, and the halves do not wait for
@@ -569,7 +597,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         PipeState wr;
         for (int it = 0;; it++) {
             int row0 = 0, len = 0, m = 0;
-            bool got = xwait<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
+            bool got = xwait_item<CTAS>(ifull_bar(wr.stage), wr.phase, ab);
             if (got) {
                 row0 = ring[wr.stage].row0; len = ring[wr.stage].len; m = ring[wr.stage].m;
                 __syncwarp();
@@ -623,7 +651,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 __nv_bfloat16 *dst_row;
                 if (MODE == X_DOWN && a.rowinfo) {
                     const int info = __ldg(a.rowinfo + row0 + r);
-                    dst_row = a.ret[info >> 20] + (long)(info & 0xfffff) * M::OUT_COLS;
+                    dst_row = reinterpret_cast<__nv_bfloat16 *>(a.pe.dret[info >> 20]) + (long)(info & 0xfffff) * M::OUT_COLS;
                 } else {
                     dst_row = a.out + (long)(row0 + r) * M::OUT_COLS;
                 }
@@ -656,13 +684,13 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 // ====================================================================== launchers
 namespace {
 
-template <int MODE, int CTAS>
+template <int MODE, int CTAS, bool COPY>
 cudaError_t launch_pair(const CUtensorMap *tm_w, const CUtensorMap *tm_tok4, const XArgs &args, int n_sm, cudaStream_t s) {
     XTokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_tok4[i];
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(n_sm - n_sm % CTAS));
-    cfg.blockDim = dim3(X_THREADS);
+    cfg.blockDim = dim3(X_THREADS + (COPY ? X_COPY_THREADS : 0));
     cfg.dynamicSmemBytes = XCfg<MODE, CTAS>::TOTAL_BYTES;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
@@ -679,7 +707,12 @@ cudaError_t launch_pair(const CUtensorMap *tm_w, const CUtensorMap *tm_tok4, con
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, expert_pair_kernel<MODE, CTAS>, *tm_w, tok, args);
+    return cudaLaunchKernelEx(&cfg, expert_pair_kernel<MODE, CTAS, COPY>, *tm_w, tok, args);
+}
+
+template <int MODE, int CTAS, bool COPY>
+cudaError_t set_smem() {
+    return cudaFuncSetAttribute(expert_pair_kernel<MODE, CTAS, COPY>, cudaFuncAttributeMaxDynamicSharedMemorySize, XCfg<MODE, CTAS>::TOTAL_BYTES);
 }
 
 }  // namespace
@@ -688,38 +721,41 @@ extern "C" {
 
 cudaError_t omni_expert_configure(void) {
     cudaError_t e;
-    e = cudaFuncSetAttribute(expert_pair_kernel<X_GATEUP, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, XCfg<X_GATEUP, 1>::TOTAL_BYTES);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(expert_pair_kernel<X_GATEUP, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, XCfg<X_GATEUP, 2>::TOTAL_BYTES);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(expert_pair_kernel<X_DOWN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, XCfg<X_DOWN, 1>::TOTAL_BYTES);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(expert_pair_kernel<X_DOWN, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, XCfg<X_DOWN, 2>::TOTAL_BYTES);
+    if ((e = set_smem<X_GATEUP, 1, false>()) != cudaSuccess) return e;
+    if ((e = set_smem<X_GATEUP, 2, false>()) != cudaSuccess) return e;
+    if ((e = set_smem<X_GATEUP, 1, true>()) != cudaSuccess) return e;
+    if ((e = set_smem<X_GATEUP, 2, true>()) != cudaSuccess) return e;
+    if ((e = set_smem<X_DOWN, 1, false>()) != cudaSuccess) return e;
+    return set_smem<X_DOWN, 2, false>();
 }
 
 cudaError_t omni_launch_gateup_pair(int ctas, const CUtensorMap *tm_w3, const CUtensorMap *tm_x4, const omni_sort_state st,
                                     void *h, const uint32_t *ready, const int32_t *need, int group_size,
-                                    const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
+                                    const void *gather_src, const int32_t *gather_rows, const omni_ep_peers *dispatch_to,
+                                    const void *disp_src, const int32_t *send_base, int early_dependents, int n_sm,
                                     cudaStream_t s) {
     XArgs a = {};
     a.ttiles = st.ttiles; a.n_ttiles = st.n_ttiles; a.work_counter = st.sched; a.out = (__nv_bfloat16 *)h; a.status = st.status;
     a.ready = ready; a.need = need; a.group_size = group_size > 0 ? group_size : 1;
     a.gather_src = (const __nv_bfloat16 *)gather_src; a.gather_rows = gather_rows;
     a.early_dependents = early_dependents;
-    return ctas == 2 ? launch_pair<X_GATEUP, 2>(tm_w3, tm_x4, a, n_sm, s) : launch_pair<X_GATEUP, 1>(tm_w3, tm_x4, a, n_sm, s);
+    if (dispatch_to) {
+        a.pe = *dispatch_to;
+        a.disp_src = (const uint4 *)disp_src; a.disp_rowmap = st.rowmap; a.disp_offsets = st.offsets; a.disp_send_base = send_base;
+        return ctas == 2 ? launch_pair<X_GATEUP, 2, true>(tm_w3, tm_x4, a, n_sm, s) : launch_pair<X_GATEUP, 1, true>(tm_w3, tm_x4, a, n_sm, s);
+    }
+    return ctas == 2 ? launch_pair<X_GATEUP, 2, false>(tm_w3, tm_x4, a, n_sm, s) : launch_pair<X_GATEUP, 1, false>(tm_w3, tm_x4, a, n_sm, s);
 }
 
 cudaError_t omni_launch_down_pair(int ctas, const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                  void *d, const int32_t *tile_bounds, int group, const int32_t *rowinfo, void *const *ret,
-                                  int early_dependents, int n_sm, cudaStream_t s) {
+                                  void *d, const omni_ep_peers *return_to, const int32_t *rowinfo, int early_dependents, int n_sm,
+                                  cudaStream_t s) {
     XArgs a = {};
-    a.ttiles = st.ttiles; a.n_ttiles = st.n_ttiles; a.work_counter = st.sched + 1 + (tile_bounds ? group : 0);
+    a.ttiles = st.ttiles; a.n_ttiles = st.n_ttiles; a.work_counter = st.sched + 1;
     a.out = (__nv_bfloat16 *)d; a.status = st.status; a.group_size = 1;
-    a.tile_bounds = tile_bounds; a.tile_group = group;
-    a.rowinfo = rowinfo;
-    if (rowinfo) for (int r = 0; r < OMNI_EP_MAX; r++) a.ret[r] = (__nv_bfloat16 *)ret[r];
+    if (return_to) { a.pe = *return_to; a.rowinfo = rowinfo; }
     a.early_dependents = early_dependents;
-    return ctas == 2 ? launch_pair<X_DOWN, 2>(tm_w, tm_h4, a, n_sm, s) : launch_pair<X_DOWN, 1>(tm_w, tm_h4, a, n_sm, s);
+    return ctas == 2 ? launch_pair<X_DOWN, 2, false>(tm_w, tm_h4, a, n_sm, s) : launch_pair<X_DOWN, 1, false>(tm_w, tm_h4, a, n_sm, s);
 }
 
 }  // extern "C"

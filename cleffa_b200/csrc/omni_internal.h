@@ -77,7 +77,6 @@ enum { OMNI_EP_SYNC_WORD = 16, OMNI_EP_READY_WORD = 64, OMNI_EP_FLAG_WORDS = 64 
 __host__ __device__
 #endif
 static inline int omni_ep_group_size(int world) { const int el = OMNI_E / world; return el >= 4 ? el / 4 : 1; }
-enum { OMNI_EP_RET_GROUPS = 4 };   /* the down product runs as this many launches so that results travel back under it */
 
 /* ---- plain kernels (omni_kernels.cu) ---- */
 cudaError_t omni_launch_router_simple(const void *xn, const void *router, const float *bias, int T,
@@ -146,24 +145,26 @@ cudaError_t omni_expert_configure(void);  /* opt-in shared-memory sizes; call on
  * omni_launch_gateup_sm100. */
 cudaError_t omni_launch_gateup_pair(int ctas, const CUtensorMap *tm_w3, const CUtensorMap *tm_x4, const omni_sort_state st,
                                     void *h, const uint32_t *ready, const int32_t *need, int group_size,
-                                    const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
+                                    const void *gather_src, const int32_t *gather_rows, const omni_ep_peers *dispatch_to,
+                                    const void *disp_src, const int32_t *send_base, int early_dependents, int n_sm,
                                     cudaStream_t s);
-/* rowinfo/ret (may be NULL): expert parallelism -- result row i is written to row
- * (rowinfo[i] & 0xfffff) of ret[rowinfo[i] >> 20] (the buffer of the rank the token came from)
- * instead of row i of d */
+/* dispatch_to (may be NULL): expert parallelism -- four more warps per CTA send this rank's token
+ * rows (rows st.rowmap[r] of disp_src, destinations from send_base) to the owners of their experts
+ * and announce them on the owners' arrival counters, which `ready`/`need` of every rank wait for.
+ * return_to/rowinfo (may be NULL): result row i is written to row (rowinfo[i] & 0xfffff) of
+ * return_to->dret[rowinfo[i] >> 20] (the rank the token came from) instead of row i of d */
 cudaError_t omni_launch_down_pair(int ctas, const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                  void *d, const int32_t *tile_bounds, int group, const int32_t *rowinfo, void *const *ret,
-                                  int early_dependents, int n_sm, cudaStream_t s);
+                                  void *d, const omni_ep_peers *return_to, const int32_t *rowinfo, int early_dependents, int n_sm,
+                                  cudaStream_t s);
 
 /* Programmatic dependent launch of the pass's kernel chain (process-wide, default on) */
 void omni_set_dependent_launch(int on);
 int omni_dependent_launch_enabled(void);
 
 /* ---- expert parallel (omni_ep.cu) ---- */
-/* ret_bounds: [2][RET_GROUPS+1] tile bounds, then row bounds, of the groups the down product is launched in */
 /* limit_ns = 0 (here and below): the default bound of 2 s on the wait for the other ranks */
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, int32_t *need, int32_t *ret_bounds, uint64_t limit_ns, cudaStream_t s);
+                                int32_t *n_local_rows, int32_t *need, uint64_t limit_ns, cudaStream_t s);
 /* realignment barrier: result[0] = agreed sync count, result[1] = agreed epoch (written on success only) */
 cudaError_t omni_launch_ep_sync(const omni_ep_peers *pe, uint32_t count, uint32_t epoch, uint32_t *status, uint32_t *result,
                                 uint64_t limit_ns, cudaStream_t s);
@@ -171,10 +172,6 @@ cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint
                                    cudaStream_t s);
 cudaError_t omni_launch_ep_dispatch(const omni_ep_peers *pe, const void *xn, const int32_t *rowmap, const int32_t *offsets,
                                     const int32_t *send_base, int rows8, int signal, int n_sm, cudaStream_t s);
-/* rows [row_bounds[group], row_bounds[group_end]) */
-cudaError_t omni_launch_ep_return(const omni_ep_peers *pe, const void *d, const int32_t *rowinfo,
-                                  const int32_t *row_bounds, int group, int group_end, int n_sm, cudaStream_t s);
-
 #ifdef __cplusplus
 }
 #endif

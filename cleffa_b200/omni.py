@@ -36,7 +36,7 @@ EXPORTS = [
     "clef_omni_stage_route", "clef_omni_stage_assign", "clef_omni_stage_experts", "clef_omni_read",
     "clef_omni_set_option", "clef_omni_profile", "clef_omni_arena_bytes",
     "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
-    "clef_omni_assign_noalloc", "clef_omni_ep_gate", "clef_omni_ep_sync",
+    "clef_omni_assign_noalloc", "clef_omni_ep_sync",
     "clef_omni_bind_norm", "clef_omni_encode_norm_moe", "clef_omni_bind_gguf", "clef_omni_gguf_check",
 ]
 NOALLOC_MAX_ROWS = 4096
@@ -74,7 +74,6 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_ep_connect": (C.c_bool, [vp, ci, ci, vp, cc, cz]),
         "clef_omni_ep_connect_local": (C.c_bool, [vp, ci, ci, C.POINTER(vp), cc, cz]),
         "clef_omni_ep_disconnect": (None, [vp]),
-        "clef_omni_ep_gate": (C.c_bool, [vp, vp, vp]),
         "clef_omni_ep_sync": (C.c_bool, [vp, ci, cc, cz]),
         "clef_omni_assign_noalloc": (C.c_bool, [vp, ci, vp, vp, vp, vp, vp, vp, cc, cz]),
         "clef_omni_bind_norm": (C.c_bool, [vp, ci, vp, C.c_float, ci, cc, cz]),
@@ -295,11 +294,6 @@ class OmniBackend:
     def ep_sync(self, timeout_ms: int = 20000):
         """Barrier across the ranks (every rank must call it), waited for on the host."""
         self._check(self.lib.clef_omni_ep_sync(self._g, timeout_ms, self._err, _ERRLEN))
-
-    def ep_gate(self, wait_event: int | None, record_event: int | None):
-        """cudaEvent_t handles (ints) the dispatch phase waits on / records; None for none."""
-        self.lib.clef_omni_ep_gate(self._g, C.c_void_p(wait_event) if wait_event else None,
-                                   C.c_void_p(record_event) if record_event else None)
 
     def ep_disconnect(self):
         self.lib.clef_omni_ep_disconnect(self._g)

@@ -154,7 +154,9 @@ bool clef_omni_gguf_check(const char *path, int n_layer, int H, int ffn, int n_e
 
 /* The 128 experts are sharded in contiguous ranges of 128/world per rank; tokens stay with the
  * rank that owns them.  Rows travel by peer stores into buffers each rank exports to the others
- * (CUDA IPC between processes, direct peer access inside one process).  Order of calls on
+ * (CUDA IPC between processes, direct peer access inside one process), written by the expert
+ * kernels themselves while they compute.  One context per GPU takes part: the kernels of a pass
+ * wait for rows from the other ranks, so two contexts of one GPU could wait on each other.  Order of calls on
  * every rank: open, reserve, ep_export, [exchange handles], ep_connect, bind_layer, then
  * begin / encode_moe / complete as usual; every rank must make the same sequence of encode_moe
  * calls (T <= 16384 per call, T may differ per rank).  After connect:
@@ -182,14 +184,6 @@ void clef_omni_ep_disconnect(clef_gpu *g);
  * 131072 expert rows from all ranks together are routed to the experts of one rank -- with
  * evenly spread routing that is 16384 tokens per rank, with skewed routing fewer. */
 bool clef_omni_ep_sync(clef_gpu *g, int timeout_ms, char *err, size_t errlen);
-/* Overlap of transfers and expert products is the host's choice: drive two (or more) contexts
- * per GPU on separate streams, each with a share of the rank's tokens (micro-batches), all
- * bound to one device copy of the weights.  To keep their phases staggered instead of in
- * lock-step, a context can wait on `wait_event` (a cudaEvent_t, may be NULL) before its
- * dispatch phase and record `record_event` (may be NULL) after it; chain the contexts of a GPU
- * in a ring with these.  The events stay owned by the caller. */
-bool clef_omni_ep_gate(clef_gpu *g, void *wait_event, void *record_event);
-
 /* ---- stage entry points (model-free tests, mirroring tests/test_omni_*.m) ---------- */
 
 /* omni_router (clef.metal:2330-2345): logits[t][e] as FP64 sums of exact BF16 products. */
@@ -243,8 +237,12 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
 /* Options: "debug_poison" 0/1 (CLEF_DEBUG_POISON), "router_exact" 0/1 (decide every row with
  * FP64 logits), "router_eps" (bound on the tensor-core logit error, x1e-9), "gemm" 0 =
  * tcgen05 kernels, 1 = plain CUDA-core check kernels, "router" likewise, "profile" 0/1,
- * "ep_overlap" 0/1 (expert parallelism: run the transfers under the expert kernels instead of
- * between them; same results; must be the same on every rank, as it changes the number of barriers per pass),
+ * "ep_fused" 0/1 (expert parallelism, default 1: the expert kernels move the rows themselves -- the
+ * gate/up kernel's spare warps send the token rows while it computes, the down kernel writes its
+ * results straight to the ranks they belong to; 0: a copy kernel and a barrier in front of the
+ * gate/up kernel; same results; must be the same on every rank, as it changes the number of barriers per pass),
+ * "expert_kernel" 0/1/2 (2: expert products on pairs of CTAs, tcgen05.mma.cta_group::2; 1: the same
+ * kernel on single CTAs; 0: the earlier single-CTA kernels; same results),
  * "ep_wait_ms" N (bound on each in-pass wait for other ranks, 0 = 2000), "reserve_sms" N (the persistent expert kernels use all SMs but N, so that kernels of another
  * context on the same GPU -- another micro-batch -- are not locked out while they run),
  * "fused_gather" 0/1 (default 1: the gate/up kernel fetches its token rows through the permutation

@@ -26,13 +26,14 @@ def run_single(weights, x, bias=None):
         return out.cpu(), b.read("ids", x.shape[0])
 
 
-def run_sharded(weights, x, splits, bias=None, passes=1, overlap=False):
+def run_sharded(weights, x, splits, bias=None, passes=1, fused=True, ctas=2):
     world = len(splits)
     backends = [OmniBackend(r) for r in range(world)]
     try:
         for b in backends:
             b.reserve(1)
-            b.set_option("ep_overlap", int(overlap))
+            b.set_option("ep_fused", int(fused))
+            b.set_option("expert_kernel", ctas)
         for r, b in enumerate(backends):
             b.ep_connect_local(r, world, backends)
         for b in backends:
@@ -57,12 +58,14 @@ def run_sharded(weights, x, splits, bias=None, passes=1, overlap=False):
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("overlap", [False, True])
+@pytest.mark.parametrize("fused,ctas", [(True, 2), (False, 2), (True, 1)])
 @pytest.mark.parametrize("splits", [(300, 212), (1, 511), (2048, 2048)])
-def test_two_ranks_equal_single_gpu_bitwise(weights0, splits, overlap):
+def test_two_ranks_equal_single_gpu_bitwise(weights0, splits, fused, ctas):
+    """fused: the expert kernels send and return the rows themselves; not fused: a copy kernel and
+    a barrier in front of them.  Either way, on CTA pairs or single CTAs, the bytes of one GPU."""
     x = orc.make_activations(60 + splits[0], sum(splits))
     want, _ = run_single(weights0, x)
-    got = run_sharded(weights0, x, splits, passes=2, overlap=overlap)   # second pass reuses every exchange buffer
+    got = run_sharded(weights0, x, splits, passes=2, fused=fused, ctas=ctas)   # second pass reuses every exchange buffer
     assert torch.equal(got, want)
 
 
