@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <type_traits>
 
 #include "omni_internal.h"
 #include "omni_ep_dev.cuh"
@@ -184,6 +185,17 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 
 // ------------------------------------------------------------------ configuration
 enum { X_GATEUP = 0, X_DOWN = 1 };
+#ifndef X_GU_WS
+#define X_GU_WS 7
+#define X_GU_TS 5
+#endif
+#ifndef X_DN_WS
+#define X_DN_WS 6
+#define X_DN_TS 4
+#endif
+#ifndef X_GATHER_LAG            /* stages between issuing a gathered stage and handing it to the MMA thread */
+#define X_GATHER_LAG 3
+#endif
 
 // ROWS: accumulator rows (weight rows) of one CTA; OUTC: output columns one CTA produces;
 // MT: such CTA-level weight tiles per expert.
@@ -197,8 +209,9 @@ template <int MODE, int CTAS> struct XCfg {
     static constexpr int T_BYTES = TOK_ROWS * BK * 2;                   // 32 KiB or 16 KiB
     static constexpr int W_BYTES = A_TILE_BYTES;                        // 16 KiB: 128 weight rows
     static constexpr int STAGE_OUT_BYTES = OMNI_TILE_N * M::OUTC * 2;   // 32 KiB (gate/up) or 64 KiB (down)
-    static constexpr int WS = CTAS == 2 ? 6 : 4;
-    static constexpr int TS = CTAS == 2 ? (MODE == X_GATEUP ? 5 : 4) : 3;
+    // ring depths (stages of 64 K elements): weights come from HBM, token rows mostly from L2
+    static constexpr int WS = CTAS == 2 ? (MODE == X_GATEUP ? X_GU_WS : X_DN_WS) : 4;
+    static constexpr int TS = CTAS == 2 ? (MODE == X_GATEUP ? X_GU_TS : X_DN_TS) : 3;
     static constexpr int RING_BYTES = WS * W_BYTES + TS * T_BYTES;
     static constexpr int TOTAL_BYTES = RING_BYTES + STAGE_OUT_BYTES + 1024 + 1024;
     static constexpr int ITEMS_PER_TILE = M::MT / CTAS;
@@ -426,7 +439,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // 128-byte-swizzled layout the MMA descriptors expect (chunk c of row r at c ^ (r & 7)
         // inside its 8-row group).  A stage is handed to the MMA thread two stages after it was
         // issued, once the copies have landed and are ordered before the tensor core's reads.
-        constexpr int LAG = 2;
+        constexpr int LAG = (CTAS == 2 && MODE == X_GATEUP) ? X_GATHER_LAG : 2;
         static_assert(TS > LAG, "token ring too short for the copy lag");
         constexpr int NR = C::TOK_ROWS / 8;
         const uint64_t pol_t = l2_policy_evict_last();
@@ -451,16 +464,20 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             }
             return len;
         };
+        // hands the oldest stage still in flight to the MMA thread once at most `left` newer ones are
+        auto hand_over = [&](auto left) {
+            cp_async_wait<decltype(left)::value>();
+            fence_proxy_async_smem();
+            arrive_lead(tfull_bar(pend.stage));
+            pend.advance(TS);
+        };
         int len = next_item(off);
         while (len >= 0) {
             bool ok = true;
             for (int ks = 0; ks < KSTAGES; ks++) {
-                if (ks >= LAG) {
-                    cp_async_wait<LAG - 1>();
-                    fence_proxy_async_smem();
-                    arrive_lead(tfull_bar(pend.stage));
-                    pend.advance(TS);
-                }
+                // hand over before blocking on a free stage: the MMA thread must never wait for
+                // this loop to issue further copies
+                if (ks >= LAG) hand_over(std::integral_constant<int, LAG - 1>{});
                 ok = xwait<CTAS>(tempty_bar(p.stage), p.phase ^ 1u, ab);
                 if (!ok) break;
                 const uint32_t sb = tok_base + p.stage * C::T_BYTES + dst_off;
@@ -472,15 +489,15 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 p.advance(TS);
             }
             if (!ok) break;
+            // the next item's row indices travel while the last stages of this one land
             len = next_item(off_next);
-            cp_async_wait<1>();
-            fence_proxy_async_smem();
-            arrive_lead(tfull_bar(pend.stage));
-            pend.advance(TS);
-            cp_async_wait<0>();
-            fence_proxy_async_smem();
-            arrive_lead(tfull_bar(pend.stage));
-            pend.advance(TS);
+            static_assert(LAG >= 1 && LAG <= 6, "copy lag");
+            if (LAG >= 6) hand_over(std::integral_constant<int, 5>{});
+            if (LAG >= 5) hand_over(std::integral_constant<int, 4>{});
+            if (LAG >= 4) hand_over(std::integral_constant<int, 3>{});
+            if (LAG >= 3) hand_over(std::integral_constant<int, 2>{});
+            if (LAG >= 2) hand_over(std::integral_constant<int, 1>{});
+            hand_over(std::integral_constant<int, 0>{});
 #pragma unroll
             for (int i = 0; i < NR; i++) off[i] = off_next[i];
         }

@@ -44,7 +44,9 @@ EP_HANDLES, EP_HANDLE_BYTES = 5, 64
 
 
 def load_library(path: Path | None = None) -> C.CDLL:
-    path = Path(path) if path else _LIB_PATH
+    """Loads the library: `path`, else the file named by CLEF_CUDA_OMNI_LIB, else the in-tree build."""
+    import os
+    path = Path(path) if path else Path(os.environ.get("CLEF_CUDA_OMNI_LIB") or _LIB_PATH)
     if not path.exists():
         raise OmniError(f"{path} is missing: build it with `python -m cleffa_b200.build` (there is no fallback path)")
     lib = C.CDLL(str(path))
