@@ -197,6 +197,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     }
     e = omni_sm100_configure();
     if (e == cudaSuccess) e = omni_expert_configure();
+    if (e == cudaSuccess) e = omni_router_configure();
     if (e != cudaSuccess) {
         set_err(err, errlen, "cuda: cannot configure sm_100a kernels: %s", cudaGetErrorString(e));
         if (g->own_stream) cudaStreamDestroy(g->stream);
@@ -288,7 +289,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         {(void **)&s->n_flag, 256},
         {(void **)&s->status, 256},
         {(void **)&s->sink, 256},
-        {(void **)&s->stamps, (size_t)(OMNI_CHUNK / 128) * 8 * 8},
+        {(void **)&s->stamps, (size_t)(OMNI_CHUNK / 32) * 8 * 8},
         {(void **)&s->sort.counts, (size_t)OMNI_E * 4},
         {(void **)&s->sort.offsets, (size_t)(OMNI_E + 1) * 4},
         {(void **)&s->sort.rowmap, (size_t)OMNI_ROWS * 4},
@@ -556,14 +557,15 @@ static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int row
     if (low && !launched(g, "capture reset", cudaMemsetAsync(low, 0, (size_t)rows * OMNI_E * 4, g->stream))) return false;
     if (g->router_impl == 0) {
         CUtensorMap tm_x;
-        if (!make_map(g, &tm_x, xn, (uint64_t)rows, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
+        const int nt = omni_router_tile(rows, g->n_sm);
+        if (!make_map(g, &tm_x, xn, (uint64_t)rows, OMNI_H, (uint32_t)nt, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
             note_failure(g, "router activation descriptor", cudaErrorInvalidValue);
             return false;
         }
         /* default: the router kernel also counts the experts per sort segment and the exact
          * pass moves the counts of the rows it re-decides, so no histogram kernel is launched */
         fused = g->fused_router != 0;
-        if (!launched(g, "router", omni_launch_router_sm100(&tm_x, &L->tm_router, L->bias, rows, g->router_eps, g->router_exact,
+        if (!launched(g, "router", omni_launch_router_sm100(&tm_x, nt, &L->tm_router, L->bias, rows, g->router_eps, g->router_exact,
                                                             s->logits, s->ids, s->weights, s->flag_rows, s->n_flag, s->status,
                                                             g->debug_stamps ? s->stamps : NULL, fused ? s->sort.segcount : NULL,
                                                             g->stream))) return false;
@@ -923,7 +925,7 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
     else if (!strcmp(what, "rechecked")) { src = s->n_flag; have = 4; }
     else if (!strcmp(what, "n_ttiles")) { src = s->sort.n_ttiles; have = 4; }
     else if (!strcmp(what, "xnorm") && g->xnorm) { src = g->xnorm; have = T * OMNI_H * 2; }
-    else if (!strcmp(what, "router_stamps")) { src = s->stamps; have = (size_t)(OMNI_CHUNK / 128) * 64; }
+    else if (!strcmp(what, "router_stamps")) { src = s->stamps; have = (size_t)(OMNI_CHUNK / 32) * 64; }
     if (!src || !dst || bytes > have || !bytes) { set_err(err, errlen, "cuda: unknown or oversized Omni read: %s", what); return false; }
     cudaError_t e = cudaStreamSynchronize(g->stream);
     if (e == cudaSuccess) e = cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost);

@@ -114,7 +114,11 @@ cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, i
 
 /* ---- tcgen05 kernels (omni_sm100.cu) ---- */
 cudaError_t omni_sm100_configure(void);   /* opt-in shared-memory sizes; call once per device */
-cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
+/* ---- router (omni_router.cu) ---- */
+cudaError_t omni_router_configure(void);
+int omni_router_tile(int T, int n_sm);     /* tokens per CTA: 32 while that gives at most one CTA per SM, else 128 */
+/* tm_x: the activations with a box of 64 K elements x nt rows (nt = omni_router_tile(T, n_sm)) */
+cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, int nt, const CUtensorMap *tm_w, const float *bias, int T,
                                      float eps, int exact_all, float *logits, int32_t *ids, float *weights,
                                      int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
                                      int32_t *segcount, cudaStream_t s);

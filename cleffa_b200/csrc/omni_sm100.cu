@@ -1,13 +1,9 @@
-// Tensor-core stages of the Clef-Omni MoE block, written for sm_100a only:
-//   * router_sm100_kernel   x[T][2048] . W_r[128][2048]^T on tcgen05 with the FP32 accumulator in
-//                           TMEM, fused with bias, nonfinite check, top-8 selection, renormalised
-//                           weights and the near-tie flagging that feeds the exact pass
-//                           (reference: metal/clef.metal:2330-2394, omni_router + omni_route),
-//                           and with the per-segment expert counts of the counting sort
-//                           (metal/clef.metal:2396-2410, omni_assign_count)
+// The two grouped expert products of the Clef-Omni MoE block on single CTAs (sm_100a, tcgen05
+// cta_group::1): the schedule used on one GPU.  omni_expert.cu holds the CTA-pair schedule that
+// also moves the rows of expert parallelism; omni_router.cu the router.
 //   * expert_gemm_kernel<GATEUP>  per expert: h = silu(Xe Wg^T) * (Xe Wu^T), SwiGLU in the epilogue
 //                           (reference: metal/clef.metal:2455-2492, omni_expert_gemm + omni_swiglu);
-//                           on one GPU the kernel also fetches the expert's token rows through
+//                           the kernel also fetches the expert's token rows through
 //                           the permutation itself (metal/clef.metal:2445-2453, omni_gather)
 //   * expert_gemm_kernel<DOWN>    per expert: d = He Wd^T            (clef.metal:2455-2482)
 //
@@ -464,238 +460,6 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-// ====================================================================== router
-// Top-9 of 128 per thread without data-dependent branches or predicates: logits become
-// order-preserving unsigned keys whose low 7 bits carry (127 - expert id); bitonic networks of
-// min/max sort eight groups of 16 and merge them, keeping the best 16 each time.  Equal values
-// order by lower id.  The 7 borrowed bits cost a relative 2^-16 in the comparison, which the
-// near-tie threshold accounts for; selected values are re-read at full precision afterwards.
-__device__ __forceinline__ void ce_desc(uint32_t &x, uint32_t &y) { const uint32_t hi = max(x, y), lo = min(x, y); x = hi; y = lo; }
-
-template <int OFF>
-__device__ __forceinline__ void sort16_desc(uint32_t (&k)[OMNI_E]) {
-#pragma unroll
-    for (int size = 2; size <= 16; size <<= 1)
-#pragma unroll
-        for (int stride = size >> 1; stride > 0; stride >>= 1)
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int l = i ^ stride;
-                if (l > i) {
-                    if ((i & size) == 0) ce_desc(k[OFF + i], k[OFF + l]);
-                    else ce_desc(k[OFF + l], k[OFF + i]);
-                }
-            }
-}
-
-// k[A..A+16) and k[B..B+16) sorted descending -> k[A..A+16) = their best 16, sorted descending
-template <int A, int B>
-__device__ __forceinline__ void merge_top16(uint32_t (&k)[OMNI_E]) {
-#pragma unroll
-    for (int i = 0; i < 16; i++) k[A + i] = max(k[A + i], k[B + 15 - i]);
-#pragma unroll
-    for (int stride = 8; stride > 0; stride >>= 1)
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const int l = i ^ stride;
-            if (l > i) ce_desc(k[A + i], k[A + l]);
-        }
-}
-
-constexpr int RT_STAGES = 6;
-constexpr int RT_STAGE_BYTES = 2 * A_TILE_BYTES;        // 128 token rows + 128 expert rows, 64 K each
-constexpr int RT_THREADS = 256;                         // warp 0 TMA, 1 MMA, 2 TMEM, 3 spare, 4..7 epilogue
-constexpr int RT_SMEM_BYTES = RT_STAGES * RT_STAGE_BYTES + 1024 + 256;
-
-__global__ void __launch_bounds__(RT_THREADS, 1)
-router_sm100_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                    const float *__restrict__ bias, int T, float eps, int exact_all, float *__restrict__ logits,
-                    int32_t *__restrict__ ids, float *__restrict__ weights, int32_t *__restrict__ flag_rows,
-                    int32_t *__restrict__ n_flag, uint32_t *__restrict__ status, unsigned long long *__restrict__ dbg,
-                    int32_t *__restrict__ segcount) {
-    constexpr int KSTAGES = OMNI_H / BK;
-    // optional per-CTA timestamps (ns): 0 start, 1 loads issued, 2 MMAs issued, 3 accumulator
-    // ready, 4 logits stored, 5 selection stored
-    auto stamp = [&](int i) { if (dbg) dbg[blockIdx.x * 8 + i] = globaltimer_ns(); };
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = smem_base + RT_STAGES * RT_STAGE_BYTES;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (RT_STAGES + s); };
-    const uint32_t tfull_bar = bar_base + 8u * (2 * RT_STAGES);
-    uint8_t *misc = smem_raw + (bar_base - smem_u32(smem_raw)) + 8 * (2 * RT_STAGES + 1);
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
-    volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);
-    // expert counts per warp [4][128], in pipeline stages that are idle by then (behind the
-    // 64 KiB of full-precision logits)
-    int *hist = reinterpret_cast<int *>(smem_raw + (smem_base - smem_u32(smem_raw)) + OMNI_E * 128 * 4);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * 128;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < RT_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); armed[s] = -1; }
-        mbar_init(tfull_bar, 1);
-        *abort_flag = 0;
-        fence_mbar_init();
-        prefetch_tmap(&tm_x);
-        prefetch_tmap(&tm_w);
-    }
-    if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 128); tmem_relinquish(); }
-    dep_wait();                 // everything above overlaps the tail of the previous kernel
-    dep_launch();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0 && lane == 0) {
-        PipeState p;
-        stamp(0);
-        for (int ks = 0; ks < KSTAGES; ks++) {
-            if (!mbar_wait(empty_bar(p.stage), p.phase ^ 1u, abort_flag, status)) break;
-            const uint32_t sa = smem_base + p.stage * RT_STAGE_BYTES;
-            armed[p.stage] = (int)p.phase;
-            mbar_expect_tx(full_bar(p.stage), RT_STAGE_BYTES);
-            tma_load_2d(sa, &tm_x, ks * BK, row0, full_bar(p.stage));             // rows past T read as zero
-            tma_load_2d(sa + A_TILE_BYTES, &tm_w, ks * BK, 0, full_bar(p.stage));
-            p.advance(RT_STAGES);
-        }
-        stamp(1);
-    } else if (warp == 1 && lane == 0) {
-        PipeState p;
-        const uint32_t idesc = idesc_bf16(128, OMNI_E);
-        bool ok = true;
-        for (int ks = 0; ks < KSTAGES; ks++) {
-            ok = mbar_wait(full_bar(p.stage), p.phase, abort_flag, status);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t sa = smem_base + p.stage * RT_STAGE_BYTES;
-            const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TILE_BYTES);
-#pragma unroll
-            for (int k = 0; k < BK / 16; k++) umma_bf16(tmem_base, da + 2u * k, db + 2u * k, idesc, (ks | k) ? 1u : 0u);
-            umma_commit(empty_bar(p.stage));
-            p.advance(RT_STAGES);
-        }
-        umma_commit(tfull_bar);
-        stamp(2);
-    } else if (warp >= 4) {
-        // One thread per token: its 128 logits sit in one TMEM lane.
-        const int q = warp & 3;
-        const long row = row0 + q * 32 + lane;
-        if (mbar_wait(tfull_bar, 0, abort_flag, status)) {
-            tc_fence_after();
-            if (threadIdx.x == 128) stamp(3);
-            float v[OMNI_E];
-            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t r[32];
-                tmem_ld32(t0 + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; j++) v[c * 32 + j] = __uint_as_float(r[j]);
-            }
-            if (bias) {
-#pragma unroll
-                for (int i = 0; i < OMNI_E; i++) v[i] += __ldg(bias + i);
-            }
-            if (row < T) {
-                float4 *lp = reinterpret_cast<float4 *>(logits + row * OMNI_E);
-                bool bad = false;
-#pragma unroll
-                for (int i = 0; i < OMNI_E / 4; i++) {
-                    lp[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                    bad |= !(fabsf(v[4 * i]) < CUDART_INF_F) || !(fabsf(v[4 * i + 1]) < CUDART_INF_F) ||
-                           !(fabsf(v[4 * i + 2]) < CUDART_INF_F) || !(fabsf(v[4 * i + 3]) < CUDART_INF_F);
-                }
-                if (threadIdx.x == 128) stamp(4);
-                int4 *ip = reinterpret_cast<int4 *>(ids + row * 8);
-                float4 *wp = reinterpret_cast<float4 *>(weights + row * 8);
-                if (bad) {
-                    atomicOr(status, OMNI_ST_NONFINITE);     // clef.metal:2362-2367
-                    ip[0] = make_int4(0, 1, 2, 3); ip[1] = make_int4(4, 5, 6, 7);
-                    wp[0] = make_float4(0.f, 0.f, 0.f, 0.f); wp[1] = wp[0];
-                } else {
-                    // keep the full-precision row in shared memory (the pipeline stages are
-                    // idle by now): column layout, so a thread's dynamic index never conflicts
-                    float *col = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
-                    const int et = threadIdx.x - 128;
-                    uint32_t key[OMNI_E];
-                    float max_abs = 0.f;
-#pragma unroll
-                    for (int i = 0; i < OMNI_E; i++) {
-                        col[i * 128 + et] = v[i];
-                        max_abs = fmaxf(max_abs, fabsf(v[i]));
-                        const uint32_t u = __float_as_uint(v[i]);
-                        const uint32_t ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-                        key[i] = (ord & ~127u) | (uint32_t)(127 - i);
-                    }
-                    sort16_desc<0>(key); sort16_desc<16>(key); sort16_desc<32>(key); sort16_desc<48>(key);
-                    sort16_desc<64>(key); sort16_desc<80>(key); sort16_desc<96>(key); sort16_desc<112>(key);
-                    merge_top16<0, 16>(key); merge_top16<32, 48>(key); merge_top16<64, 80>(key); merge_top16<96, 112>(key);
-                    merge_top16<0, 32>(key); merge_top16<64, 96>(key);
-                    merge_top16<0, 64>(key);
-                    float tv[9]; int ti[9];
-#pragma unroll
-                    for (int r = 0; r < 9; r++) { ti[r] = 127 - (int)(key[r] & 127u); tv[r] = col[ti[r] * 128 + et]; }
-                    // near-tie threshold: the row's assumed accumulation error (it grows with the
-                    // row's largest |logit|) plus what the borrowed key bits can hide
-                    const float thr = 2.f * omni_row_eps(eps, max_abs) + fmaxf(fabsf(tv[0]), fabsf(tv[8])) * 6.1035156e-5f;   // 2^-14
-                    bool close = exact_all != 0;
-#pragma unroll
-                    for (int k = 0; k < 8; k++) close |= (tv[k] - tv[k + 1]) < thr;
-                    float p[8], sum = 0.f;
-#pragma unroll
-                    for (int k = 0; k < 8; k++) { p[k] = expf(tv[k] - tv[0]); sum += p[k]; }
-                    const float inv = 1.f / sum;
-                    ip[0] = make_int4(ti[0], ti[1], ti[2], ti[3]); ip[1] = make_int4(ti[4], ti[5], ti[6], ti[7]);
-                    wp[0] = make_float4(p[0] * inv, p[1] * inv, p[2] * inv, p[3] * inv);
-                    wp[1] = make_float4(p[4] * inv, p[5] * inv, p[6] * inv, p[7] * inv);
-                    if (close) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
-                }
-                if (threadIdx.x == 128) stamp(5);
-            }
-        }
-        if (segcount) {
-            // Each warp's 32 tokens are one 256-assignment segment of the counting sort: count
-            // their experts here (the exact pass corrects the counts of the rows it changes).
-            int *h = hist + q * OMNI_E;
-#pragma unroll
-            for (int j = 0; j < 4; j++) h[lane + 32 * j] = 0;
-            __syncwarp();
-            if (row < T) {
-                const int4 a = *reinterpret_cast<const int4 *>(ids + row * 8), b = *reinterpret_cast<const int4 *>(ids + row * 8 + 4);
-                atomicAdd(h + a.x, 1); atomicAdd(h + a.y, 1); atomicAdd(h + a.z, 1); atomicAdd(h + a.w, 1);
-                atomicAdd(h + b.x, 1); atomicAdd(h + b.y, 1); atomicAdd(h + b.z, 1); atomicAdd(h + b.w, 1);
-            }
-            __syncwarp();
-            const int seg = blockIdx.x * 4 + q;
-            if (seg * OMNI_SEG < T * OMNI_TOP) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) segcount[(long)seg * OMNI_E + lane + 32 * j] = h[lane + 32 * j];
-            }
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (*abort_flag && threadIdx.x == 0) {
-        for (int s = 0; s < RT_STAGES; s++) {
-            const int par = armed[s];
-            if (par < 0) continue;
-            const uint64_t t0 = globaltimer_ns();
-            while (!mbar_try_wait(full_bar(s), (uint32_t)par) && globaltimer_ns() - t0 < 50000000ull) {}
-        }
-        // and the MMAs that may still be reading them
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(tfull_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {}
-    }
-    __syncthreads();
-    if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
-}
-
 }  // namespace
 
 // ====================================================================== launchers
@@ -708,16 +472,7 @@ cudaError_t omni_sm100_configure(void) {
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(expert_gemm_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GemmSmem<MODE_DOWN>::TOTAL_BYTES);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(router_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM_BYTES);
-}
-
-cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, const CUtensorMap *tm_w, const float *bias, int T,
-                                     float eps, int exact_all, float *logits, int32_t *ids, float *weights,
-                                     int32_t *flag_rows, int32_t *n_flag, uint32_t *status, unsigned long long *dbg,
-                                     int32_t *segcount, cudaStream_t s) {
-    return omni_launch_chain(router_sm100_kernel, dim3((T + 127) / 128), dim3(RT_THREADS), RT_SMEM_BYTES, s, *tm_x, *tm_w, bias, T,
-                             eps, exact_all, logits, ids, weights, flag_rows, n_flag, status, dbg, segcount);
+    return e;
 }
 
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
