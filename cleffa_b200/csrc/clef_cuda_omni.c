@@ -68,6 +68,7 @@ struct clef_gpu {
     int expert_kernel;                  /* tcgen05 expert products: 2 = pairs of CTAs (cta_group::2), 1 = the same kernel on
                                            single CTAs, 0 = the earlier single-CTA kernels (two accumulators for gate/up) */
     int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
+    int host_pieces;                    /* clef_omni_forward_host: pieces the batch is cut into (0 = chosen from T) */
     int fused_router;                   /* the router kernel counts experts per sort segment (no histogram kernel) */
     int fused_gather;                   /* gate/up fetches its token rows through rowmap (no gather kernel) */
     long alloc_fail_at, alloc_count;    /* host-side fault injection */
@@ -309,6 +310,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         else s->bytes += want[i].bytes;
     }
     s->sort.status = s->status;
+    s->sort.n_flag = s->n_flag;
     for (int i = 0; i < 4 && ok; i++)
         ok = make_map(g, &s->tm_xg[i], s->xg, OMNI_ROWS, OMNI_H, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
              make_map(g, &s->tm_h[i], s->h, OMNI_ROWS, OMNI_F, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
@@ -342,6 +344,8 @@ void clef_omni_begin(clef_gpu *g) {
     g->fail_msg[0] = 0;
     g->trace_valid = false;
     if (cudaMemsetAsync(s->status, 0, 4, g->stream) != cudaSuccess) note_failure(g, "status clear", cudaGetLastError());
+    /* a pass that failed between the router and the scan leaves its flagged-row count behind */
+    if (cudaMemsetAsync(s->n_flag, 0, 4, g->stream) != cudaSuccess) note_failure(g, "flag clear", cudaGetLastError());
     if (g->debug_poison) {
         /* clef_metal_omni.m:152-158: every float scratch buffer starts as NaN */
         poison(g, s->logits, (size_t)OMNI_CHUNK * OMNI_E * 4, 0x7fc00000u);
@@ -551,7 +555,8 @@ static bool run_router(clef_gpu *g, const omni_layer *L, const void *xn, int row
     omni_arena *s = g->omni;
     bool fused = false;
     *have_counts = false;
-    if (!launched(g, "flag reset", cudaMemsetAsync(s->n_flag, 0, 4, g->stream))) return false;
+    /* the flagged-row count is cleared by begin and, after each chunk, by the scan kernel: no
+     * memset node sits between the kernels of consecutive layers */
     /* the remainders of the exact logits are only read by route capture */
     float *low = g->trace ? s->logits_low : NULL;
     if (low && !launched(g, "capture reset", cudaMemsetAsync(low, 0, (size_t)rows * OMNI_E * 4, g->stream))) return false;
@@ -804,16 +809,25 @@ bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *
      * need xn; the FP32 residual is first touched by the combine and travels beside them.
      * With expert parallelism every rank must issue the same passes: one piece. */
     /* piece size: where a piece's kernels (0.19 ms of weight streaming + 0.06 us per token) take
-     * about as long as its upload (0.22 us per token): ~1400 tokens */
+     * about as long as its upload (0.22 us per token): ~1400 tokens.  What is left exposed at
+     * the end of the call is the last piece's kernels and its download, so the last piece gets
+     * half the tokens of the others. */
     int n_piece = g->ep.world > 1 || T <= 1536 ? 1 : (T + 1399) / 1400;
+    if (g->host_pieces > 0 && g->ep.world <= 1) n_piece = g->host_pieces;
     if (n_piece > HOST_PIECES) n_piece = HOST_PIECES;
-    int per = ((T + n_piece - 1) / n_piece + 127) & ~127;
-    if (g->ep.world > 1) per = T;
+    int cut[HOST_PIECES + 1];
+    cut[0] = 0;
+    {
+        const int unit = n_piece > 1 ? ((int)((2L * T) / (2 * n_piece - 1)) + 127) & ~127 : T;
+        for (int i = 1; i < n_piece; i++) cut[i] = cut[i - 1] + unit < T ? cut[i - 1] + unit : T;
+        cut[n_piece] = T;
+        while (n_piece > 1 && cut[n_piece - 1] >= T) n_piece--;      /* tiny batches: fewer pieces */
+    }
     clef_omni_begin(g);
     cudaError_t e = cudaSuccess;
     int n_used = 0;
-    for (int start = 0; start < T && e == cudaSuccess; start += per, n_used++) {
-        const size_t rows = (size_t)(T - start < per ? T - start : per), off = (size_t)start * OMNI_H;
+    for (; n_used < n_piece && e == cudaSuccess; n_used++) {
+        const size_t rows = (size_t)(cut[n_used + 1] - cut[n_used]), off = (size_t)cut[n_used] * OMNI_H;
         e = cudaMemcpyAsync((char *)g->stage_x + off * 2, (const char *)xn_host + off * 2, rows * OMNI_H * 2, cudaMemcpyHostToDevice, g->copy_stream);
         if (e == cudaSuccess) e = cudaEventRecord(g->ev_xn[n_used], g->copy_stream);
         if (e == cudaSuccess) e = cudaMemcpyAsync((float *)g->stage_res + off, x_host + off, rows * OMNI_H * 4, cudaMemcpyHostToDevice, g->copy_stream);
@@ -826,7 +840,7 @@ bool clef_omni_forward_host(clef_gpu *g, int layer, const void *xn_host, float *
     }
     bool encoded = true;
     for (int p = 0; p < n_used && encoded; p++) {
-        const int start = p * per, rows = T - start < per ? T - start : per;
+        const int start = cut[p], rows = cut[p + 1] - cut[p];
         const size_t off = (size_t)start * OMNI_H;
         e = cudaStreamWaitEvent(g->stream, g->ev_xn[p], 0);
         g->residual_uploaded = g->ev_res[p];
@@ -922,7 +936,7 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
     else if (!strcmp(what, "rowmap")) { src = s->sort.rowmap; have = T * OMNI_TOP * 4; }
     else if (!strcmp(what, "slots")) { src = s->sort.slots; have = T * OMNI_TOP * 4; }
     else if (!strcmp(what, "status")) { src = s->status; have = 4; }
-    else if (!strcmp(what, "rechecked")) { src = s->n_flag; have = 4; }
+    else if (!strcmp(what, "rechecked")) { src = s->n_flag + 1; have = 4; }
     else if (!strcmp(what, "n_ttiles")) { src = s->sort.n_ttiles; have = 4; }
     else if (!strcmp(what, "xnorm") && g->xnorm) { src = g->xnorm; have = T * OMNI_H * 2; }
     else if (!strcmp(what, "router_stamps")) { src = s->stamps; have = (size_t)(OMNI_CHUNK / 32) * 64; }
@@ -948,6 +962,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "dependent_launch")) omni_set_dependent_launch(value != 0);
     else if (!strcmp(name, "fused_router")) g->fused_router = value != 0;
     else if (!strcmp(name, "fused_gather")) g->fused_gather = value != 0;
+    else if (!strcmp(name, "host_pieces")) { if (value < 0 || value > HOST_PIECES) return false; g->host_pieces = (int)value; }
     else if (!strcmp(name, "reserve_sms")) { if (value < 0 || value >= g->n_sm) return false; g->reserve_sms = (int)value; }
     else if (!strcmp(name, "alloc_fail_at")) { g->alloc_fail_at = value; g->alloc_count = 0; }
     else if (!strcmp(name, "launch_fail_at")) { g->launch_fail_at = value; g->launch_count = 0; }

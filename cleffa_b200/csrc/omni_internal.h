@@ -56,6 +56,7 @@ typedef struct {
     int32_t *n_ttiles;     /* [1]                                     */
     int32_t *sched;        /* [8] work counters: [0] gate/up, [1..] down (one per launch group), zeroed by the scan */
     uint32_t *status;      /* [1]                                     */
+    int32_t *n_flag;       /* [2] rows flagged for the exact pass: the scan moves [0] to [1] and clears [0] for the next pass */
 } omni_sort_state;
 
 /* Expert parallelism: every rank's view of every rank's exchange buffers (index = rank). */

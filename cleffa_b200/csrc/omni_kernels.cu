@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) select_kernel(const float *__restrict__ l
 #pragma unroll
     for (int k = 0; k < 8; k++) close |= (top_v[k] - top_v[k + 1]) < 2.0 * bound;
     write_selection(top_v, top_id, lane, ids, weights, row);
-    if (close && lane == 0) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
+    if (close && lane == 0) { const int at = atomicAdd(n_flag, 1); if (at < OMNI_CHUNK) flag_rows[at] = (int32_t)row; }
 }
 
 // One block (four warps) per flagged row.
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(128) recheck_kernel(const __nv_bfloat16 *__res
     dep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int n = *n_flag;
-    if (n > T) n = T;
+    if (n > T) n = T;                  // a count left by a pass that failed half-way can be no larger than this
     for (int f = blockIdx.x; f < n; f += gridDim.x)
         recheck_row(xn, w, bias, logits, low, flag_rows[f], eps, ids, weights, segcount, status, exact_s, lane, warp, [] { __syncthreads(); });
 }
@@ -230,6 +230,9 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
             st.ttiles[first + j] = omni_ttile{e, off + j * base + min(j, extra), base + (j < extra), first | (nt << 16)};
         if (e < 8) st.sched[e] = 0;
         if (e == OMNI_E - 1) *st.n_ttiles = tiles_incl;
+        // the router and the exact pass of this chunk are done with the flagged-row count: keep it
+        // for introspection and clear it for the next router launch (no memset between passes)
+        if (e == 0 && st.n_flag) { st.n_flag[1] = st.n_flag[0]; st.n_flag[0] = 0; }
     }
 }
 
@@ -571,6 +574,7 @@ struct NoAllocScratch {
     omni_ttile ttiles[NOALLOC_MAX_ROWS * OMNI_TOP / OMNI_TILE_N + OMNI_E];
     int32_t n_ttiles, sched[8];
     uint32_t status;
+    int32_t n_flag[2];
 };
 static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
 // Device address of the array above, per device.  In host code the symbol's name is only a
@@ -605,6 +609,7 @@ cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, i
     st.counts = counts; st.offsets = offsets; st.rowmap = rowmap; st.slots = slots;
     st.segcount = sc->segcount; st.ttiles = sc->ttiles; st.n_ttiles = &sc->n_ttiles; st.sched = sc->sched;
     st.status = status;
+    st.n_flag = sc->n_flag;
     return omni_launch_assign(ids, rows, st, 0, s);
 }
 

@@ -263,7 +263,7 @@ router_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 ip[0] = make_int4(ti[0], ti[1], ti[2], ti[3]); ip[1] = make_int4(ti[4], ti[5], ti[6], ti[7]);
                 wp[0] = make_float4(p[0] * inv, p[1] * inv, p[2] * inv, p[3] * inv);
                 wp[1] = make_float4(p[4] * inv, p[5] * inv, p[6] * inv, p[7] * inv);
-                if (close) flag_rows[atomicAdd(n_flag, 1)] = (int32_t)row;
+                if (close) { const int at = atomicAdd(n_flag, 1); if (at < OMNI_CHUNK) flag_rows[at] = (int32_t)row; }
             }
         }
         if (threadIdx.x == 128) stamp(5);

@@ -182,7 +182,8 @@ def test_ranks_out_of_step_are_realigned_by_sync(weights0):
             bs[0].ep_sync(50)
         assert sync_both(bs) == [None, None]
         assert torch.equal(one_pass(bs, xs), want)
-        # the 6th launch of rank 0's pass fails on the host: rank 0 stops mid-pass
+        # the 6th launch of rank 0's pass (the down product) fails on the host: rank 0 stops mid-pass,
+        # after it has sent its rows but before it returns any result or joins the last barrier
         bs[0].set_option("launch_fail_at", 6)
         outs = [torch.zeros(300, 2048, device=f"cuda:{r}") for r in range(2)]
         for b in bs:

@@ -55,7 +55,7 @@ def test_failed_launch_surfaces_at_complete_and_next_pass_is_identical(bound0):
         b.begin(); b.encode_moe(0, x, out); b.complete()
         return out.cpu()
     good = run()
-    for n in (1, 2, 4, 6, 7):                 # first, mid and last of the seven launches of a pass
+    for n in (1, 2, 4, 6):                    # first, mid and last of the six host launches of a pass (the sort's kernels count as one)
         b.set_option("launch_fail_at", n)
         try:
             b.begin()
