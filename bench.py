@@ -48,8 +48,8 @@ KERNELS_PER_PASS = 7     # router (counts the sort segments), exact pass, scan, 
 KERNELS_PER_PASS_EP = 9  # ... plus plan and one barrier; the expert kernels dispatch and return the rows themselves
 METRIC = "MoE-layer prefill tokens/sec at T=4096"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at T=4096, from the ncu
-# capture summarised in profiles/ncu_full_router_experts_combine_T4096.md
-GATEUP_DRAM_TRAFFIC_T4096 = 964_327_424 + 43_772_928
+# capture summarised in profiles/ncu_full_moe_layer_T4096.md
+GATEUP_DRAM_TRAFFIC_T4096 = 973_841_920 + 43_667_712
 
 
 def measured_peaks():
