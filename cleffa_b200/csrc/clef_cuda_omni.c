@@ -99,6 +99,8 @@ struct clef_gpu {
         void *dret; int32_t *rowinfo, *counts, *send_base, *n_local_rows; uint32_t *flags;
         void *opened[OMNI_EP_MAX][OMNI_EP_BUFFERS];
         int32_t *need;                        /* [128] rows each group of local experts must receive */
+        /* de-duplicated dispatch: token -> (owner, group) buckets and where they land on the owners */
+        int32_t *tok_slot, *bucket_cnt, *bucket_list, *send_cnt, *recv_base, *grow;
     } ep;
     CUresult (*encode_tiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -346,6 +348,9 @@ void clef_omni_begin(clef_gpu *g) {
     if (cudaMemsetAsync(s->status, 0, 4, g->stream) != cudaSuccess) note_failure(g, "status clear", cudaGetLastError());
     /* a pass that failed between the router and the scan leaves its flagged-row count behind */
     if (cudaMemsetAsync(s->n_flag, 0, 4, g->stream) != cudaSuccess) note_failure(g, "flag clear", cudaGetLastError());
+    /* likewise the bucket counters of the expert-parallel dispatch (cleared by the plan kernel in a pass that gets that far) */
+    if (g->ep.world > 1 && cudaMemsetAsync(g->ep.bucket_cnt, 0, (size_t)OMNI_EP_BUCKETS * 4, g->stream) != cudaSuccess)
+        note_failure(g, "bucket clear", cudaGetLastError());
     if (g->debug_poison) {
         /* clef_metal_omni.m:152-158: every float scratch buffer starts as NaN */
         poison(g, s->logits, (size_t)OMNI_CHUNK * OMNI_E * 4, 0x7fc00000u);
@@ -599,7 +604,7 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
     if (g->gemm_impl == 0 && g->expert_kernel > 0) {
         const int ctas = g->expert_kernel;
         if (!launched(g, "gate/up experts", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
-                                                                    fused ? s->sort.rowmap : NULL, NULL, NULL, NULL, g->reserve_sms == 0,
+                                                                    fused ? s->sort.rowmap : NULL, NULL, NULL, g->reserve_sms == 0,
                                                                     g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
         if (!launched(g, "down experts", omni_launch_down_pair(ctas, &L->tm_down, s->tm_h, s->sort, s->d, NULL, NULL, g->reserve_sms == 0,
@@ -640,18 +645,24 @@ static bool run_experts_ep(clef_gpu *g, const omni_layer *L, const void *xn, con
     const omni_ep_peers *pe = &g->ep.peers;
     const int ctas = g->expert_kernel == 1 ? 1 : 2;
     const int n_gemm = g->n_sm - g->reserve_sms;
+    if (g->ep_fused && !launched(g, "expert-parallel buckets", omni_launch_ep_buckets(ids, rows, pe->world, g->ep.tok_slot, g->ep.bucket_cnt,
+                                                                                       g->ep.bucket_list, g->stream))) return false;
     if (!launched(g, "assign", omni_launch_assign(ids, rows, s->sort, have_counts, g->stream))) return false;
-    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.wait_ns, g->stream))) return false;
+    if (!launched(g, "expert-parallel plan", omni_launch_ep_plan(pe, ++g->ep.epoch, s->sort, g->ep.send_base, g->ep.n_local_rows, g->ep.need,
+                                                                 g->ep.bucket_cnt, g->ep.send_cnt, g->ep.recv_base, g->ep.wait_ns, g->stream))) return false;
     if (g->ep_fused) {
+        const omni_ep_send send = {g->ep.tok_slot, g->ep.bucket_list, g->ep.send_cnt, g->ep.recv_base, g->ep.send_base,
+                                   s->sort.rowmap, s->sort.offsets, xn};
         stage_mark(g, 2);
+        /* the token rows arrive once per source token in xg; the kernel gathers each expert's rows from there through grow */
         if (!launched(g, "gate/up experts + dispatch", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, pe->flags[pe->rank] + OMNI_EP_READY_WORD,
-                                                                               g->ep.need, omni_ep_group_size(pe->world), NULL, NULL, pe, xn, g->ep.send_base,
+                                                                               g->ep.need, omni_ep_group_size(pe->world), s->xg, g->ep.grow, pe, &send,
                                                                                g->reserve_sms == 0, n_gemm, g->stream))) return false;
     } else {
         if (!launched(g, "expert-parallel dispatch", omni_launch_ep_dispatch(pe, xn, s->sort.rowmap, s->sort.offsets, g->ep.send_base, rows8, 0, g->n_sm, g->stream))) return false;
         if (!launched(g, "expert-parallel barrier", omni_launch_ep_barrier(pe, ++g->ep.epoch, s->status, g->ep.wait_ns, g->stream))) return false;
         stage_mark(g, 2);
-        if (!launched(g, "gate/up experts", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, NULL, NULL, NULL,
+        if (!launched(g, "gate/up experts", omni_launch_gateup_pair(ctas, &L->tm_gate_up3, s->tm_xg, s->sort, s->h, NULL, NULL, 1, NULL, NULL, NULL, NULL,
                                                                     g->reserve_sms == 0, n_gemm, g->stream))) return false;
     }
     stage_mark(g, 3);
@@ -992,21 +1003,30 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
     if (g->ep.dret) return true;
     void *dret = dev_alloc(g, (size_t)OMNI_ROWS * OMNI_H * 2);
     int32_t *rowinfo = dev_alloc(g, (size_t)OMNI_ROWS * 4);
-    int32_t *counts = dev_alloc(g, (size_t)OMNI_EP_MAX * OMNI_E * 4);
+    int32_t *counts = dev_alloc(g, (size_t)OMNI_EP_MAX * OMNI_EP_COUNT_STRIDE * 4);
     uint32_t *flags = dev_alloc(g, (size_t)OMNI_EP_FLAG_WORDS * 4);
     int32_t *send_base = dev_alloc(g, (size_t)OMNI_E * 4);
     int32_t *n_local = dev_alloc(g, 256);
     int32_t *need = dev_alloc(g, (size_t)OMNI_E * 4);
     uint32_t *sync_result = dev_alloc(g, 256);
-    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && sync_result;
+    int32_t *tok_slot = dev_alloc(g, (size_t)OMNI_CHUNK * OMNI_EP_MAX * 4);
+    int32_t *bucket_cnt = dev_alloc(g, (size_t)OMNI_EP_BUCKETS * 4);
+    int32_t *bucket_list = dev_alloc(g, (size_t)OMNI_EP_BUCKETS * OMNI_CHUNK * 4);
+    int32_t *send_cnt = dev_alloc(g, (size_t)OMNI_EP_BUCKETS * 4);
+    int32_t *recv_base = dev_alloc(g, (size_t)OMNI_EP_BUCKETS * 4);
+    int32_t *grow = dev_alloc(g, (size_t)OMNI_ROWS * 4);
+    bool ok = dret && rowinfo && counts && flags && send_base && n_local && need && sync_result && tok_slot && bucket_cnt &&
+              bucket_list && send_cnt && recv_base && grow;
     if (ok) ok = cudaMemsetAsync(flags, 0, (size_t)OMNI_EP_FLAG_WORDS * 4, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(need, 0, (size_t)OMNI_E * 4, g->stream) == cudaSuccess &&
-                 cudaMemsetAsync(counts, 0, (size_t)OMNI_EP_MAX * OMNI_E * 4, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(counts, 0, (size_t)OMNI_EP_MAX * OMNI_EP_COUNT_STRIDE * 4, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(bucket_cnt, 0, (size_t)OMNI_EP_BUCKETS * 4, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(n_local, 0, 256, g->stream) == cudaSuccess &&
                  cudaStreamSynchronize(g->stream) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
-        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, sync_result};
+        void *all[] = {dret, rowinfo, counts, flags, send_base, n_local, need, sync_result, tok_slot, bucket_cnt, bucket_list, send_cnt,
+                       recv_base, grow};
         for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
         set_err(err, errlen, "cuda: cannot allocate Omni expert-parallel buffers (previous buffers kept)");
         return false;
@@ -1014,15 +1034,17 @@ static bool ep_alloc(clef_gpu *g, char *err, size_t errlen) {
     g->ep.dret = dret; g->ep.rowinfo = rowinfo; g->ep.counts = counts; g->ep.flags = flags;
     g->ep.send_base = send_base; g->ep.n_local_rows = n_local; g->ep.need = need;
     g->ep.sync_result = sync_result;
+    g->ep.tok_slot = tok_slot; g->ep.bucket_cnt = bucket_cnt; g->ep.bucket_list = bucket_list; g->ep.send_cnt = send_cnt;
+    g->ep.recv_base = recv_base; g->ep.grow = grow;
     return true;
 }
 
 static void ep_local_buffers(clef_gpu *g, void *out[OMNI_EP_BUFFERS]) {
-    out[0] = g->omni->xg; out[1] = g->ep.dret; out[2] = g->ep.rowinfo; out[3] = g->ep.counts; out[4] = g->ep.flags;
+    out[0] = g->omni->xg; out[1] = g->ep.dret; out[2] = g->ep.rowinfo; out[3] = g->ep.counts; out[4] = g->ep.flags; out[5] = g->ep.grow;
 }
 
 static void ep_set_peer(omni_ep_peers *pe, int r, void *const buf[OMNI_EP_BUFFERS]) {
-    pe->xg[r] = buf[0]; pe->dret[r] = buf[1]; pe->rowinfo[r] = buf[2]; pe->counts[r] = buf[3]; pe->flags[r] = buf[4];
+    pe->xg[r] = buf[0]; pe->dret[r] = buf[1]; pe->rowinfo[r] = buf[2]; pe->counts[r] = buf[3]; pe->flags[r] = buf[4]; pe->grow[r] = buf[5];
 }
 
 bool clef_omni_ep_export(clef_gpu *g, clef_omni_ipc_handle out[CLEF_OMNI_EP_HANDLES], char *err, size_t errlen) {
@@ -1148,7 +1170,8 @@ void clef_omni_ep_disconnect(clef_gpu *g) {
     if (g->ep.ipc)
         for (int r = 0; r < OMNI_EP_MAX; r++) for (int i = 0; i < OMNI_EP_BUFFERS; i++)
             if (g->ep.opened[r][i]) { cudaIpcCloseMemHandle(g->ep.opened[r][i]); g->ep.opened[r][i] = NULL; }
-    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.sync_result};
+    void *all[] = {g->ep.dret, g->ep.rowinfo, g->ep.counts, g->ep.flags, g->ep.send_base, g->ep.n_local_rows, g->ep.need, g->ep.sync_result,
+                   g->ep.tok_slot, g->ep.bucket_cnt, g->ep.bucket_list, g->ep.send_cnt, g->ep.recv_base, g->ep.grow};
     for (size_t i = 0; i < sizeof all / sizeof all[0]; i++) if (all[i]) cudaFree(all[i]);
     memset(&g->ep, 0, sizeof g->ep);
     cudaGetLastError();

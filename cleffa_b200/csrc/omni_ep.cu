@@ -86,15 +86,55 @@ __global__ void __launch_bounds__(32) ep_sync_kernel(omni_ep_peers pe, uint32_t 
     if (t == 0 && ok) { result[0] = c; result[1] = e; }
 }
 
+// Tokens -> buckets of the de-duplicated dispatch.  One thread per token: for every owner rank
+// the first (lowest) group of that owner's experts among the token's eight; the token takes the
+// next free position of the bucket (owner, group).  Positions are handed out by atomics, so the
+// order inside a bucket differs from run to run; it only names rows of the receive buffer.
+__global__ void __launch_bounds__(256) ep_bucket_kernel(const int32_t *__restrict__ ids, int T, int world,
+                                                        int32_t *__restrict__ tok_slot, int32_t *__restrict__ bucket_cnt,
+                                                        int32_t *__restrict__ bucket_list) {
+    const int t = blockIdx.x * 256 + threadIdx.x;
+    if (t >= T) return;
+    const int EL = OMNI_E / world, gsz = omni_ep_group_size(world);
+    const int4 a = *reinterpret_cast<const int4 *>(ids + (long)t * 8), b = *reinterpret_cast<const int4 *>(ids + (long)t * 8 + 4);
+    const int id[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int o = 0; o < OMNI_EP_MAX; o++) {
+        int g = OMNI_EP_GROUPS;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int e = id[k] & (OMNI_E - 1);
+            if (e / EL == o) g = min(g, (e % EL) / gsz);
+        }
+        int slot = -1;
+        if (g < OMNI_EP_GROUPS) {
+            const int bkt = o * OMNI_EP_GROUPS + g;
+            const int pos = atomicAdd(bucket_cnt + bkt, 1);
+            bucket_list[(long)bkt * OMNI_CHUNK + pos] = t;
+            slot = (g << 24) | pos;
+        }
+        tok_slot[(long)t * OMNI_EP_MAX + o] = slot;
+    }
+}
+
 // Publish my counts, barrier, then plan.  One block of 128 threads, thread e = expert e.
 __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint32_t epoch, omni_sort_state st,
                                                          int32_t *send_base, int32_t *n_local_rows, int32_t *need,
+                                                         int32_t *bucket_cnt, int32_t *send_cnt, int32_t *recv_base,
                                                          uint64_t limit_ns) {
     __shared__ int tot[OMNI_E], scan[OMNI_E], tiles[OMNI_E];
     const int e = threadIdx.x;
     const int G = pe.world, EL = OMNI_E / G;
     const int mine = st.counts[e];
-    for (int p = 0; p < G; p++) pe.counts[p][pe.rank * OMNI_E + e] = mine;
+    for (int p = 0; p < G; p++) pe.counts[p][pe.rank * OMNI_EP_COUNT_STRIDE + e] = mine;
+    // and, for the de-duplicated dispatch, how many tokens it sends per (owner, group) bucket; the
+    // counter is left at zero for the next pass
+    if (e < OMNI_EP_BUCKETS) {
+        const int c = bucket_cnt[e];
+        send_cnt[e] = c;
+        bucket_cnt[e] = 0;
+        for (int p = 0; p < G; p++) pe.counts[p][pe.rank * OMNI_EP_COUNT_STRIDE + OMNI_E + e] = c;
+    }
     // arrival counters of this rank's experts start at zero; peers add to them only after the barrier
     pe.flags[pe.rank][OMNI_EP_READY_WORD + e] = 0;
     flag_barrier(pe, epoch, st.status, limit_ns);
@@ -102,7 +142,7 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
     const int32_t *table = pe.counts[pe.rank];
     int total = 0, before_me = 0;
     for (int s = 0; s < G; s++) {
-        const int c = __ldcv(table + s * OMNI_E + e);     // written by peers: bypass L1
+        const int c = __ldcv(table + s * OMNI_EP_COUNT_STRIDE + e);     // written by peers: bypass L1
         if (s < pe.rank) before_me += c;
         total += c;
     }
@@ -115,6 +155,20 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
         int to_owner = 0;
         for (int o = e * EL; o < (e + 1) * EL; o++) to_owner += tot[o];
         if (to_owner > OMNI_ROWS) atomicOr(st.status, OMNI_ST_EP_OVERFLOW);
+    }
+    // bucket (owner o, group g): this rank's tokens follow those of lower groups from every rank
+    // and those of this group from lower ranks in the owner's receive buffer
+    if (e < OMNI_EP_BUCKETS) {
+        const int o = e / OMNI_EP_GROUPS, g = e % OMNI_EP_GROUPS;
+        int base = 0, all = 0;
+        for (int s = 0; s < G; s++)
+            for (int gg = 0; gg < OMNI_EP_GROUPS; gg++) {
+                const int c = __ldcv(table + s * OMNI_EP_COUNT_STRIDE + OMNI_E + o * OMNI_EP_GROUPS + gg);
+                all += c;
+                if (gg < g || (gg == g && s < pe.rank)) base += c;
+            }
+        recv_base[e] = base;
+        if (o < G && all > OMNI_ROWS) atomicOr(st.status, OMNI_ST_EP_OVERFLOW);
     }
     // base of expert e inside its owner's buffer: totals of the owner's earlier experts
     const int owner = e / EL, first = owner * EL;
@@ -164,14 +218,22 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(omni_ep_peers pe, cons
 extern "C" {
 
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, int32_t *need, uint64_t limit_ns, cudaStream_t s) {
-    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, limit_ns ? limit_ns : SPIN_LIMIT_NS);
+                                int32_t *n_local_rows, int32_t *need, int32_t *bucket_cnt, int32_t *send_cnt, int32_t *recv_base,
+                                uint64_t limit_ns, cudaStream_t s) {
+    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, bucket_cnt, send_cnt, recv_base,
+                                        limit_ns ? limit_ns : SPIN_LIMIT_NS);
     return cudaGetLastError();
 }
 
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
                                    cudaStream_t s) {
     ep_barrier_kernel<<<1, 128, 0, s>>>(*pe, epoch, status, limit_ns);
+    return cudaGetLastError();
+}
+
+cudaError_t omni_launch_ep_buckets(const int32_t *ids, int T, int world, int32_t *tok_slot, int32_t *bucket_cnt,
+                                   int32_t *bucket_list, cudaStream_t s) {
+    ep_bucket_kernel<<<(T + 255) / 256, 256, 0, s>>>(ids, T, world, tok_slot, bucket_cnt, bucket_list);
     return cudaGetLastError();
 }
 

@@ -246,8 +246,8 @@ struct XArgs {
     // row r) to the owners of their experts while the other warps compute.
     omni_ep_peers pe;
     const int32_t *rowinfo;
-    const uint4 *disp_src;
-    const int32_t *disp_rowmap, *disp_offsets, *disp_send_base;
+    omni_ep_send send;                  // what the copy warps send from
+    int need_blocks;                    // > 0: an arrival counter is complete at this value (it counts sender blocks), else at need[group]
     int early_dependents;
 };
 
@@ -449,18 +449,44 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const char *src0 = reinterpret_cast<const char *>(a.gather_src) + c * 16;
         PipeState p, pend, wr;
         int off[NR], off_next[NR];
+        int ready_group = -1;
         auto next_item = [&](int (&o)[NR]) -> int {
             if (!xwait_item<CTAS>(ifull_bar(wr.stage), wr.phase, ab)) return -1;
-            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len;
+            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, expert = ring[wr.stage].expert;
             __syncwarp();
             if (lane == 0) arrive_lead(iempty_bar(wr.stage));
             wr.advance(X_RING);
+            if (a.ready && len >= 0) {
+                // expert parallelism: the rows and the row map of this expert's group are written by
+                // other GPUs while the kernel runs; they are complete once the arrival counters of
+                // every group up to it are (a token row may have come with an earlier group)
+                const int grp = expert / a.group_size;
+                bool ok = true;
+                while (ready_group < grp && ok) {
+                    const int g2 = ready_group + 1;
+                    if (lane == 0) {
+                        const uint32_t want = a.need_blocks ? (uint32_t)a.need_blocks : (uint32_t)a.need[g2];
+                        const uint64_t t0 = globaltimer_ns();
+                        while (ld_acquire_sys_u32(a.ready + g2) != want) {
+                            __nanosleep(200);
+                            if (*abort_flag || globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                                ab.raise(OMNI_ST_TIMEOUT | OMNI_ST_TIMEOUT_ARRIVAL);
+                                ok = false;
+                                break;
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    ready_group = g2;
+                }
+                if (!ok) return -1;
+            }
             const int share = (((len + 15) & ~15) / CTAS);            // token rows of the tile each CTA stages
             const int first = (int)rank * share;
 #pragma unroll
             for (int i = 0; i < NR; i++) {
                 const int r = rb + 8 * i;
-                o[i] = (r < share && first + r < len) ? a.gather_rows[row0 + first + r] * (OMNI_H * 2) : -1;
+                o[i] = (r < share && first + r < len) ? __ldcv(a.gather_rows + row0 + first + r) * (OMNI_H * 2) : -1;
             }
             return len;
         };
@@ -519,7 +545,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 // expert parallelism: this expert's rows are being written by other GPUs while the
                 // kernel runs; wait (bounded, polling gently) until its whole group has arrived
                 const int grp = expert / a.group_size;
-                const uint32_t want = (uint32_t)a.need[grp];
+                const uint32_t want = a.need_blocks ? (uint32_t)a.need_blocks : (uint32_t)a.need[grp];
                 const uint64_t t0 = globaltimer_ns();
                 while (ld_acquire_sys_u32(a.ready + grp) != want) {
                     __nanosleep(500);
@@ -592,14 +618,14 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
     } else if (COPY && warp >= 12) {
         // ---------------------------------------------------------- dispatch of this rank's token rows
-        // (expert parallelism): plain peer stores into the owners' buffers, group by group, each
-        // group announced on the owner's arrival counter -- which the token producers above,
-        // here and on the other ranks, wait for.  Virtual block = the copy warps of one CTA.
+        // (expert parallelism): each token once per owner rank, plain peer stores into the owners'
+        // receive buffers, group by group, each group announced on the owner's arrival counter --
+        // which the token producers above, here and on the other ranks, wait for.  Virtual block =
+        // the copy warps of one CTA.
         const int nvb = (int)gridDim.x - (int)gridDim.x % a.pe.world;
         if ((int)blockIdx.x < nvb)
-            ep_dispatch_rows<true>(a.pe, a.disp_src, a.disp_rowmap, a.disp_offsets, a.disp_send_base, (int)blockIdx.x, nvb,
-                                   warp - 12, X_COPY_THREADS / 32, lane, threadIdx.x == X_THREADS,
-                                   [] { named_bar_sync(3, X_COPY_THREADS); });
+            ep_dispatch_dedup(a.pe, a.send, (int)blockIdx.x, nvb, warp - 12, X_COPY_THREADS / 32, lane, threadIdx.x == X_THREADS,
+                              [] { named_bar_sync(3, X_COPY_THREADS); });
     } else if (warp >= 4 && warp < 12) {
         // ---------------------------------------------------------- epilogue: TMEM -> registers -> shared -> HBM
         // Each half stages its token rows in its own 128 rows of the shared-memory tile (which rows
@@ -749,16 +775,17 @@ cudaError_t omni_expert_configure(void) {
 cudaError_t omni_launch_gateup_pair(int ctas, const CUtensorMap *tm_w3, const CUtensorMap *tm_x4, const omni_sort_state st,
                                     void *h, const uint32_t *ready, const int32_t *need, int group_size,
                                     const void *gather_src, const int32_t *gather_rows, const omni_ep_peers *dispatch_to,
-                                    const void *disp_src, const int32_t *send_base, int early_dependents, int n_sm,
-                                    cudaStream_t s) {
+                                    const omni_ep_send *send, int early_dependents, int n_sm, cudaStream_t s) {
     XArgs a = {};
     a.ttiles = st.ttiles; a.n_ttiles = st.n_ttiles; a.work_counter = st.sched; a.out = (__nv_bfloat16 *)h; a.status = st.status;
     a.ready = ready; a.need = need; a.group_size = group_size > 0 ? group_size : 1;
     a.gather_src = (const __nv_bfloat16 *)gather_src; a.gather_rows = gather_rows;
     a.early_dependents = early_dependents;
     if (dispatch_to) {
+        const int grid = n_sm - n_sm % ctas;
         a.pe = *dispatch_to;
-        a.disp_src = (const uint4 *)disp_src; a.disp_rowmap = st.rowmap; a.disp_offsets = st.offsets; a.disp_send_base = send_base;
+        a.send = *send;
+        a.need_blocks = grid - grid % dispatch_to->world;       // every rank launches the same grid
         return ctas == 2 ? launch_pair<X_GATEUP, 2, true>(tm_w3, tm_x4, a, n_sm, s) : launch_pair<X_GATEUP, 1, true>(tm_w3, tm_x4, a, n_sm, s);
     }
     return ctas == 2 ? launch_pair<X_GATEUP, 2, false>(tm_w3, tm_x4, a, n_sm, s) : launch_pair<X_GATEUP, 1, false>(tm_w3, tm_x4, a, n_sm, s);

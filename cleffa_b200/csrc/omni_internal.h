@@ -60,13 +60,15 @@ typedef struct {
 } omni_sort_state;
 
 /* Expert parallelism: every rank's view of every rank's exchange buffers (index = rank). */
-enum { OMNI_EP_MAX = 8, OMNI_EP_BUFFERS = 5 };
+enum { OMNI_EP_MAX = 8, OMNI_EP_BUFFERS = 6, OMNI_EP_GROUPS = 4, OMNI_EP_BUCKETS = OMNI_EP_MAX * OMNI_EP_GROUPS,
+       OMNI_EP_COUNT_STRIDE = OMNI_E + OMNI_EP_BUCKETS };   /* ints one rank publishes: expert counts, then bucket counts */
 typedef struct {
     int32_t rank, world;
     void *xg[OMNI_EP_MAX];          /* [ROWS][2048] bf16: token rows received, expert-major      */
     void *dret[OMNI_EP_MAX];        /* [ROWS][2048] bf16: expert outputs returned, source order  */
     int32_t *rowinfo[OMNI_EP_MAX];  /* [ROWS] (source rank << 20) | source permuted row          */
-    int32_t *counts[OMNI_EP_MAX];   /* [EP_MAX][128] per-expert counts of every rank             */
+    int32_t *counts[OMNI_EP_MAX];   /* [EP_MAX][COUNT_STRIDE] per-expert and per-bucket counts of every rank */
+    int32_t *grow[OMNI_EP_MAX];     /* [ROWS] received row (index into xg) that holds each expert-major row's token */
     uint32_t *flags[OMNI_EP_MAX];   /* [EP_MAX] barrier epochs, written by the peers; from word
                                        OMNI_EP_READY_WORD on: rows arrived per local expert       */
 } omni_ep_peers;
@@ -77,7 +79,20 @@ enum { OMNI_EP_SYNC_WORD = 16, OMNI_EP_READY_WORD = 64, OMNI_EP_FLAG_WORDS = 64 
 #ifdef __CUDACC__
 __host__ __device__
 #endif
-static inline int omni_ep_group_size(int world) { const int el = OMNI_E / world; return el >= 4 ? el / 4 : 1; }
+static inline int omni_ep_group_size(int world) { const int el = OMNI_E / world; return el >= OMNI_EP_GROUPS ? el / OMNI_EP_GROUPS : 1; }
+
+/* What the sender side of the de-duplicated dispatch works from (all device pointers of this rank).
+ * A token goes ONCE to every rank that owns at least one of its experts, into the bucket
+ * (owner, first group of that owner's experts that needs it). */
+typedef struct {
+    const int32_t *tok_slot;      /* [T][EP_MAX]  (group << 24) | position of the token in its bucket for that owner, -1: not sent there */
+    const int32_t *bucket_list;   /* [BUCKETS][CHUNK] tokens of each bucket */
+    const int32_t *send_cnt;      /* [BUCKETS] tokens this rank sends per bucket */
+    const int32_t *recv_base;     /* [BUCKETS] first row of this rank's tokens of a bucket in the owner's receive buffer */
+    const int32_t *send_base;     /* [128] first expert-major row of this rank's rows of an expert on its owner */
+    const int32_t *rowmap, *offsets;
+    const void *xn;               /* [T][2048] bf16 */
+} omni_ep_send;
 
 /* ---- plain kernels (omni_kernels.cu) ---- */
 cudaError_t omni_launch_router_simple(const void *xn, const void *router, const float *bias, int T,
@@ -151,11 +166,11 @@ cudaError_t omni_expert_configure(void);  /* opt-in shared-memory sizes; call on
 cudaError_t omni_launch_gateup_pair(int ctas, const CUtensorMap *tm_w3, const CUtensorMap *tm_x4, const omni_sort_state st,
                                     void *h, const uint32_t *ready, const int32_t *need, int group_size,
                                     const void *gather_src, const int32_t *gather_rows, const omni_ep_peers *dispatch_to,
-                                    const void *disp_src, const int32_t *send_base, int early_dependents, int n_sm,
-                                    cudaStream_t s);
-/* dispatch_to (may be NULL): expert parallelism -- four more warps per CTA send this rank's token
- * rows (rows st.rowmap[r] of disp_src, destinations from send_base) to the owners of their experts
- * and announce them on the owners' arrival counters, which `ready`/`need` of every rank wait for.
+                                    const omni_ep_send *send, int early_dependents, int n_sm, cudaStream_t s);
+/* dispatch_to/send (may be NULL): expert parallelism -- four more warps per CTA send this rank's
+ * token rows, each once per owner rank, into the owners' receive buffers (gather_src of the
+ * owner) with the row map (gather_rows of the owner) and the origin tags, and count themselves on
+ * the owners' arrival counters, which `ready` of every rank waits for, group by group.
  * return_to/rowinfo (may be NULL): result row i is written to row (rowinfo[i] & 0xfffff) of
  * return_to->dret[rowinfo[i] >> 20] (the rank the token came from) instead of row i of d */
 cudaError_t omni_launch_down_pair(int ctas, const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
@@ -169,7 +184,12 @@ int omni_dependent_launch_enabled(void);
 /* ---- expert parallel (omni_ep.cu) ---- */
 /* limit_ns = 0 (here and below): the default bound of 2 s on the wait for the other ranks */
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
-                                int32_t *n_local_rows, int32_t *need, uint64_t limit_ns, cudaStream_t s);
+                                int32_t *n_local_rows, int32_t *need, int32_t *bucket_cnt, int32_t *send_cnt, int32_t *recv_base,
+                                uint64_t limit_ns, cudaStream_t s);
+/* tokens of this rank -> buckets (owner, first group that needs the token); bucket_cnt must be zero on entry
+ * (the plan kernel leaves it so) */
+cudaError_t omni_launch_ep_buckets(const int32_t *ids, int T, int world, int32_t *tok_slot, int32_t *bucket_cnt,
+                                   int32_t *bucket_list, cudaStream_t s);
 /* realignment barrier: result[0] = agreed sync count, result[1] = agreed epoch (written on success only) */
 cudaError_t omni_launch_ep_sync(const omni_ep_peers *pe, uint32_t count, uint32_t epoch, uint32_t *status, uint32_t *result,
                                 uint64_t limit_ns, cudaStream_t s);

@@ -40,7 +40,7 @@ EXPORTS = [
     "clef_omni_bind_norm", "clef_omni_encode_norm_moe", "clef_omni_bind_gguf", "clef_omni_gguf_check",
 ]
 NOALLOC_MAX_ROWS = 4096
-EP_HANDLES, EP_HANDLE_BYTES = 5, 64
+EP_HANDLES, EP_HANDLE_BYTES = 6, 64
 
 
 def load_library(path: Path | None = None) -> C.CDLL:
@@ -276,7 +276,7 @@ class OmniBackend:
 
     # -- expert parallelism
     def ep_export(self) -> bytes:
-        """This rank's exchange-buffer handles (5 x 64 bytes) for the other ranks."""
+        """This rank's exchange-buffer handles (6 x 64 bytes) for the other ranks."""
         buf = C.create_string_buffer(EP_HANDLES * EP_HANDLE_BYTES)
         self._check(self.lib.clef_omni_ep_export(self._g, buf, self._err, _ERRLEN))
         return buf.raw

@@ -165,7 +165,7 @@ bool clef_omni_gguf_check(const char *path, int n_layer, int H, int ffn, int n_e
  *     [128/world][1536][2048] and [128/world][2048][768].
  *   - results are bitwise those of the single-GPU path on the same tokens. */
 typedef struct { unsigned char reserved[64]; } clef_omni_ipc_handle;
-enum { CLEF_OMNI_EP_HANDLES = 5, CLEF_OMNI_EP_MAX_WORLD = 8 };
+enum { CLEF_OMNI_EP_HANDLES = 6, CLEF_OMNI_EP_MAX_WORLD = 8 };
 bool clef_omni_ep_export(clef_gpu *g, clef_omni_ipc_handle out[CLEF_OMNI_EP_HANDLES], char *err, size_t errlen);
 /* all = world x CLEF_OMNI_EP_HANDLES handles, rank-major, as exported by every rank */
 bool clef_omni_ep_connect(clef_gpu *g, int rank, int world, const clef_omni_ipc_handle *all, char *err, size_t errlen);

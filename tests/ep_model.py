@@ -47,3 +47,43 @@ def destinations(ids: np.ndarray, table: np.ndarray, rank: int):
     owner = e_of_row // el
     dst = send_base[e_of_row] + (np.arange(flat.size) - offsets[e_of_row])
     return dict(owner=owner, dst=dst, offsets=offsets, slots=slots, rowmap=rowmap, expert=e_of_row)
+
+
+GROUPS = 4
+
+
+def group_size(world: int) -> int:
+    el = E // world
+    return el // GROUPS if el >= GROUPS else 1
+
+
+def buckets(ids: np.ndarray, world: int):
+    """De-duplicated dispatch, sender side (ep_bucket_kernel): a token goes once to every rank that
+    owns one of its experts, in the bucket (owner, lowest group of that owner's experts among the
+    token's).  Returns slot[T][world] = (group, position in bucket) or (-1, -1) and the bucket
+    counts [world][GROUPS].  Positions here are in token order; the device hands them out by
+    atomics, in any order."""
+    ids = np.asarray(ids, dtype=np.int64)
+    el, gs = E // world, group_size(world)
+    slot = np.full((ids.shape[0], world, 2), -1, np.int64)
+    cnt = np.zeros((world, GROUPS), np.int64)
+    for t, row in enumerate(ids):
+        for o in range(world):
+            mine = row[(row // el) == o]
+            if len(mine):
+                g = int(((mine % el) // gs).min())
+                slot[t, o] = (g, cnt[o, g])
+                cnt[o, g] += 1
+    return slot, cnt
+
+
+def recv_base(bucket_table: np.ndarray, rank: int):
+    """bucket_table[s][o][g] = tokens rank s sends into bucket (o, g).  Where rank `rank`'s tokens
+    of each bucket start in the owner's receive buffer: lower groups of every rank first, then
+    this group of lower ranks (ep_plan_kernel)."""
+    world = bucket_table.shape[0]
+    base = np.zeros((world, GROUPS), np.int64)
+    for o in range(world):
+        for g in range(GROUPS):
+            base[o, g] = bucket_table[:, o, :g].sum() + bucket_table[:rank, o, g].sum()
+    return base

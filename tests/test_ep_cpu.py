@@ -120,3 +120,48 @@ def test_plan_is_a_partition():
                 for e in range(owner * el, (owner + 1) * el):
                     rows.extend(range(base[e], base[e] + table[s, e]))
             assert sorted(rows) == list(range(table[:, owner * el:(owner + 1) * el].sum()))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_deduplicated_dispatch_bookkeeping(world):
+    """Every token reaches every owner of one of its experts exactly once; the received rows of an
+    owner are a partition of its receive buffer; the row map written beside the origin tags leads
+    every expert-major row to its token's activations; and a row needed by group g has arrived
+    with a group <= g (the owner's kernel waits for the arrival counters of groups 0..g)."""
+    tokens = [40 + 7 * r for r in range(world)]
+    ids_all, _, x_all = make_case(3, sum(tokens))
+    bounds = np.concatenate([[0], np.cumsum(tokens)])
+    per_rank = [ids_all[bounds[r]:bounds[r + 1]] for r in range(world)]
+    el, gs = E // world, ep.group_size(world)
+    table = np.stack([np.bincount(i.reshape(-1), minlength=E) for i in per_rank])
+    slots, cnts = zip(*[ep.buckets(i, world) for i in per_rank])
+    bucket_table = np.stack(cnts)
+    for owner in range(world):
+        n_recv = bucket_table[:, owner, :].sum()
+        recv = np.full((n_recv, H), np.nan)
+        recv_group = np.full(n_recv, -1)
+        _, local_off = ep.plan(table, owner)
+        grow = np.full(local_off[-1], -1)
+        for s in range(world):
+            base = ep.recv_base(bucket_table, s)
+            x = x_all[bounds[s]:bounds[s + 1]]
+            for t in range(tokens[s]):
+                g, pos = slots[s][t, owner]
+                if g >= 0:
+                    assert np.isnan(recv[base[owner, g] + pos]).all(), "two tokens on one received row"
+                    recv[base[owner, g] + pos] = x[t]
+                    recv_group[base[owner, g] + pos] = g
+            d = ep.destinations(per_rank[s], table, s)
+            for r in np.where(d["owner"] == owner)[0]:
+                g, pos = slots[s][d["rowmap"][r], owner]
+                grow[d["dst"][r]] = base[owner, g] + pos
+        assert not np.isnan(recv).any() and (grow >= 0).all()
+        # the owner's expert-major rows, read through the row map, are the single-device permutation
+        flat = ids_all.reshape(-1)
+        order = np.argsort(flat, kind="stable")
+        mine = order[(flat[order] >= owner * el) & (flat[order] < (owner + 1) * el)]
+        assert np.array_equal(recv[grow], x_all[mine // K])
+        expert_group = (flat[mine] % el) // gs
+        assert (recv_group[grow] <= expert_group).all()
+        # and fewer rows travel than with one row per (token, expert)
+        assert n_recv <= len(mine)
