@@ -25,6 +25,7 @@
 
 #include "omni_internal.h"
 #include "omni_ep_dev.cuh"
+#include "omni_pdl.cuh"
 
 namespace {
 
@@ -93,6 +94,8 @@ __global__ void __launch_bounds__(32) ep_sync_kernel(omni_ep_peers pe, uint32_t 
 __global__ void __launch_bounds__(256) ep_bucket_kernel(const int32_t *__restrict__ ids, int T, int world,
                                                         int32_t *__restrict__ tok_slot, int32_t *__restrict__ bucket_cnt,
                                                         int32_t *__restrict__ bucket_list) {
+    dep_wait();
+    dep_launch();
     const int t = blockIdx.x * 256 + threadIdx.x;
     if (t >= T) return;
     const int EL = OMNI_E / world, gsz = omni_ep_group_size(world);
@@ -123,6 +126,8 @@ __global__ void __launch_bounds__(OMNI_E) ep_plan_kernel(omni_ep_peers pe, uint3
                                                          int32_t *bucket_cnt, int32_t *send_cnt, int32_t *recv_base,
                                                          uint64_t limit_ns) {
     __shared__ int tot[OMNI_E], scan[OMNI_E], tiles[OMNI_E];
+    dep_wait();
+    dep_launch();
     const int e = threadIdx.x;
     const int G = pe.world, EL = OMNI_E / G;
     const int mine = st.counts[e];
@@ -220,9 +225,8 @@ extern "C" {
 cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_sort_state st, int32_t *send_base,
                                 int32_t *n_local_rows, int32_t *need, int32_t *bucket_cnt, int32_t *send_cnt, int32_t *recv_base,
                                 uint64_t limit_ns, cudaStream_t s) {
-    ep_plan_kernel<<<1, OMNI_E, 0, s>>>(*pe, epoch, st, send_base, n_local_rows, need, bucket_cnt, send_cnt, recv_base,
-                                        limit_ns ? limit_ns : SPIN_LIMIT_NS);
-    return cudaGetLastError();
+    return omni_launch_chain(ep_plan_kernel, dim3(1), dim3(OMNI_E), 0, s, *pe, epoch, st, send_base, n_local_rows, need, bucket_cnt, send_cnt,
+                             recv_base, limit_ns ? limit_ns : SPIN_LIMIT_NS);
 }
 
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
@@ -233,8 +237,7 @@ cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint
 
 cudaError_t omni_launch_ep_buckets(const int32_t *ids, int T, int world, int32_t *tok_slot, int32_t *bucket_cnt,
                                    int32_t *bucket_list, cudaStream_t s) {
-    ep_bucket_kernel<<<(T + 255) / 256, 256, 0, s>>>(ids, T, world, tok_slot, bucket_cnt, bucket_list);
-    return cudaGetLastError();
+    return omni_launch_chain(ep_bucket_kernel, dim3((T + 255) / 256), dim3(256), 0, s, ids, T, world, tok_slot, bucket_cnt, bucket_list);
 }
 
 cudaError_t omni_launch_ep_sync(const omni_ep_peers *pe, uint32_t count, uint32_t epoch, uint32_t *status, uint32_t *result,
