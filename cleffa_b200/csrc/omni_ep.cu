@@ -49,6 +49,8 @@ __device__ void flag_barrier(const omni_ep_peers &pe, uint32_t epoch, uint32_t *
 }
 
 __global__ void __launch_bounds__(128) ep_barrier_kernel(omni_ep_peers pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns) {
+    dep_wait();                 // part of the pass's dependent-launch chain: resident early, works only after the down kernel
+    dep_launch();
     flag_barrier(pe, epoch, status, limit_ns ? limit_ns : SPIN_LIMIT_NS);
 }
 
@@ -231,8 +233,7 @@ cudaError_t omni_launch_ep_plan(const omni_ep_peers *pe, uint32_t epoch, omni_so
 
 cudaError_t omni_launch_ep_barrier(const omni_ep_peers *pe, uint32_t epoch, uint32_t *status, uint64_t limit_ns,
                                    cudaStream_t s) {
-    ep_barrier_kernel<<<1, 128, 0, s>>>(*pe, epoch, status, limit_ns);
-    return cudaGetLastError();
+    return omni_launch_chain(ep_barrier_kernel, dim3(1), dim3(128), 0, s, *pe, epoch, status, limit_ns);
 }
 
 cudaError_t omni_launch_ep_buckets(const int32_t *ids, int T, int world, int32_t *tok_slot, int32_t *bucket_cnt,
