@@ -181,3 +181,29 @@ def test_rmsnorm_c_restatement_agrees():
     scale = np.abs(g["y"]).max(axis=1, keepdims=True) + 1e-300
     assert (np.abs(got - g["y"]) / scale).max() < 1e-14
     assert np.all(got[4] == 0.0)
+
+
+def test_attention_oracle_reproduces_the_reference_fp64_functions():
+    """oracle/omni_attn_oracle.py against what the reference's own text_attention / rotary
+    (ref/omni_fp64.py:78-105) returned on a small seeded problem (tests/golden/make_golden_attn.py):
+    rotary tables bit for bit, the layer output to FP64 rounding (the reference's attention runs an
+    online softmax over key blocks, the restatement a plain softmax per record)."""
+    from pathlib import Path
+    from oracle import omni_attn_oracle as ao
+    g = np.load(Path(__file__).resolve().parent / "golden" / "attn_small.npz")
+    H, nh, nkv, hd, T, s0, s1, s2 = (int(v) for v in g["geometry"])
+    sections = (s0, s1, s2)
+    cos, sin = ao.rotary(g["positions"], hd, float(g["theta"]), sections)
+    assert np.array_equal(cos.numpy(), g["cos"]) and np.array_equal(sin.numpy(), g["sin"])
+    w_qkv = torch.from_numpy(np.concatenate([g["w_q"], g["w_k"], g["w_v"]]))
+    r = ao.attention_half(torch.from_numpy(g["hidden"]), g["positions"], [0, T], torch.from_numpy(g["attn_norm"]), w_qkv,
+                          torch.from_numpy(g["q_norm"]), torch.from_numpy(g["k_norm"]), torch.from_numpy(g["w_o"]), nh, nkv, hd,
+                          float(g["theta"]), sections, float(g["eps"]))
+    assert np.abs(r["out"].numpy() - g["out"]).max() < 1e-12
+    # a packed batch of two records equals the two records run alone (per-record causal masks)
+    x = torch.from_numpy(g["hidden"])
+    both = ao.attention_half(x, g["positions"], [0, 20, T], torch.from_numpy(g["attn_norm"]), w_qkv, torch.from_numpy(g["q_norm"]),
+                             torch.from_numpy(g["k_norm"]), torch.from_numpy(g["w_o"]), nh, nkv, hd, float(g["theta"]), sections, float(g["eps"]))
+    first = ao.attention_half(x[:20], g["positions"][:, :20], [0, 20], torch.from_numpy(g["attn_norm"]), w_qkv, torch.from_numpy(g["q_norm"]),
+                              torch.from_numpy(g["k_norm"]), torch.from_numpy(g["w_o"]), nh, nkv, hd, float(g["theta"]), sections, float(g["eps"]))
+    assert np.abs(both["out"][:20].numpy() - first["out"].numpy()).max() < 1e-13
