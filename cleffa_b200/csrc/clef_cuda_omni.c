@@ -56,6 +56,22 @@ struct clef_gpu {
     float *norm_w[MAX_LAYERS];          /* device, FP32 [2048]; NULL = not bound */
     float norm_eps[MAX_LAYERS];
     void *xnorm;                        /* BF16 [CHUNK][2048]: the normalised rows of the chunk in flight */
+    /* attention half (clef_omni_bind_attention / clef_omni_encode_attention) */
+    struct {
+        float *norm_w, *q_norm, *k_norm;   /* device FP32 [2048], [128], [128] */
+        void *qkv, *out;                   /* device BF16 [5120][2048], [2048][4096] */
+        float eps; double theta;
+        bool bound;
+        CUtensorMap tm_qkv, tm_out;
+    } attn[MAX_LAYERS];
+    struct {
+        void *p, *q, *k, *vt, *a;          /* BF16: q|k|v rows [CHUNK][5120]; Q [32][CHUNK][128]; K [4][CHUNK][128]; Vt [4][128][VPITCH]; attention output [CHUNK][4096] */
+        int32_t *tiles, *vcol, *sched;     /* device: query tiles, Vt column of every token, work counters of the two projections */
+        int32_t *h_tiles, *h_vcol, *h_bounds;   /* host copies; h_bounds remembers the batch the device copies describe */
+        int n_tiles, last_T, last_nseq;
+        CUtensorMap tm_xn[4], tm_a[4], tm_q, tm_k, tm_vt;
+        bool ready;
+    } at;
     /* route capture */
     omni_route_row *trace;              /* device */
     int trace_first, trace_rows, trace_layers;
@@ -201,6 +217,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     e = omni_sm100_configure();
     if (e == cudaSuccess) e = omni_expert_configure();
     if (e == cudaSuccess) e = omni_router_configure();
+    if (e == cudaSuccess) e = omni_attn_configure();
     if (e != cudaSuccess) {
         set_err(err, errlen, "cuda: cannot configure sm_100a kernels: %s", cudaGetErrorString(e));
         if (g->own_stream) cudaStreamDestroy(g->stream);
@@ -227,6 +244,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
 }
 
 void clef_omni_ep_disconnect(clef_gpu *g);
+static void attn_free(clef_gpu *g);
 
 static void free_layer(omni_layer *L) {
     if (L->owned) { cudaFree(L->router); cudaFree(L->gate_up); cudaFree(L->down); cudaFree(L->bias); }
@@ -256,6 +274,7 @@ void clef_cuda_omni_close(clef_gpu *g) {
     clef_omni_ep_disconnect(g);
     clef_omni_free(g);
     for (int l = 0; l < MAX_LAYERS; l++) free_layer(&g->layer[l]);
+    attn_free(g);
     for (int l = 0; l < MAX_LAYERS; l++) if (g->norm_w[l]) cudaFree(g->norm_w[l]);
     if (g->xnorm) cudaFree(g->xnorm);
     if (g->trace) cudaFree(g->trace);
@@ -950,6 +969,8 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
     else if (!strcmp(what, "rechecked")) { src = s->n_flag + 1; have = 4; }
     else if (!strcmp(what, "n_ttiles")) { src = s->sort.n_ttiles; have = 4; }
     else if (!strcmp(what, "xnorm") && g->xnorm) { src = g->xnorm; have = T * OMNI_H * 2; }
+    else if (!strcmp(what, "attn_qkv") && g->at.ready) { src = g->at.p; have = (size_t)OMNI_CHUNK * OMNI_QKV * 2; }
+    else if (!strcmp(what, "attn_out") && g->at.ready) { src = g->at.a; have = (size_t)OMNI_CHUNK * OMNI_NH * OMNI_HD * 2; }
     else if (!strcmp(what, "router_stamps")) { src = s->stamps; have = (size_t)(OMNI_CHUNK / 32) * 64; }
     if (!src || !dst || bytes > have || !bytes) { set_err(err, errlen, "cuda: unknown or oversized Omni read: %s", what); return false; }
     cudaError_t e = cudaStreamSynchronize(g->stream);
@@ -1193,4 +1214,175 @@ bool clef_omni_assign_noalloc(const int32_t *ids, int rows, int32_t *counts, int
     else
         set_err(err, errlen, "cuda: allocation-free Omni assignment failed: %s", cudaGetErrorString(e));
     return false;
+}
+
+/* ---------------------------------------------------------------- attention half */
+enum { ATTN_VPITCH = 2 * OMNI_CHUNK, ATTN_MAX_TILES = OMNI_CHUNK / 128 + 4096 };
+
+static void attn_free(clef_gpu *g) {
+    void *dev[] = {g->at.p, g->at.q, g->at.k, g->at.vt, g->at.a, g->at.tiles, g->at.vcol, g->at.sched};
+    for (size_t i = 0; i < sizeof dev / sizeof dev[0]; i++) if (dev[i]) cudaFree(dev[i]);
+    free(g->at.h_tiles); free(g->at.h_vcol); free(g->at.h_bounds);
+    memset(&g->at, 0, sizeof g->at);
+    for (int l = 0; l < MAX_LAYERS; l++) {
+        void *w[] = {g->attn[l].norm_w, g->attn[l].q_norm, g->attn[l].k_norm, g->attn[l].qkv, g->attn[l].out};
+        for (size_t i = 0; i < sizeof w / sizeof w[0]; i++) if (w[i]) cudaFree(w[i]);
+        memset(&g->attn[l], 0, sizeof g->attn[l]);
+    }
+}
+
+/* scratch of the attention half, allocated with the first binding: 0.6 GB, independent of T */
+static bool attn_reserve(clef_gpu *g, char *err, size_t errlen) {
+    if (g->at.ready) return true;
+    struct { void **p; size_t bytes; } want[] = {
+        {&g->at.p, (size_t)OMNI_CHUNK * OMNI_QKV * 2},
+        {&g->at.q, (size_t)OMNI_NH * OMNI_CHUNK * OMNI_HD * 2},
+        {&g->at.k, (size_t)OMNI_NKV * OMNI_CHUNK * OMNI_HD * 2},
+        {&g->at.vt, (size_t)OMNI_NKV * OMNI_HD * ATTN_VPITCH * 2},
+        {&g->at.a, (size_t)OMNI_CHUNK * OMNI_NH * OMNI_HD * 2},
+        {(void **)&g->at.tiles, (size_t)ATTN_MAX_TILES * 16},
+        {(void **)&g->at.vcol, (size_t)OMNI_CHUNK * 4},
+        {(void **)&g->at.sched, 256},
+    };
+    void *xnorm = g->xnorm ? g->xnorm : dev_alloc(g, (size_t)OMNI_CHUNK * OMNI_H * 2);
+    bool ok = xnorm != NULL;
+    for (size_t i = 0; i < sizeof want / sizeof want[0] && ok; i++) ok = (*want[i].p = dev_alloc(g, want[i].bytes)) != NULL;
+    g->at.h_tiles = malloc((size_t)ATTN_MAX_TILES * 16);
+    g->at.h_vcol = malloc((size_t)OMNI_CHUNK * 4);
+    g->at.h_bounds = malloc((size_t)(OMNI_CHUNK + 2) * 4);
+    ok = ok && g->at.h_tiles && g->at.h_vcol && g->at.h_bounds;
+    /* the padding columns of Vt are multiplied by probabilities that are exactly zero: they must stay finite */
+    if (ok) ok = cudaMemsetAsync(g->at.vt, 0, (size_t)OMNI_NKV * OMNI_HD * ATTN_VPITCH * 2, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(g->at.k, 0, (size_t)OMNI_NKV * OMNI_CHUNK * OMNI_HD * 2, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(g->at.q, 0, (size_t)OMNI_NH * OMNI_CHUNK * OMNI_HD * 2, g->stream) == cudaSuccess &&
+                 cudaStreamSynchronize(g->stream) == cudaSuccess;
+    for (int i = 0; i < 4 && ok; i++)
+        ok = make_map(g, &g->at.tm_xn[i], xnorm, OMNI_CHUNK, OMNI_H, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
+             make_map(g, &g->at.tm_a[i], g->at.a, OMNI_CHUNK, OMNI_NH * OMNI_HD, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (ok) ok = make_map(g, &g->at.tm_q, g->at.q, (uint64_t)OMNI_NH * OMNI_CHUNK, OMNI_HD, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
+                 make_map(g, &g->at.tm_k, g->at.k, (uint64_t)OMNI_NKV * OMNI_CHUNK, OMNI_HD, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
+                 make_map(g, &g->at.tm_vt, g->at.vt, (uint64_t)OMNI_NKV * OMNI_HD, ATTN_VPITCH, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (!ok) {
+        cudaGetLastError();
+        if (xnorm && !g->xnorm) cudaFree(xnorm);
+        void *dev[] = {g->at.p, g->at.q, g->at.k, g->at.vt, g->at.a, g->at.tiles, g->at.vcol, g->at.sched};
+        for (size_t i = 0; i < sizeof dev / sizeof dev[0]; i++) if (dev[i]) cudaFree(dev[i]);
+        free(g->at.h_tiles); free(g->at.h_vcol); free(g->at.h_bounds);
+        memset(&g->at, 0, sizeof g->at);
+        set_err(err, errlen, "cuda: cannot allocate Omni attention scratch (previous buffers kept)");
+        return false;
+    }
+    g->xnorm = xnorm;
+    g->at.ready = true;
+    g->at.last_T = -1;
+    return true;
+}
+
+bool clef_omni_bind_attention(clef_gpu *g, int layer, const float *attn_norm, const void *attn_qkv, const void *attn_output,
+                              const float *q_norm, const float *k_norm, float eps, float rope_theta, int where, char *err,
+                              size_t errlen) {
+    if (!g || !g->omni || layer < 0 || layer >= MAX_LAYERS || !attn_norm || !attn_qkv || !attn_output || !q_norm || !k_norm ||
+        !(eps > 0.f) || !isfinite(eps) || !(rope_theta > 1.f) || (where != CLEF_OMNI_HOST && where != CLEF_OMNI_DEVICE)) {
+        set_err(err, errlen, "cuda: invalid Omni attention binding");
+        return false;
+    }
+    cudaSetDevice(g->device);
+    if (!attn_reserve(g, err, errlen)) return false;
+    const size_t nq = (size_t)OMNI_QKV * OMNI_H * 2, no = (size_t)OMNI_H * OMNI_NH * OMNI_HD * 2;
+    const enum cudaMemcpyKind kind = where == CLEF_OMNI_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+    float *nw = dev_alloc(g, OMNI_H * 4), *qn = dev_alloc(g, OMNI_HD * 4), *kn = dev_alloc(g, OMNI_HD * 4);
+    void *qkv = dev_alloc(g, nq), *out = dev_alloc(g, no);
+    bool ok = nw && qn && kn && qkv && out;
+    if (ok) ok = cudaMemcpyAsync(nw, attn_norm, OMNI_H * 4, kind, g->stream) == cudaSuccess &&
+                 cudaMemcpyAsync(qn, q_norm, OMNI_HD * 4, kind, g->stream) == cudaSuccess &&
+                 cudaMemcpyAsync(kn, k_norm, OMNI_HD * 4, kind, g->stream) == cudaSuccess &&
+                 cudaMemcpyAsync(qkv, attn_qkv, nq, kind, g->stream) == cudaSuccess &&
+                 cudaMemcpyAsync(out, attn_output, no, kind, g->stream) == cudaSuccess &&
+                 cudaStreamSynchronize(g->stream) == cudaSuccess;
+    CUtensorMap tm_qkv, tm_out;
+    if (ok) ok = make_map(g, &tm_qkv, qkv, OMNI_QKV, OMNI_H, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) &&
+                 make_map(g, &tm_out, out, OMNI_H, OMNI_NH * OMNI_HD, 128, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (!ok) {
+        cudaGetLastError();
+        void *w[] = {nw, qn, kn, qkv, out};
+        for (size_t i = 0; i < sizeof w / sizeof w[0]; i++) if (w[i]) cudaFree(w[i]);
+        set_err(err, errlen, "cuda: cannot upload Omni attention tensors of layer %d (previous binding kept)", layer);
+        return false;
+    }
+    void *old[] = {g->attn[layer].norm_w, g->attn[layer].q_norm, g->attn[layer].k_norm, g->attn[layer].qkv, g->attn[layer].out};
+    for (size_t i = 0; i < sizeof old / sizeof old[0]; i++) if (old[i]) cudaFree(old[i]);
+    g->attn[layer].norm_w = nw; g->attn[layer].q_norm = qn; g->attn[layer].k_norm = kn; g->attn[layer].qkv = qkv; g->attn[layer].out = out;
+    g->attn[layer].eps = eps; g->attn[layer].theta = (double)rope_theta;
+    g->attn[layer].tm_qkv = tm_qkv; g->attn[layer].tm_out = tm_out;
+    g->attn[layer].bound = true;
+    return true;
+}
+
+/* Query tiles (<= 128 rows, cut from each record's start) and the Vt column of every token (a
+ * record's columns start at a multiple of 64): rebuilt only when the batch's shape changes. */
+static bool attn_plan(clef_gpu *g, int T, int n_seq, const int32_t *seq_bounds, char *err, size_t errlen) {
+    const int32_t whole[2] = {0, T};
+    const int32_t *b = seq_bounds ? seq_bounds : whole;
+    if (g->at.last_T == T && g->at.last_nseq == n_seq && !memcmp(g->at.h_bounds, b, (size_t)(n_seq + 1) * 4)) return true;
+    int n_tiles = 0, col = 0;
+    for (int r = 0; r < n_seq; r++) {
+        const int lo = b[r], hi = b[r + 1];
+        if (col + (hi - lo) > ATTN_VPITCH || n_tiles + (hi - lo + 127) / 128 > ATTN_MAX_TILES) {
+            set_err(err, errlen, "cuda: too many records in one Omni attention pass (%d)", n_seq);
+            return false;
+        }
+        for (int q0 = lo; q0 < hi; q0 += 128) {
+            int32_t *t = g->at.h_tiles + 4 * n_tiles++;
+            t[0] = lo; t[1] = q0; t[2] = hi - q0 < 128 ? hi - q0 : 128; t[3] = col;
+        }
+        for (int t = lo; t < hi; t++) g->at.h_vcol[t] = col + (t - lo);
+        col = (col + (hi - lo) + 63) & ~63;
+    }
+    if (cudaMemcpyAsync(g->at.tiles, g->at.h_tiles, (size_t)n_tiles * 16, cudaMemcpyHostToDevice, g->stream) != cudaSuccess ||
+        cudaMemcpyAsync(g->at.vcol, g->at.h_vcol, (size_t)T * 4, cudaMemcpyHostToDevice, g->stream) != cudaSuccess) {
+        cudaGetLastError();
+        g->at.last_T = -1;
+        set_err(err, errlen, "cuda: cannot upload the Omni attention plan");
+        return false;
+    }
+    memcpy(g->at.h_bounds, b, (size_t)(n_seq + 1) * 4);
+    g->at.n_tiles = n_tiles; g->at.last_T = T; g->at.last_nseq = n_seq;
+    return true;
+}
+
+bool clef_omni_encode_attention(clef_gpu *g, int layer, float *x, const int32_t *pos3, int T, int n_seq,
+                                const int32_t *seq_bounds, char *err, size_t errlen) {
+    if (!g || !g->omni || layer < 0 || layer >= MAX_LAYERS || !g->attn[layer].bound) {
+        set_err(err, errlen, "cuda: invalid Omni layer dispatch (no attention tensors bound)");
+        return false;
+    }
+    if (!x || !pos3 || T <= 0 || T > OMNI_CHUNK || n_seq < 1 || ((uintptr_t)x & 15)) {
+        set_err(err, errlen, T > OMNI_CHUNK ? "cuda: an Omni attention pass takes at most 16384 tokens" : "cuda: invalid Omni layer dispatch");
+        return false;
+    }
+    if (seq_bounds) {
+        bool ok = seq_bounds[0] == 0 && seq_bounds[n_seq] == T;
+        for (int i = 0; i < n_seq && ok; i++) ok = seq_bounds[i] < seq_bounds[i + 1];
+        if (!ok) { set_err(err, errlen, "cuda: invalid Omni sequence bounds"); return false; }
+    } else if (n_seq != 1) {
+        set_err(err, errlen, "cuda: invalid Omni sequence bounds");
+        return false;
+    }
+    cudaSetDevice(g->device);
+    if (g->failed) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    if (!attn_plan(g, T, n_seq, seq_bounds, err, errlen)) return false;
+    omni_arena *s = g->omni;
+    bool ok = launched(g, "attention norm", omni_launch_rmsnorm(x, g->attn[layer].norm_w, g->attn[layer].eps, T, g->xnorm, g->stream)) &&
+              launched(g, "projection tiles", omni_launch_dense_tiles(T, s->sort.ttiles, s->sort.n_ttiles, g->at.sched, g->stream)) &&
+              launched(g, "q|k|v projection", omni_launch_dense_pair(0, &g->attn[layer].tm_qkv, g->at.tm_xn, s->sort, g->at.sched, g->at.p, NULL,
+                                                                       g->n_sm, g->stream)) &&
+              launched(g, "attention prep", omni_launch_attn_prep(g->at.p, g->attn[layer].q_norm, g->attn[layer].k_norm, pos3, g->at.vcol, T, OMNI_CHUNK,
+                                                                   ATTN_VPITCH, g->attn[layer].eps, g->attn[layer].theta, g->at.q, g->at.k, g->at.vt,
+                                                                   s->status, g->stream)) &&
+              launched(g, "attention", omni_launch_attention(&g->at.tm_q, &g->at.tm_k, &g->at.tm_vt, g->at.tiles, g->at.n_tiles, OMNI_CHUNK, g->at.a,
+                                                             s->status, g->stream)) &&
+              launched(g, "output projection", omni_launch_dense_pair(1, &g->attn[layer].tm_out, g->at.tm_a, s->sort, g->at.sched + 1, NULL, x,
+                                                                        g->n_sm, g->stream));
+    if (!ok) { set_err(err, errlen, "%s", g->fail_msg); return false; }
+    return true;
 }

@@ -184,7 +184,10 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 }
 
 // ------------------------------------------------------------------ configuration
-enum { X_GATEUP = 0, X_DOWN = 1 };
+enum { X_GATEUP = 0, X_DOWN = 1,
+       // the two dense projections of the attention half, run as "one expert" over all token rows:
+       X_QKV = 2,      // P[T][5120] = xn[T][2048] . W_qkv^T, BF16 out
+       X_OPROJ = 3 };  // x[T][2048] += A[T][4096] . W_out^T, added into the FP32 residual
 #ifndef X_GU_WS
 #define X_GU_WS 7
 #define X_GU_TS 5
@@ -202,6 +205,8 @@ enum { X_GATEUP = 0, X_DOWN = 1 };
 template <int MODE> struct XMode;
 template <> struct XMode<X_GATEUP> { static constexpr int KTOT = OMNI_H, OUTC = 64, MT = OMNI_F / 64, OUT_COLS = OMNI_F; };
 template <> struct XMode<X_DOWN> { static constexpr int KTOT = OMNI_F, OUTC = 128, MT = OMNI_H / 128, OUT_COLS = OMNI_H; };
+template <> struct XMode<X_QKV> { static constexpr int KTOT = OMNI_H, OUTC = 128, MT = OMNI_QKV / 128, OUT_COLS = OMNI_QKV; };
+template <> struct XMode<X_OPROJ> { static constexpr int KTOT = OMNI_NH * OMNI_HD, OUTC = 128, MT = OMNI_H / 128, OUT_COLS = OMNI_H; };
 
 template <int MODE, int CTAS> struct XCfg {
     using M = XMode<MODE>;
@@ -216,7 +221,8 @@ template <int MODE, int CTAS> struct XCfg {
     static constexpr int TOTAL_BYTES = RING_BYTES + STAGE_OUT_BYTES + 1024 + 1024;
     static constexpr int ITEMS_PER_TILE = M::MT / CTAS;
 };
-static_assert(XCfg<X_GATEUP, 1>::TOTAL_BYTES <= 232448 && XCfg<X_DOWN, 1>::TOTAL_BYTES <= 232448 &&
+static_assert(XCfg<X_QKV, 2>::TOTAL_BYTES <= 232448 && XCfg<X_OPROJ, 2>::TOTAL_BYTES <= 232448 &&
+              XCfg<X_GATEUP, 1>::TOTAL_BYTES <= 232448 && XCfg<X_DOWN, 1>::TOTAL_BYTES <= 232448 &&
               XCfg<X_GATEUP, 2>::TOTAL_BYTES <= 232448 && XCfg<X_DOWN, 2>::TOTAL_BYTES <= 232448, "shared memory budget");
 
 constexpr int X_THREADS = 384;      // warp 0 scheduler + weight loads, 1 MMA, 2 TMEM (2+3 gather), 3 token loads, 4..11 epilogue
@@ -231,7 +237,8 @@ struct XArgs {
     const omni_ttile *ttiles;
     const int32_t *n_ttiles;
     int32_t *work_counter;
-    __nv_bfloat16 *out;                 // h [rows][768] or d [rows][2048]
+    __nv_bfloat16 *out;                 // h [rows][768], d [rows][2048] or the q|k|v projections [rows][5120]
+    float *resid;                       // output projection: the FP32 residual stream it adds into
     uint32_t *status;
     // expert parallelism, overlap mode: rows of a group of experts may be read once ready[grp] == need[grp]
     const uint32_t *ready;
@@ -349,7 +356,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     auto load_weights = [&](uint32_t dst, int expert, int m, int ks, uint32_t bar, uint64_t pol) {
         const int m_cta = m * CTAS + (int)rank;
         if (MODE == X_GATEUP) xtma_3d<CTAS>(dst, &tm_w, ks * BK, 0, expert * (2 * OMNI_F) + m_cta * 64, bar, pol);
-        else xtma_2d<CTAS>(dst, &tm_w, ks * BK, expert * OMNI_H + m_cta * 128, bar, pol);
+        else xtma_2d<CTAS>(dst, &tm_w, ks * BK, expert * M::OUT_COLS + m_cta * 128, bar, pol);
     };
 
     if (warp == 0 && lane == 0 && leader) {
@@ -671,6 +678,12 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                                                  : silu_mul(__uint_as_float(v[j]), __uint_as_float(recv));
                             tile16[(half * 128 + (c - c_lo) * 32 + j + odd) * M::OUTC + col] = __bfloat16_as_ushort(__float2bfloat16(hv));
                         }
+                    } else if (MODE == X_OPROJ) {
+                        // added into the FP32 residual: a warp's 32 lanes are 32 consecutive columns of one row
+                        float *xr = a.resid + (long)(row0 + c * 32) * M::OUT_COLS + (m * CTAS + (int)rank) * M::OUTC + q * 32 + lane;
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (c * 32 + j < len) xr[(long)j * M::OUT_COLS] += __uint_as_float(v[j]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; j++)
@@ -685,7 +698,7 @@ expert_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             if (!got) epi_quit[half] = 1;
             named_bar_sync(1 + half, 128);            // the four quadrants of this half have written their columns
             if (stop || epi_quit[half]) break;
-            const int r_lo = c_lo * 32, r_hi = min(len, c_hi * 32);
+            const int r_lo = c_lo * 32, r_hi = MODE == X_OPROJ ? 0 : min(len, c_hi * 32);    // the output projection has stored already
             constexpr int LANES_PER_ROW = M::OUTC * 2 / 16;              // 8 (gate/up) or 16 (down)
             const int sub = th % LANES_PER_ROW;
             const int m_cta = m * CTAS + (int)rank;
@@ -769,6 +782,8 @@ cudaError_t omni_expert_configure(void) {
     if ((e = set_smem<X_GATEUP, 1, true>()) != cudaSuccess) return e;
     if ((e = set_smem<X_GATEUP, 2, true>()) != cudaSuccess) return e;
     if ((e = set_smem<X_DOWN, 1, false>()) != cudaSuccess) return e;
+    if ((e = set_smem<X_QKV, 2, false>()) != cudaSuccess) return e;
+    if ((e = set_smem<X_OPROJ, 2, false>()) != cudaSuccess) return e;
     return set_smem<X_DOWN, 2, false>();
 }
 
@@ -800,6 +815,18 @@ cudaError_t omni_launch_down_pair(int ctas, const CUtensorMap *tm_w, const CUten
     if (return_to) { a.pe = *return_to; a.rowinfo = rowinfo; }
     a.early_dependents = early_dependents;
     return ctas == 2 ? launch_pair<X_DOWN, 2, false>(tm_w, tm_h4, a, n_sm, s) : launch_pair<X_DOWN, 1, false>(tm_w, tm_h4, a, n_sm, s);
+}
+
+// The dense projections of the attention half on the same kernel: `st` holds a tile list that cuts
+// the T token rows into tiles of one "expert" (omni_launch_dense_tiles), tm_w is the weight matrix
+// [OUT_COLS][K] with a 64 x 128 box, tm_tok4 the token operand with boxes of 32..256 rows.
+cudaError_t omni_launch_dense_pair(int which, const CUtensorMap *tm_w, const CUtensorMap *tm_tok4, const omni_sort_state st,
+                                   int32_t *work_counter, void *out_bf16, float *resid, int n_sm, cudaStream_t s) {
+    XArgs a = {};
+    a.ttiles = st.ttiles; a.n_ttiles = st.n_ttiles; a.work_counter = work_counter;
+    a.out = (__nv_bfloat16 *)out_bf16; a.resid = resid; a.status = st.status; a.group_size = 1;
+    a.early_dependents = 1;
+    return which == 0 ? launch_pair<X_QKV, 2, false>(tm_w, tm_tok4, a, n_sm, s) : launch_pair<X_OPROJ, 2, false>(tm_w, tm_tok4, a, n_sm, s);
 }
 
 }  // extern "C"

@@ -13,6 +13,7 @@ extern "C" {
 
 enum {
     OMNI_H = 2048, OMNI_F = 768, OMNI_E = 128, OMNI_TOP = 8,
+    OMNI_NH = 32, OMNI_NKV = 4, OMNI_HD = 128, OMNI_QKV = (OMNI_NH + 2 * OMNI_NKV) * OMNI_HD,   /* attention half: 32 query, 4 key/value heads of 128 */
     OMNI_CHUNK = 16384,                    /* tokens per arena pass */
     OMNI_ROWS = OMNI_CHUNK * OMNI_TOP,     /* permuted rows per pass */
     OMNI_SEG = 256,                        /* assignments per sort segment (one warp) */
@@ -27,7 +28,9 @@ enum { OMNI_ST_NONFINITE = 1u, OMNI_ST_BAD_ID = 8u, OMNI_ST_TIMEOUT = 16u, OMNI_
        OMNI_ST_TIMEOUT_BARRIER = 64u, OMNI_ST_TIMEOUT_ARRIVAL = 128u,
        /* the exact pass found a tensor-core logit further from its exact value than the bound the
         * near-tie test assumes: rows that were not re-decided may carry a wrong order */
-       OMNI_ST_ROUTER_EPS = 256u };
+       OMNI_ST_ROUTER_EPS = 256u,
+       /* nonfinite values met while preparing q, k, v (the reference's attention status bit, clef.metal:2120) */
+       OMNI_ST_ATTN_NONFINITE = 2u };
 
 /* Bound assumed on |tensor-core logit - exact logit| for one row: `eps` for rows whose largest
  * |logit| is at most OMNI_EPS_REF_SCALE, growing in proportion beyond that (the FP32 accumulation
@@ -176,6 +179,22 @@ cudaError_t omni_launch_gateup_pair(int ctas, const CUtensorMap *tm_w3, const CU
 cudaError_t omni_launch_down_pair(int ctas, const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
                                   void *d, const omni_ep_peers *return_to, const int32_t *rowinfo, int early_dependents, int n_sm,
                                   cudaStream_t s);
+
+/* ---- attention half (omni_attn.cu; the two projections run on the kernel of omni_expert.cu) ---- */
+cudaError_t omni_attn_configure(void);
+/* tile list that cuts T token rows into tiles of one "expert"; counters[0..1] are cleared (work counters of the two projections) */
+cudaError_t omni_launch_dense_tiles(int T, omni_ttile *ttiles, int32_t *n_ttiles, int32_t *counters, cudaStream_t s);
+/* which: 0 = q|k|v projection (out_bf16 [T][5120]), 1 = output projection (added into resid [T][2048]) */
+cudaError_t omni_launch_dense_pair(int which, const CUtensorMap *tm_w, const CUtensorMap *tm_tok4, const omni_sort_state st,
+                                   int32_t *work_counter, void *out_bf16, float *resid, int n_sm, cudaStream_t s);
+/* qkv [T][5120] BF16 -> Q [32][T][128], K [4][T][128], Vt [4][128][vpitch] (column vcol[t] for token t), BF16;
+ * pos [T][3] positions (temporal, row, column); head_stride: rows between two heads of Q and K */
+cudaError_t omni_launch_attn_prep(const void *qkv, const float *qw, const float *kw, const int32_t *pos, const int32_t *vcol, int T,
+                                  int head_stride, int vpitch, float eps, double theta, void *Q, void *K, void *Vt, uint32_t *status,
+                                  cudaStream_t s);
+/* tiles: [n_tiles] x {record start, first query row, rows (<= 128), Vt column of the record start}; out [T][4096] BF16 */
+cudaError_t omni_launch_attention(const CUtensorMap *tm_q, const CUtensorMap *tm_k, const CUtensorMap *tm_vt, const void *tiles,
+                                  int n_tiles, int T, void *out, uint32_t *status, cudaStream_t s);
 
 /* Programmatic dependent launch of the pass's kernel chain (process-wide, default on) */
 void omni_set_dependent_launch(int on);

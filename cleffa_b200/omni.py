@@ -38,6 +38,7 @@ EXPORTS = [
     "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
     "clef_omni_assign_noalloc", "clef_omni_ep_sync",
     "clef_omni_bind_norm", "clef_omni_encode_norm_moe", "clef_omni_bind_gguf", "clef_omni_gguf_check",
+    "clef_omni_bind_attention", "clef_omni_encode_attention",
 ]
 NOALLOC_MAX_ROWS = 4096
 EP_HANDLES, EP_HANDLE_BYTES = 6, 64
@@ -81,6 +82,8 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_bind_norm": (C.c_bool, [vp, ci, vp, C.c_float, ci, cc, cz]),
         "clef_omni_encode_norm_moe": (C.c_bool, [vp, ci, vp, ci, ci, vp, cc, cz]),
         "clef_omni_bind_gguf": (C.c_bool, [vp, cc, ci, cc, cz]),
+        "clef_omni_bind_attention": (C.c_bool, [vp, ci, vp, vp, vp, vp, vp, C.c_float, C.c_float, ci, cc, cz]),
+        "clef_omni_encode_attention": (C.c_bool, [vp, ci, vp, vp, ci, ci, vp, cc, cz]),
         "clef_omni_gguf_check": (C.c_bool, [cc, ci, ci, ci, ci, C.POINTER(C.c_float), cc, cz]),
     }
     for name, (res, args) in sig.items():
@@ -211,6 +214,29 @@ class OmniBackend:
         seq_bounds = np.ascontiguousarray(seq_bounds, dtype=np.int32)
         self._check(self.lib.clef_omni_encode_norm_moe(self._g, layer, _ptr(x), T, len(seq_bounds) - 1, _ptr(seq_bounds),
                                                        self._err, _ERRLEN))
+
+    def bind_attention(self, layer: int, attn_norm, attn_qkv, attn_output, q_norm, k_norm, eps: float = 1e-6, rope_theta: float = 1e6):
+        """Tensors of the layer's attention half (host or CUDA tensors, all on the same side; the library copies them)."""
+        for t, shape, dt in ((attn_norm, (H,), torch.float32), (attn_qkv, (5120, H), torch.bfloat16), (attn_output, (H, 4096), torch.bfloat16),
+                             (q_norm, (128,), torch.float32), (k_norm, (128,), torch.float32)):
+            if tuple(t.shape) != shape or t.dtype != dt or not t.is_contiguous():
+                raise ValueError(f"expected contiguous {dt} {shape}, got {t.dtype} {tuple(t.shape)}")
+        where = DEVICE if attn_qkv.is_cuda else HOST
+        self._check(self.lib.clef_omni_bind_attention(self._g, layer, _ptr(attn_norm), _ptr(attn_qkv), _ptr(attn_output), _ptr(q_norm),
+                                                      _ptr(k_norm), float(eps), float(rope_theta), where, self._err, _ERRLEN))
+
+    def encode_attention(self, layer: int, x: torch.Tensor, pos3: torch.Tensor, seq_bounds=None):
+        """x[T][2048] (float32, CUDA) += attention half; pos3 int32 CUDA [T][3].  Asynchronous."""
+        T = x.shape[0]
+        if x.dtype != torch.float32 or tuple(x.shape) != (T, H) or not x.is_cuda:
+            raise ValueError("x must be a CUDA float32 [T,2048] tensor")
+        if pos3.dtype != torch.int32 or tuple(pos3.shape) != (T, 3) or not pos3.is_cuda or not pos3.is_contiguous():
+            raise ValueError("pos3 must be a contiguous CUDA int32 [T,3] tensor")
+        if seq_bounds is None:
+            seq_bounds = np.array([0, T], dtype=np.int32)
+        seq_bounds = np.ascontiguousarray(seq_bounds, dtype=np.int32)
+        self._check(self.lib.clef_omni_encode_attention(self._g, layer, _ptr(x), _ptr(pos3), T, len(seq_bounds) - 1, _ptr(seq_bounds),
+                                                        self._err, _ERRLEN))
 
     def bind_gguf(self, path, n_layer: int):
         """Bind layers 0..n_layer-1 (experts, router, ffn_norm) from a converted checkpoint file."""

@@ -137,6 +137,32 @@ bool clef_omni_bind_norm(clef_gpu *g, int layer, const float *weight, float eps,
 bool clef_omni_encode_norm_moe(clef_gpu *g, int layer, float *x, int T, int n_seq, const int32_t *seq_bounds,
                                char *err, size_t errlen);
 
+/* The attention half in front of it: clef_omni_encode_attention (clef_metal_omni.m:200-246), the
+ * sequence norm(attn_norm) -> q|k|v projection -> omni_attn_prep (per-head RMS norm of q and k,
+ * interleaved three-axis rotary; clef.metal:2073-2130) -> omni_attention (causal inside each record
+ * of the packed batch, 32 query heads over 4 key/value heads of 128; clef.metal:2174-2319) -> output
+ * projection added into the residual.  The reference's closing norm(ffn_norm) is the first step of
+ * clef_omni_encode_norm_moe.  Tensors of one layer, in the converted layout (clef_engine.h:35-40):
+ *   attn_norm  FP32 [2048]            (blk.N.attn_norm.weight)
+ *   attn_qkv   BF16 [5120][2048]      (blk.N.attn_qkv.weight: 4096 query rows, 512 key rows, 512 value rows)
+ *   attn_output BF16 [2048][4096]     (blk.N.attn_output.weight)
+ *   q_norm, k_norm FP32 [128]         (blk.N.attn_q_norm / attn_k_norm.weight)
+ * eps and rope_theta are clef_config's (1e-6 and 1e6 for Clef-Omni, clef.c:84-86).  where as in
+ * clef_omni_bind_layer; the library keeps its own device copy.  The first binding allocates the
+ * scratch of the attention half (0.6 GB, independent of T). */
+bool clef_omni_bind_attention(clef_gpu *g, int layer, const float *attn_norm, const void *attn_qkv, const void *attn_output,
+                              const float *q_norm, const float *k_norm, float eps, float rope_theta, int where, char *err,
+                              size_t errlen);
+/* x (device FP32 [T][2048], the residual stream) += attention half of `layer`.  pos3: device int32
+ * [T][3], each token's temporal, row and column rotary position (clef_record_positions; all three
+ * equal to the index inside the record for text).  seq_bounds: host, n_seq + 1 ascending offsets
+ * ending at T; a token attends to the earlier tokens of its own record.  T <= 16384 per call.
+ * Asynchronous like clef_omni_encode_moe; nonfinite q/k/v set status bit 1 (value 2) as in the
+ * reference (clef.metal:2120) and fail clef_omni_complete.  BF16 operands on the tensor cores,
+ * FP32 softmax and accumulation. */
+bool clef_omni_encode_attention(clef_gpu *g, int layer, float *x, const int32_t *pos3, int T, int n_seq,
+                                const int32_t *seq_bounds, char *err, size_t errlen);
+
 /* Binds layers 0..n_layer-1 from a converted checkpoint (GGUF v3 as tools/convert_omni.py:135-139
  * writes it): router, gate/up and down expert tensors and the ffn_norm weights, with the type,
  * rank and extent checks and messages of clef.c:194-246 (`bind_experts`, `bind_weights`), after the
@@ -232,7 +258,9 @@ bool clef_omni_assign_noalloc(const int32_t *ids, int rows, int32_t *counts, int
  * "ids" int32[T][8], "weights" f32[T][8], "logits" f32[T][128], "counts" int32[128],
  * "offsets" int32[129], "rowmap" int32[T*8], "slots" int32[T*8], "status" u32,
  * "rechecked" int32 (rows whose order was decided by the exact pass), "xnorm" bf16[T][2048]
- * (the normalised rows clef_omni_encode_norm_moe fed to the block). */
+ * (the normalised rows clef_omni_encode_norm_moe fed to the block); of the last attention pass:
+ * "attn_qkv" bf16 [T][5120] (the q|k|v projections) and "attn_out" bf16 [T][4096] (the attention
+ * output before the output projection). */
 bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char *err, size_t errlen);
 /* Options: "debug_poison" 0/1 (CLEF_DEBUG_POISON), "router_exact" 0/1 (decide every row with
  * FP64 logits), "router_eps" (bound on the tensor-core logit error, x1e-9), "gemm" 0 =
