@@ -446,6 +446,87 @@ def ours(args):
         raise SystemExit("expert-parallel output differs from the single-GPU output")
 
 
+def attention_bench(args):
+    """The attention half in front of the block (and, with --layers N, whole decoder layers:
+    attention half + norm + MoE): one GPU, seeded random weights, text-like positions.  One JSON line
+    with the time per pass of the attention half alone and of the layer, and the attention half's
+    FLOP rate (projections 2 T (2048 x 5120 + 4096 x 2048), attention 4 x 128 x 32 x sum over records of L(L+1)/2)."""
+    import numpy as np
+    import torch
+    from cleffa_b200 import OmniBackend, workloads
+    from oracle import omni_attn_oracle as ao     # weight and position generators only (not the timed path)
+
+    torch.cuda.set_device(0)
+    T, n_layers = T_TOKENS, max(1, args.layers)
+    single = n_layers > 1 or T > 4096
+    bounds = np.array([0, T], np.int32) if single else workloads.varlen_bounds(SEED, T)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    peaks = measured_peaks()
+    with OmniBackend(0, stream=stream.cuda_stream) as b:
+        b.reserve(T, n_layer=n_layers)
+        g = torch.Generator(device="cuda").manual_seed(SEED)
+        router, gate_up, down = workloads.make_weights(SEED)
+        aw = ao.make_attention_weights(SEED)
+        for l in range(n_layers):
+            if l == 0:
+                b.bind_layer(0, router, gate_up, down)
+                b.bind_attention(0, aw["attn_norm"], aw["w_qkv"], aw["w_out"], aw["q_norm"], aw["k_norm"])
+            else:
+                b.bind_layer(l, *[(torch.randn(sh, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                                  for sh in ((E, H), (E, 2 * F, H), (E, H, F))])
+                qkv, out = [(torch.randn(sh, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16) for sh in ((5120, H), (H, 4096))]
+                b.bind_attention(l, torch.ones(H, device="cuda"), qkv, out, torch.ones(128, device="cuda"), torch.ones(128, device="cuda"))
+            b.bind_norm(l, torch.ones(H), 1e-6)
+        pos = torch.from_numpy(np.ascontiguousarray(ao.make_positions(SEED, bounds).T)).cuda()
+        x0 = workloads.make_activations(SEED, T).float().cuda()
+        x = x0.clone()
+
+        def run(attention_only):
+            x.copy_(x0)
+            b.begin()
+            for l in range(n_layers):
+                b.encode_attention(l, x, pos, bounds)
+                if not attention_only:
+                    b.encode_norm_moe(l, x, bounds)
+
+        def timed(attention_only):
+            for _ in range(max(3, args.warmup)):
+                run(attention_only)
+            b.complete()
+            regions = []
+            while sum(regions) < args.min_time_ms and len(regions) < args.max_regions:
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record(stream)
+                for _ in range(args.steps):
+                    run(attention_only)
+                stop.record(stream)
+                b.complete()
+                regions.append(start.elapsed_time(stop))
+            return statistics.median(regions) / args.steps, len(regions)
+
+        with ClockSampler(0) as sampler:
+            attn_ms, n1 = timed(True)
+            layer_ms, n2 = timed(False)
+        lens = np.diff(bounds).astype(np.float64)
+        flop = n_layers * (2.0 * T * (H * 5120 + 4096 * H) + 4.0 * 128 * 32 * float((lens * (lens + 1) / 2).sum()))
+        print(json.dumps({
+            "metric": f"decoder-layer prefill tokens/sec at T={T}" + (f" through {n_layers} layers" if n_layers > 1 else ""),
+            "value": T / (layer_ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": layer_ms, "regions": n2, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"Clef-Omni decoder layer(s): attention half (32/4 heads of 128, causal per record) + RMSNorm + MoE block, T={T}, "
+                                   f"{len(lens)} record(s), {n_layers} layer(s), bf16 weights N(0,0.02), seed {SEED}",
+                       "timing": f"CUDA events around exactly {args.steps} passes, median of the regions"},
+            "attention_half": {"ms_per_pass": attn_ms, "ms_per_layer": attn_ms / n_layers, "tflops": flop / (attn_ms * 1e-3) / 1e12,
+                               "frac_of_bf16_peak": flop / (attn_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "regions": n1,
+                               "flop": flop},
+            "moe_half_ms_per_layer": (layer_ms - attn_ms) / n_layers,
+            "clocks": sampler.summary(),
+        }), flush=True)
+
+
 def sweep(args):
     """BASELINE configuration 5: layer latency and achieved weight-streaming bandwidth at small
     batch sizes (seed 4), one GPU.  One JSON line holding the whole table."""
@@ -503,6 +584,7 @@ def main():
     ap.add_argument("--seed", type=int, default=None, help="workload seed (default 1; 2 with --layers, 3 with --bias zipf)")
     ap.add_argument("--min-time-ms", type=float, default=1000.0, help="repeat the K-step timed region until this much device time was timed")
     ap.add_argument("--max-regions", type=int, default=400)
+    ap.add_argument("--attention", action="store_true", help="time the attention half and whole decoder layers (attention + norm + MoE), one GPU")
     ap.add_argument("--sweep", action="store_true", help="BASELINE configuration 5: latency table over small batch sizes, one GPU")
     ap.add_argument("--sweep-tokens", type=int, nargs="+", default=[1, 8, 32, 64, 128, 256])
     ap.add_argument("--norm", action="store_true", help="with --layers: each layer normalises the residual stream itself (RMSNorm, unit weights) instead of taking a BF16 copy")
@@ -512,7 +594,9 @@ def main():
     args = ap.parse_args()
     T_TOKENS = args.tokens
     SEED = args.seed if args.seed is not None else (3 if args.bias == "zipf" else 2 if args.layers > 1 else 1)
-    if args.sweep:
+    if args.attention:
+        attention_bench(args)
+    elif args.sweep:
         sweep(args)
     elif args.impl == "reference":
         reference_arm(args)

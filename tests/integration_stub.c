@@ -19,16 +19,21 @@ bool cuda_backend_open(const clef_engine *e, char *err, size_t errlen) {
             return false;
         if (!clef_omni_bind_norm(G, l, (const float *)w->ffn_norm->data, e->cfg.eps, CLEF_OMNI_HOST, err, errlen))
             return false;
+        if (!clef_omni_bind_attention(G, l, (const float *)w->attn_norm->data, w->attn_qkv->data, w->attn_output->data,
+                                      (const float *)w->attn_q_norm->data, (const float *)w->attn_k_norm->data, e->cfg.eps,
+                                      e->cfg.rope_theta, CLEF_OMNI_HOST, err, errlen))
+            return false;
     }
     return clef_omni_trace_reserve(G, 1, e->cfg.n_layer, e->route_rows, e->capture_routes, err, errlen);
 }
 
-/* one pass over a packed batch: d_x is the FP32 residual stream on the device, [T][H] */
-bool cuda_backend_moe_layers(const clef_engine *e, float *d_x, int T, int n_seq, const int32_t *seq_bounds,
-                             char *err, size_t errlen) {
+/* one pass over a packed batch: d_x is the FP32 residual stream on the device, [T][H]; d_pos3 the
+ * tokens' three rotary positions, [T][3] (clef_record_positions), also on the device */
+bool cuda_backend_layers(const clef_engine *e, float *d_x, const int32_t *d_pos3, int T, int n_seq, const int32_t *seq_bounds,
+                         char *err, size_t errlen) {
     clef_omni_begin(G);                                        /* once per pass (clef_metal.m:1150) */
-    for (int l = 0; l < e->cfg.n_layer; l++) {
-        /* ... the attention half of the layer updates d_x here ... */
+    for (int l = 0; l < e->cfg.n_layer; l++) {                 /* clef_omni_encode_layer, clef_metal_omni.m:248 */
+        if (!clef_omni_encode_attention(G, l, d_x, d_pos3, T, n_seq, seq_bounds, err, errlen)) return false;
         if (!clef_omni_encode_norm_moe(G, l, d_x, T, n_seq, seq_bounds, err, errlen)) return false;
     }
     return clef_omni_complete(G, err, errlen);                 /* clef_metal.m:1597 */
