@@ -495,7 +495,7 @@ def attention_bench(args):
                 run(attention_only)
             b.complete()
             regions = []
-            while sum(regions) < args.min_time_ms and len(regions) < args.max_regions:
+            while not regions or (sum(regions) < args.min_time_ms and len(regions) < args.max_regions):
                 torch.cuda.synchronize()
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record(stream)

@@ -38,69 +38,99 @@ __global__ void dense_tiles_kernel(int T, omni_ttile *ttiles, int32_t *n_ttiles,
 }
 
 // ------------------------------------------------------------------ q/k norm + rotary + layout
-// One warp per (token, head): 128 values, four per lane (elements lane + 32 j).  Pair p of a head
-// is (element p, element p + 64); its angle is position[axis] * theta^(-p/64) with axis = p % 3 for
-// p < 60 and the temporal axis above (sections 24/20/20 interleaved; clef.metal:2051-2053).  The
-// angle is formed and reduced in FP64: FP32 loses ~pos * 6e-8 rad (clef.metal:2055-2060).
+// One block per token, four warps, nine heads each (32 query heads, then the 4 key heads): 128
+// values per head, four per lane (elements lane + 32 j).  Pair p of a head is (element p, element
+// p + 64); its angle is position[axis] * theta^(-p/64) with axis = p % 3 for p < 60 and the
+// temporal axis above (sections 24/20/20 interleaved; clef.metal:2051-2053).  The angle is formed
+// and reduced modulo 2 pi in FP64 -- FP32 loses ~pos * 6e-8 rad (clef.metal:2055-2060) -- and its
+// cosine and sine, the same for every head of the token, are computed once per warp.
 __global__ void __launch_bounds__(128) attn_prep_kernel(const __nv_bfloat16 *__restrict__ qkv, const float *__restrict__ qw,
                                                         const float *__restrict__ kw, const int32_t *__restrict__ pos,
-                                                        const int32_t *__restrict__ vcol, int T /* head stride of Q and K, in rows */, int vpitch, float eps, double theta,
+                                                        int head_stride, float eps, double theta,
                                                         __nv_bfloat16 *__restrict__ Q, __nv_bfloat16 *__restrict__ K,
-                                                        __nv_bfloat16 *__restrict__ Vt, uint32_t *__restrict__ status) {
+                                                        uint32_t *__restrict__ status) {
     dep_wait();
     dep_launch();
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = blockIdx.x;
-    const int h = blockIdx.y * 4 + (threadIdx.x >> 5);             // 0..31 query heads, 32..35 key heads (with their values)
-    if (h >= NH + NKV) return;
-    const bool query = h < NH;
-    const int kh = h - NH;
-    const __nv_bfloat16 *src = qkv + t * OMNI_QKV + (long)h * HD;
-    const float *w = query ? qw : kw;
-    float x[4], sum = 0.f;
-    bool bad = false;
-#pragma unroll
-    for (int j = 0; j < 4; j++) { x[j] = __bfloat162float(src[lane + 32 * j]); bad |= !(fabsf(x[j]) < CUDART_INF_F); sum += x[j] * x[j]; }
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
-    const float inv = rsqrtf(sum / (float)HD + eps);
-#pragma unroll
-    for (int j = 0; j < 4; j++) x[j] = x[j] * inv * __ldg(w + lane + 32 * j);
+    float cs[2], sn[2];
 #pragma unroll
     for (int j = 0; j < 2; j++) {
         const int pair = lane + 32 * j, axis = pair < 60 ? pair % 3 : 0;
-        const double angle = (double)__ldg(pos + 3 * t + axis) * pow(theta, -(double)pair / 64.0);
-        double sn, cs;
-        sincos(angle, &sn, &cs);
-        const float c = (float)cs, s = (float)sn, lo = x[j], hi = x[j + 2];
-        x[j] = lo * c - hi * s;
-        x[j + 2] = hi * c + lo * s;
+        const double angle = (double)__ldg(pos + 3 * t + axis) * exp2(-(double)pair * (1.0 / 64.0) * log2(theta));
+        const double turns = rint(angle * 0.15915494309189535);
+        const float r = (float)fma(-turns, 6.283185307179586, angle);           // |r| <= pi, accurate to FP32 rounding
+        sincosf(r, &sn[j], &cs[j]);
     }
-    __nv_bfloat16 *dst = query ? Q + ((long)h * T + t) * HD : K + ((long)kh * T + t) * HD;
+    float wq[4], wk[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) { bad |= !(fabsf(x[j]) < CUDART_INF_F); dst[lane + 32 * j] = __float2bfloat16(x[j]); }
-    if (!query) {
-        // the head's values, transposed: Vt[kh][d][column of the token]
-        const __nv_bfloat16 *vs = qkv + t * OMNI_QKV + (long)(NH + NKV + kh) * HD;
-        const long col = __ldg(vcol + t);
+    for (int j = 0; j < 4; j++) { wq[j] = __ldg(qw + lane + 32 * j); wk[j] = __ldg(kw + lane + 32 * j); }
+    bool bad = false;
+    for (int h = warp; h < NH + NKV; h += 4) {
+        const bool query = h < NH;
+        const __nv_bfloat16 *src = qkv + t * OMNI_QKV + (long)h * HD;
+        float x[4], sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const __nv_bfloat16 v = vs[lane + 32 * j];
-            bad |= !(fabsf(__bfloat162float(v)) < CUDART_INF_F);
-            Vt[((long)kh * HD + lane + 32 * j) * vpitch + col] = v;
+        for (int j = 0; j < 4; j++) { x[j] = __bfloat162float(src[lane + 32 * j]); bad |= !(fabsf(x[j]) < CUDART_INF_F); sum += x[j] * x[j]; }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+        const float inv = rsqrtf(sum / (float)HD + eps);
+#pragma unroll
+        for (int j = 0; j < 4; j++) x[j] = x[j] * inv * (query ? wq[j] : wk[j]);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const float lo = x[j], hi = x[j + 2];
+            x[j] = lo * cs[j] - hi * sn[j];
+            x[j + 2] = hi * cs[j] + lo * sn[j];
         }
+        __nv_bfloat16 *dst = query ? Q + ((long)h * head_stride + t) * HD : K + ((long)(h - NH) * head_stride + t) * HD;
+#pragma unroll
+        for (int j = 0; j < 4; j++) { bad |= !(fabsf(x[j]) < CUDART_INF_F); dst[lane + 32 * j] = __float2bfloat16(x[j]); }
     }
     // reported at completion like the reference's status bit 2 (clef.metal:2120)
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, OMNI_ST_ATTN_NONFINITE);
+}
+
+// Values, transposed: Vt[kh][d][column of the token].  One block per (64 tokens, key/value head):
+// rows read whole (256 bytes per token), written as 64-token runs per head dimension.
+__global__ void __launch_bounds__(256) v_transpose_kernel(const __nv_bfloat16 *__restrict__ qkv, const int32_t *__restrict__ vcol,
+                                                          int T, int vpitch, __nv_bfloat16 *__restrict__ Vt,
+                                                          uint32_t *__restrict__ status) {
+    __shared__ unsigned short tile[64][HD + 2];
+    __shared__ int col[64];
+    dep_wait();
+    dep_launch();
+    const int t0 = blockIdx.x * 64, kh = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    bool bad = false;
+    if (threadIdx.x < 64) col[threadIdx.x] = t0 + threadIdx.x < T ? __ldg(vcol + t0 + threadIdx.x) : -1;
+    for (int i = warp; i < 64; i += 8) {
+        const long t = t0 + i;
+        if (t < T) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(qkv + t * OMNI_QKV + (long)(NH + NKV + kh) * HD + lane * 4);
+            const unsigned short e[4] = {(unsigned short)(v.x & 0xffff), (unsigned short)(v.x >> 16), (unsigned short)(v.y & 0xffff), (unsigned short)(v.y >> 16)};
+#pragma unroll
+            for (int k = 0; k < 4; k++) { bad |= (e[k] & 0x7f80) == 0x7f80; tile[i][lane * 4 + k] = e[k]; }
+        }
+    }
+    __syncthreads();
+    unsigned short *out = reinterpret_cast<unsigned short *>(Vt) + (long)kh * HD * vpitch;
+    for (int d = warp; d < HD; d += 8)
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const int i = lane + 32 * k;
+            if (col[i] >= 0) out[(long)d * vpitch + col[i]] = tile[i][d];
+        }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, OMNI_ST_ATTN_NONFINITE);
 }
 
 // ------------------------------------------------------------------ attention
 struct AttnTile { int32_t rec_start, q0, q_len, vcol0; };          // vcol0: Vt column of the record's first token
 
-constexpr int AT_THREADS = 256;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..7 softmax
+constexpr int AT_THREADS = 384;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..11 softmax (two threads per query row)
 constexpr int AT_TILE_BYTES = 128 * 128 * 2;                       // 32 KiB: 128 rows x 128 BF16 as two 64-column halves
 constexpr int AT_KV_STAGES = 2;
-constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + 256;     // Q, P, K and Vt stages
+constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + 64 + 32 + 1024 + 64;     // Q, P, K and Vt stages; barriers; exchange
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -122,6 +152,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
     volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);          // [3]: q, kv stage 0, kv stage 1 (parity, -1 none)
+    volatile int *quit = reinterpret_cast<volatile int *>(misc + 20);          // a softmax thread's wait ran out: all of them leave together
+    float *xch = reinterpret_cast<float *>(misc + 32);                         // [2][128] what the two threads of a row tell each other
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const AttnTile tile = tiles[blockIdx.x];
@@ -132,8 +164,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < AT_KV_STAGES; s++) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
-        mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(o_full, 1);
+        mbar_init(s_full, 1); mbar_init(p_full, 256); mbar_init(o_full, 1);
         *abort_flag = 0;
+        *quit = 0;
         armed[0] = armed[1] = armed[2] = -1;
         fence_mbar_init();
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_vt);
@@ -167,23 +200,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------- MMA issuer
+        // S_0, then per block: O_j = P_j V_j as soon as P_j is written (the softmax threads are done
+        // with S_j by then), and straight after it S_{j+1}, so that the next scores are ready while
+        // the softmax threads still add O_j into their registers.
         const uint32_t idesc = idesc_bf16(128, 128);
-        PipeState p;
-        bool ok = mbar_wait(q_full, 0, abort_flag, status);
-        for (int j = 0; j < n_blocks && ok; j++) {
-            ok = mbar_wait(kv_full(p.stage), p.phase, abort_flag, status);
-            if (!ok) break;
-            tc_fence_after();
-            // S = Q K^T over the 128 head dimensions: two 64-wide halves, four K=16 steps each
+        auto scores = [&](int stage) {       // S = Q K^T over the 128 head dimensions: two 64-wide halves, four K=16 steps each
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 const uint64_t da = smem_desc_sw128(q_smem + half * (AT_TILE_BYTES / 2));
-                const uint64_t db = smem_desc_sw128(k_smem(p.stage) + half * (AT_TILE_BYTES / 2));
+                const uint64_t db = smem_desc_sw128(k_smem(stage) + half * (AT_TILE_BYTES / 2));
 #pragma unroll
                 for (int k = 0; k < 4; k++) umma_bf16(tmem_s, da + 2u * k, db + 2u * k, idesc, (half | k) ? 1u : 0u);
             }
             umma_commit(s_full);
-            // O_j = P V_j once the softmax threads have written P (which also means they are done with S)
+        };
+        PipeState p, nx;
+        bool ok = mbar_wait(q_full, 0, abort_flag, status) && mbar_wait(kv_full(0), 0, abort_flag, status);
+        if (ok) { tc_fence_after(); scores(0); nx.advance(AT_KV_STAGES); }
+        for (int j = 0; j < n_blocks && ok; j++) {
             ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, status);
             if (!ok) break;
             tc_fence_after();
@@ -197,86 +231,101 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             umma_commit(kv_empty(p.stage));                // K and Vt of this block are free once both products are done
             umma_commit(o_full);
             p.advance(AT_KV_STAGES);
+            if (j + 1 < n_blocks) {
+                ok = mbar_wait(kv_full(nx.stage), nx.phase, abort_flag, status);
+                if (!ok) break;
+                tc_fence_after();
+                scores(nx.stage);
+                nx.advance(AT_KV_STAGES);
+            }
         }
     } else if (warp >= 4) {
-        // ---------------------------------------------------------- softmax + accumulation: one query row per thread
-        const int q4 = warp & 3;
+        // ---------------------------------------------------------- softmax + accumulation: two threads per query row
+        // Thread (row r, half hf) owns keys hf*64.. of every score block and head dimensions hf*64.. of
+        // the output.  The two threads of a row sit in different warps and exchange their partial
+        // row maxima through shared memory at a named barrier; a thread whose wait ran out marks
+        // `quit` and still joins that barrier, after which all of them leave together.
+        const int q4 = warp & 3, hf = (warp - 4) >> 2;
         const int r = q4 * 32 + lane;                                             // row inside the tile = TMEM lane
         const int qg = tile.q0 + r;                                               // global token index of the row
-        const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
-        float acc[HD];
+        const uint32_t lane_addr = ((uint32_t)(q4 * 32) << 16) + hf * 64;
+        float acc[64];
 #pragma unroll
-        for (int d = 0; d < HD; d++) acc[d] = 0.f;
+        for (int d = 0; d < 64; d++) acc[d] = 0.f;
         float m = -CUDART_INF_F, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_blocks && ok; j++) {
-            ok = mbar_wait(s_full, (uint32_t)j & 1u, abort_flag, status);
-            if (!ok) break;
-            tc_fence_after();
-            const int key0 = tile.rec_start + j * 128;
-            // first sweep over the scores: the row's new maximum (the scores stay in tensor memory)
-            float mx = m;
+        bool alive = true;
+        for (int j = 0; j < n_blocks; j++) {
+            if (alive) alive = mbar_wait(s_full, (uint32_t)j & 1u, abort_flag, status);
+            const int key0 = tile.rec_start + j * 128 + hf * 64;
+            float sc[64], pmax = -CUDART_INF_F;
+            if (alive) {
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t t32[32];
-                tmem_ld32(tmem_s + lane_addr + c * 32, t32);
-                tmem_ld_wait();
+                for (int c = 0; c < 2; c++) {
+                    uint32_t t32[32];
+                    tmem_ld32(tmem_s + lane_addr + c * 32, t32);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; i++)
-                    if (key0 + c * 32 + i <= qg) mx = fmaxf(mx, __uint_as_float(t32[i]) * scale);
+                    for (int i = 0; i < 32; i++) {
+                        sc[c * 32 + i] = key0 + c * 32 + i <= qg ? __uint_as_float(t32[i]) * scale : -CUDART_INF_F;
+                        pmax = fmaxf(pmax, sc[c * 32 + i]);
+                    }
+                }
+                xch[hf * 128 + r] = pmax;
+            } else {
+                *quit = 1;
             }
-            // every block holds at least one key the row may see (tiles and blocks are both cut
-            // from the record's start in steps of 128), so mx is finite
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (*quit) break;
+            // every block holds at least one key the row may see (tiles and blocks are both cut from
+            // the record's start in steps of 128), so the row maximum is finite
+            const float mx = fmaxf(m, fmaxf(pmax, xch[(hf ^ 1) * 128 + r]));
             const float corr = __expf(m - mx);
             float sum = 0.f;
-            // second sweep: P = exp(s - mx) as BF16 into the swizzled K-major layout (two halves of
-            // 64 keys; row r is 128 bytes per half, chunk c8 of 8 keys at c8 ^ (r & 7))
-            uint8_t *prow = smem_gen + AT_TILE_BYTES + r * 128;
+            // P = exp(s - mx) as BF16 into the swizzled K-major layout: this thread's 64 keys are one
+            // 128-byte row of its half tile, chunk c8 of 8 keys at c8 ^ (r & 7)
+            uint8_t *prow = smem_gen + AT_TILE_BYTES + hf * (AT_TILE_BYTES / 2) + r * 128;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t t32[32];
-                tmem_ld32(tmem_s + lane_addr + c * 32, t32);
-                tmem_ld_wait();
+            for (int c8 = 0; c8 < 8; c8++) {
+                uint32_t w[4];
 #pragma unroll
-                for (int c4 = 0; c4 < 4; c4++) {                                  // four chunks of 8 keys
-                    uint32_t w[4];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int k0 = c * 32 + c4 * 8 + 2 * i;
-                        const float p0 = key0 + k0 <= qg ? __expf(__uint_as_float(t32[c4 * 8 + 2 * i]) * scale - mx) : 0.f;
-                        const float p1 = key0 + k0 + 1 <= qg ? __expf(__uint_as_float(t32[c4 * 8 + 2 * i + 1]) * scale - mx) : 0.f;
-                        const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                        // the sum uses the rounded probabilities the second product multiplies with
-                        sum += __bfloat162float(b.x) + __bfloat162float(b.y);
-                        w[i] = *reinterpret_cast<const uint32_t *>(&b);
-                    }
-                    const int ch = c * 4 + c4, half = ch >> 3, c8 = ch & 7;
-                    *reinterpret_cast<uint4 *>(prow + half * (AT_TILE_BYTES / 2) + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int i = 0; i < 4; i++) {
+                    const __nv_bfloat162 b = __floats2bfloat162_rn(__expf(sc[c8 * 8 + 2 * i] - mx), __expf(sc[c8 * 8 + 2 * i + 1] - mx));
+                    // the sum uses the rounded probabilities the second product multiplies with
+                    sum += __bfloat162float(b.x) + __bfloat162float(b.y);
+                    w[i] = *reinterpret_cast<const uint32_t *>(&b);
                 }
+                *reinterpret_cast<uint4 *>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             l = l * corr + sum;
             m = mx;
             tc_fence_before();
             fence_proxy_async_smem();
             mbar_arrive(p_full);
-            ok = mbar_wait(o_full, (uint32_t)j & 1u, abort_flag, status);
-            if (!ok) break;
-            tc_fence_after();
+            alive = mbar_wait(o_full, (uint32_t)j & 1u, abort_flag, status);
+            if (alive) {
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t t32[32];
-                tmem_ld32(tmem_o + lane_addr + c * 32, t32);
-                tmem_ld_wait();
+                for (int c = 0; c < 2; c++) {
+                    uint32_t t32[32];
+                    tmem_ld32(tmem_o + lane_addr + c * 32, t32);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; i++) acc[c * 32 + i] = acc[c * 32 + i] * corr + __uint_as_float(t32[i]);
+                    for (int i = 0; i < 32; i++) acc[c * 32 + i] = acc[c * 32 + i] * corr + __uint_as_float(t32[i]);
+                }
+                tc_fence_before();
             }
-            tc_fence_before();
         }
-        if (ok && r < tile.q_len) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + h * HD);
+        // the row's denominator is the sum of what its two threads added up (same maximum in both)
+        if (!alive) *quit = 1;
+        xch[hf * 128 + r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (!*quit && r < tile.q_len) {
+            const float lt = l + xch[(hf ^ 1) * 128 + r];
+            const float inv = lt > 0.f ? 1.f / lt : 0.f;
+            uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + h * HD + hf * 64);
 #pragma unroll
-            for (int ch = 0; ch < 16; ch++) {
+            for (int ch = 0; ch < 8; ch++) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
@@ -320,8 +369,11 @@ cudaError_t omni_launch_dense_tiles(int T, omni_ttile *ttiles, int32_t *n_ttiles
 cudaError_t omni_launch_attn_prep(const void *qkv, const float *qw, const float *kw, const int32_t *pos, const int32_t *vcol, int T,
                                   int head_stride, int vpitch, float eps, double theta, void *Q, void *K, void *Vt, uint32_t *status,
                                   cudaStream_t s) {
-    return omni_launch_chain(attn_prep_kernel, dim3(T, (OMNI_NH + OMNI_NKV + 3) / 4), dim3(128), 0, s, (const __nv_bfloat16 *)qkv, qw, kw, pos,
-                             vcol, head_stride, vpitch, eps, theta, (__nv_bfloat16 *)Q, (__nv_bfloat16 *)K, (__nv_bfloat16 *)Vt, status);
+    cudaError_t e = omni_launch_chain(attn_prep_kernel, dim3(T), dim3(128), 0, s, (const __nv_bfloat16 *)qkv, qw, kw, pos, head_stride, eps,
+                                      theta, (__nv_bfloat16 *)Q, (__nv_bfloat16 *)K, status);
+    if (e != cudaSuccess) return e;
+    return omni_launch_chain(v_transpose_kernel, dim3((T + 63) / 64, OMNI_NKV), dim3(256), 0, s, (const __nv_bfloat16 *)qkv, vcol, T, vpitch,
+                             (__nv_bfloat16 *)Vt, status);
 }
 
 // tiles: [n_tiles] of {record start, first query row, rows (<= 128), Vt column of the record start}
