@@ -125,13 +125,72 @@ __global__ void __launch_bounds__(256) v_transpose_kernel(const __nv_bfloat16 *_
 }
 
 // ------------------------------------------------------------------ attention
+// One CTA per (query head, tile of <= 128 query rows of one record).  Key blocks of 128 run from the
+// record's start to the tile's diagonal.  Per block j:
+//   S_j = Q K_j^T        tcgen05, FP32 in TMEM, two score buffers so that S_{j+1} is formed while
+//                        the softmax threads work on S_j
+//   P_j = exp2(c S_j - m)  256 threads, two per query row (64 keys each), BF16 into a swizzled
+//                        shared-memory tile
+//   O  += P_j V_j        tcgen05, accumulated in TMEM over all blocks
+// m is the row's reference maximum.  It follows the running maximum lazily: only when a block's
+// maximum exceeds it by more than 2^8 are O and the running sum rescaled (by the softmax threads,
+// in TMEM, between two value products); otherwise P simply holds values up to 256.  The result is
+// the same softmax; the accumulator never leaves TMEM until the tile is done.
 struct AttnTile { int32_t rec_start, q0, q_len, vcol0; };          // vcol0: Vt column of the record's first token
 
 constexpr int AT_THREADS = 384;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..11 softmax (two threads per query row)
 constexpr int AT_TILE_BYTES = 128 * 128 * 2;                       // 32 KiB: 128 rows x 128 BF16 as two 64-column halves
 constexpr int AT_KV_STAGES = 2;
-constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + 64 + 32 + 1024 + 64;     // Q, P, K and Vt stages; barriers; exchange
+constexpr int AT_TMEM_COLS = 512;                                  // S0, S1, O of 128 columns each
+constexpr int AT_N_BARS = 14;
+constexpr int AT_XCH_BYTES = 2 * 2 * 128 * 4;                      // [block parity][row half][row]
+constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + AT_N_BARS * 8 + 16 + 64 + AT_XCH_BYTES;
+#ifndef AT_DBG_KSTEPS
+#define AT_DBG_KSTEPS 4
+#endif
+constexpr float AT_LAZY = 8.f;                                     // log2 of how far a block may exceed the reference maximum
 
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(addr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {          // 2^x, -inf -> 0; relative error ~2^-22, far below BF16's
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two FP32 lanes per instruction: (a.x * b.x + c.x, a.y * b.y + c.y) and (a.x + b.x, a.y + b.y)
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)),
+        "l"(*reinterpret_cast<uint64_t *>(&c)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+#ifdef AT_DBG_CLOCK
+__device__ unsigned long long at_dbg[16];
+#define AT_TICK(k) { const long long now_ = clock64(); tk[k] += now_ - tprev; tprev = now_; }
+#else
+#define AT_TICK(k)
+#endif
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_vt, const AttnTile *__restrict__ tiles, int T, float scale,
@@ -143,17 +202,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     auto k_smem = [&](int s) { return smem_base + AT_TILE_BYTES * (2 + s); };
     auto v_smem = [&](int s) { return smem_base + AT_TILE_BYTES * (2 + AT_KV_STAGES + s); };
     const uint32_t bar_base = smem_base + AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES);
-    // barriers: q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, pv_done
     const uint32_t q_full = bar_base;
-    auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-    auto kv_empty = [&](int s) { return bar_base + 8u * (3 + s); };
-    const uint32_t s_full = bar_base + 8u * 5, p_full = bar_base + 8u * 6, o_full = bar_base + 8u * 7;
-    uint8_t *misc = smem_gen + AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 64;
+    auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
+    auto s_full = [&](int b) { return bar_base + 8u * (9 + b); };
+    const uint32_t p_full = bar_base + 8u * 11, pv_done = bar_base + 8u * 12;
+    uint8_t *misc = smem_gen + AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + AT_N_BARS * 8;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
-    volatile int *armed = reinterpret_cast<volatile int *>(misc + 8);          // [3]: q, kv stage 0, kv stage 1 (parity, -1 none)
-    volatile int *quit = reinterpret_cast<volatile int *>(misc + 20);          // a softmax thread's wait ran out: all of them leave together
-    float *xch = reinterpret_cast<float *>(misc + 32);                         // [2][128] what the two threads of a row tell each other
+    volatile int *quit = reinterpret_cast<volatile int *>(misc + 8);           // a softmax thread's wait ran out: all of them leave together
+    volatile int *armed = reinterpret_cast<volatile int *>(misc + 16);         // [5]: q, k stages, v stages (parity of the load in flight, -1 none)
+    float *xch = reinterpret_cast<float *>(misc + 16 + 64);                    // what the two threads of a row tell each other
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const AttnTile tile = tiles[blockIdx.x];
@@ -163,176 +225,238 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < AT_KV_STAGES; s++) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
-        mbar_init(s_full, 1); mbar_init(p_full, 256); mbar_init(o_full, 1);
+        for (int s = 0; s < AT_KV_STAGES; s++) {
+            mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
+            mbar_init(s_full(s), 1);
+        }
+        mbar_init(p_full, 256); mbar_init(pv_done, 1);
         *abort_flag = 0;
         *quit = 0;
-        armed[0] = armed[1] = armed[2] = -1;
+        for (int i = 0; i < 5; i++) armed[i] = -1;
         fence_mbar_init();
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_vt);
     }
-    if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 256); tmem_relinquish(); }
+    if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), AT_TMEM_COLS); tmem_relinquish(); }
     dep_wait();
     dep_launch();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+    const uint32_t tmem_o = tmem_base + 256;
 
     if (warp == 0 && lane == 0) {
-        // ---------------------------------------------------------- loads: Q once, then K / Vt blocks
+        // ---------------------------------------------------------- loads: Q once, then K one block ahead of Vt
         armed[0] = 0;
         mbar_expect_tx(q_full, AT_TILE_BYTES);
         tma_load_2d(q_smem, &tm_q, 0, h * T + tile.q0, q_full);                        // d 0..63
         tma_load_2d(q_smem + AT_TILE_BYTES / 2, &tm_q, 64, h * T + tile.q0, q_full);   // d 64..127
-        PipeState p;
-        for (int j = 0; j < n_blocks; j++) {
-            if (!mbar_wait(kv_empty(p.stage), p.phase ^ 1u, abort_flag, status)) break;
+        PipeState pk, pv;
+        auto load_k = [&](int j) {
+            if (!mbar_wait(k_empty(pk.stage), pk.phase ^ 1u, abort_flag, status)) return false;
             const int key0 = tile.rec_start + j * 128;
-            armed[1 + p.stage] = (int)p.phase;
-            mbar_expect_tx(kv_full(p.stage), 2 * AT_TILE_BYTES);
-            tma_load_2d(k_smem(p.stage), &tm_k, 0, kh * T + key0, kv_full(p.stage));
-            tma_load_2d(k_smem(p.stage) + AT_TILE_BYTES / 2, &tm_k, 64, kh * T + key0, kv_full(p.stage));
-            tma_load_2d(v_smem(p.stage), &tm_vt, tile.vcol0 + j * 128, kh * HD, kv_full(p.stage));            // keys 0..63 of the block
-            tma_load_2d(v_smem(p.stage) + AT_TILE_BYTES / 2, &tm_vt, tile.vcol0 + j * 128 + 64, kh * HD, kv_full(p.stage));
-            p.advance(AT_KV_STAGES);
+            armed[1 + pk.stage] = (int)pk.phase;
+            mbar_expect_tx(k_full(pk.stage), AT_TILE_BYTES);
+            tma_load_2d(k_smem(pk.stage), &tm_k, 0, kh * T + key0, k_full(pk.stage));
+            tma_load_2d(k_smem(pk.stage) + AT_TILE_BYTES / 2, &tm_k, 64, kh * T + key0, k_full(pk.stage));
+            pk.advance(AT_KV_STAGES);
+            return true;
+        };
+        bool ok = load_k(0);
+        for (int j = 0; j < n_blocks && ok; j++) {
+            if (j + 1 < n_blocks) ok = load_k(j + 1);
+            if (!ok || !mbar_wait(v_empty(pv.stage), pv.phase ^ 1u, abort_flag, status)) break;
+            armed[3 + pv.stage] = (int)pv.phase;
+            mbar_expect_tx(v_full(pv.stage), AT_TILE_BYTES);
+            tma_load_2d(v_smem(pv.stage), &tm_vt, tile.vcol0 + j * 128, kh * HD, v_full(pv.stage));            // keys 0..63 of the block
+            tma_load_2d(v_smem(pv.stage) + AT_TILE_BYTES / 2, &tm_vt, tile.vcol0 + j * 128 + 64, kh * HD, v_full(pv.stage));
+            pv.advance(AT_KV_STAGES);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------- MMA issuer
-        // S_0, then per block: O_j = P_j V_j as soon as P_j is written (the softmax threads are done
-        // with S_j by then), and straight after it S_{j+1}, so that the next scores are ready while
-        // the softmax threads still add O_j into their registers.
+        // S_{j+1} goes to the tensor pipe before the wait for P_j, so that it is there when the softmax
+        // threads come back; O += P_j V_j follows as soon as P_j is written.
         const uint32_t idesc = idesc_bf16(128, 128);
-        auto scores = [&](int stage) {       // S = Q K^T over the 128 head dimensions: two 64-wide halves, four K=16 steps each
+        PipeState pk, pv;
+        auto scores = [&](int j) {       // S = Q K^T over the 128 head dimensions: two 64-wide halves, four K=16 steps each
+            if (!mbar_wait(k_full(pk.stage), pk.phase, abort_flag, status)) return false;
+            tc_fence_after();
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 const uint64_t da = smem_desc_sw128(q_smem + half * (AT_TILE_BYTES / 2));
-                const uint64_t db = smem_desc_sw128(k_smem(stage) + half * (AT_TILE_BYTES / 2));
+                const uint64_t db = smem_desc_sw128(k_smem(pk.stage) + half * (AT_TILE_BYTES / 2));
 #pragma unroll
-                for (int k = 0; k < 4; k++) umma_bf16(tmem_s, da + 2u * k, db + 2u * k, idesc, (half | k) ? 1u : 0u);
+                for (int k = 0; k < AT_DBG_KSTEPS; k++) umma_bf16(tmem_base + (j & 1) * 128, da + 2u * k, db + 2u * k, idesc, (half | k) ? 1u : 0u);
             }
-            umma_commit(s_full);
+            umma_commit(k_empty(pk.stage));
+            umma_commit(s_full(j & 1));
+            pk.advance(AT_KV_STAGES);
+            return true;
         };
-        PipeState p, nx;
-        bool ok = mbar_wait(q_full, 0, abort_flag, status) && mbar_wait(kv_full(0), 0, abort_flag, status);
-        if (ok) { tc_fence_after(); scores(0); nx.advance(AT_KV_STAGES); }
+        bool ok = mbar_wait(q_full, 0, abort_flag, status) && scores(0);
         for (int j = 0; j < n_blocks && ok; j++) {
-            ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, status);
+            // the score buffer of block j+1 held block j-1, which the softmax threads left before they wrote P_{j-1}
+            if (j + 1 < n_blocks) ok = scores(j + 1);
+            ok = ok && mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, status) && mbar_wait(v_full(pv.stage), pv.phase, abort_flag, status);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 const uint64_t da = smem_desc_sw128(p_smem + half * (AT_TILE_BYTES / 2));
-                const uint64_t db = smem_desc_sw128(v_smem(p.stage) + half * (AT_TILE_BYTES / 2));
+                const uint64_t db = smem_desc_sw128(v_smem(pv.stage) + half * (AT_TILE_BYTES / 2));
 #pragma unroll
-                for (int k = 0; k < 4; k++) umma_bf16(tmem_o, da + 2u * k, db + 2u * k, idesc, (half | k) ? 1u : 0u);
+                for (int k = 0; k < AT_DBG_KSTEPS; k++) umma_bf16(tmem_o, da + 2u * k, db + 2u * k, idesc, (j | half | k) ? 1u : 0u);
             }
-            umma_commit(kv_empty(p.stage));                // K and Vt of this block are free once both products are done
-            umma_commit(o_full);
-            p.advance(AT_KV_STAGES);
-            if (j + 1 < n_blocks) {
-                ok = mbar_wait(kv_full(nx.stage), nx.phase, abort_flag, status);
-                if (!ok) break;
-                tc_fence_after();
-                scores(nx.stage);
-                nx.advance(AT_KV_STAGES);
-            }
+            umma_commit(v_empty(pv.stage));
+            umma_commit(pv_done);
+            pv.advance(AT_KV_STAGES);
         }
     } else if (warp >= 4) {
-        // ---------------------------------------------------------- softmax + accumulation: two threads per query row
-        // Thread (row r, half hf) owns keys hf*64.. of every score block and head dimensions hf*64.. of
-        // the output.  The two threads of a row sit in different warps and exchange their partial
-        // row maxima through shared memory at a named barrier; a thread whose wait ran out marks
-        // `quit` and still joins that barrier, after which all of them leave together.
+        // ---------------------------------------------------------- softmax: two threads per query row
+        // Thread (row r, half hf) owns keys hf*64.. of every score block and, at the end, head
+        // dimensions hf*64.. of the output.  The two threads of a row sit in different warps and
+        // exchange their partial row maxima through shared memory at a named barrier; a thread whose
+        // wait ran out marks `quit` and still joins that barrier, after which all of them leave.
         const int q4 = warp & 3, hf = (warp - 4) >> 2;
         const int r = q4 * 32 + lane;                                             // row inside the tile = TMEM lane
-        const int qg = tile.q0 + r;                                               // global token index of the row
         const uint32_t lane_addr = ((uint32_t)(q4 * 32) << 16) + hf * 64;
-        float acc[64];
-#pragma unroll
-        for (int d = 0; d < 64; d++) acc[d] = 0.f;
-        float m = -CUDART_INF_F, l = 0.f;
+        const float c = scale * 1.4426950408889634f;                              // scores to log2 units
+        float m = 0.f, l = 0.f;
         bool alive = true;
+#ifdef AT_DBG_CLOCK
+        long long tk[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
+#endif
         for (int j = 0; j < n_blocks; j++) {
-            if (alive) alive = mbar_wait(s_full, (uint32_t)j & 1u, abort_flag, status);
-            const int key0 = tile.rec_start + j * 128 + hf * 64;
-            float sc[64], pmax = -CUDART_INF_F;
+            const int b = j & 1;
+            AT_TICK(0)
+            if (alive) alive = mbar_wait(s_full(b), (uint32_t)(j >> 1) & 1u, abort_flag, status);
+            alive = __all_sync(0xffffffffu, alive);
+            AT_TICK(1)
+            uint32_t sa[32], sb[32];                                              // this thread's 64 scores of the block
+            float pmax = -CUDART_INF_F;
             if (alive) {
                 tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t t32[32];
-                    tmem_ld32(tmem_s + lane_addr + c * 32, t32);
-                    tmem_ld_wait();
+                tmem_ld32(tmem_base + b * 128 + lane_addr, sa);
+                tmem_ld32(tmem_base + b * 128 + lane_addr + 32, sb);
+                tmem_ld_wait();
+                AT_TICK(2)
+                if (j == n_blocks - 1) {                                          // the only block with keys after some of the rows
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
-                        sc[c * 32 + i] = key0 + c * 32 + i <= qg ? __uint_as_float(t32[i]) * scale : -CUDART_INF_F;
-                        pmax = fmaxf(pmax, sc[c * 32 + i]);
+                        if (hf * 64 + i > r) sa[i] = 0xff800000u;
+                        if (hf * 64 + 32 + i > r) sb[i] = 0xff800000u;
                     }
                 }
-                xch[hf * 128 + r] = pmax;
+                float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx[0] = max3(mx[0], __uint_as_float(sa[i]), __uint_as_float(sa[i + 1]));
+                    mx[1] = max3(mx[1], __uint_as_float(sa[i + 2]), __uint_as_float(sa[i + 3]));
+                    mx[2] = max3(mx[2], __uint_as_float(sb[i]), __uint_as_float(sb[i + 1]));
+                    mx[3] = max3(mx[3], __uint_as_float(sb[i + 2]), __uint_as_float(sb[i + 3]));
+                }
+                pmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                xch[(b * 2 + hf) * 128 + r] = pmax;
             } else {
                 *quit = 1;
             }
+            AT_TICK(3)
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (*quit) break;
+            AT_TICK(4)
             // every block holds at least one key the row may see (tiles and blocks are both cut from
-            // the record's start in steps of 128), so the row maximum is finite
-            const float mx = fmaxf(m, fmaxf(pmax, xch[(hf ^ 1) * 128 + r]));
-            const float corr = __expf(m - mx);
-            float sum = 0.f;
-            // P = exp(s - mx) as BF16 into the swizzled K-major layout: this thread's 64 keys are one
-            // 128-byte row of its half tile, chunk c8 of 8 keys at c8 ^ (r & 7)
+            // the record's start in steps of 128), so the block maximum is finite
+            const float bm = fmaxf(pmax, xch[(b * 2 + (hf ^ 1)) * 128 + r]) * c;
+            float corr = 1.f;
+            if (j == 0) m = bm;
+            else if (bm > m + AT_LAZY) { corr = ex2_approx(m - bm); m = bm; l *= corr; }
+            const bool rescale = __any_sync(0xffffffffu, corr != 1.f);
+            // P = exp2(c s - m) as BF16 (values up to 2^8 while m lags the running maximum)
+            uint32_t pk[32];
+            float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m, -m);
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const uint32_t *src = i < 16 ? sa : sb;
+                const float2 x = ffma2(make_float2(__uint_as_float(src[(2 * i) & 31]), __uint_as_float(src[(2 * i + 1) & 31])), c2, nm2);
+#ifdef AT_DBG_NOEXP
+                const float2 pp = make_float2(fminf(fmaxf(x.x, -1.f), 1.f) * 1e-3f + 2e-3f, fminf(fmaxf(x.y, -1.f), 1.f) * 1e-3f + 2e-3f);
+#else
+                const float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+#endif
+                acc[i & 1] = fadd2(acc[i & 1], pp);
+                const __nv_bfloat162 bb = __floats2bfloat162_rn(pp.x, pp.y);
+                pk[i] = *reinterpret_cast<const uint32_t *>(&bb);
+            }
+            const float sum = (acc[0].x + acc[1].x) + (acc[0].y + acc[1].y);
+            l += sum;
+            AT_TICK(5)
+            // the P tile and the accumulator are free once the previous value product is done
+            if (j > 0) alive = mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_flag, status);
+            alive = __all_sync(0xffffffffu, alive);
+            AT_TICK(6)
+            if (!alive) continue;
+            if (rescale) {
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {                  // this warp's 32 rows, all 128 columns in two passes of two threads' halves
+                    if ((cc >> 1) != hf) continue;                // each half of the row pair rescales its own 64 columns
+                    uint32_t t32[32];
+                    tmem_ld32(tmem_o + ((uint32_t)(q4 * 32) << 16) + cc * 32, t32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) t32[i] = __float_as_uint(__uint_as_float(t32[i]) * corr);
+                    tmem_st32(tmem_o + ((uint32_t)(q4 * 32) << 16) + cc * 32, t32);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+            }
+            // swizzled K-major layout: this thread's 64 keys are one 128-byte row of its half tile,
+            // chunk c8 of 8 keys at c8 ^ (r & 7)
             uint8_t *prow = smem_gen + AT_TILE_BYTES + hf * (AT_TILE_BYTES / 2) + r * 128;
 #pragma unroll
-            for (int c8 = 0; c8 < 8; c8++) {
-                uint32_t w[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const __nv_bfloat162 b = __floats2bfloat162_rn(__expf(sc[c8 * 8 + 2 * i] - mx), __expf(sc[c8 * 8 + 2 * i + 1] - mx));
-                    // the sum uses the rounded probabilities the second product multiplies with
-                    sum += __bfloat162float(b.x) + __bfloat162float(b.y);
-                    w[i] = *reinterpret_cast<const uint32_t *>(&b);
-                }
-                *reinterpret_cast<uint4 *>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            l = l * corr + sum;
-            m = mx;
+            for (int c8 = 0; c8 < 8; c8++)
+                *reinterpret_cast<uint4 *>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[c8 * 4], pk[c8 * 4 + 1], pk[c8 * 4 + 2], pk[c8 * 4 + 3]);
             tc_fence_before();
             fence_proxy_async_smem();
             mbar_arrive(p_full);
-            alive = mbar_wait(o_full, (uint32_t)j & 1u, abort_flag, status);
-            if (alive) {
-                tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t t32[32];
-                    tmem_ld32(tmem_o + lane_addr + c * 32, t32);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) acc[c * 32 + i] = acc[c * 32 + i] * corr + __uint_as_float(t32[i]);
-                }
-                tc_fence_before();
-            }
+            AT_TICK(7)
         }
-        // the row's denominator is the sum of what its two threads added up (same maximum in both)
+#ifdef AT_DBG_CLOCK
+        if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && threadIdx.x == 128) {
+            for (int k = 0; k < 8; k++) at_dbg[k] = (unsigned long long)tk[k];
+            at_dbg[8] = (unsigned long long)n_blocks;
+        }
+#endif
+        // the row's denominator is the sum of what its two threads added up (same reference maximum in both)
+        if (alive) alive = mbar_wait(pv_done, (uint32_t)(n_blocks - 1) & 1u, abort_flag, status);
         if (!alive) *quit = 1;
-        xch[hf * 128 + r] = l;
+        xch[((n_blocks & 1) * 2 + hf) * 128 + r] = l;
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (!*quit && r < tile.q_len) {
-            const float lt = l + xch[(hf ^ 1) * 128 + r];
+        if (!*quit) {
+            tc_fence_after();
+            const float lt = l + xch[((n_blocks & 1) * 2 + (hf ^ 1)) * 128 + r];
             const float inv = lt > 0.f ? 1.f / lt : 0.f;
+            const int qg = tile.q0 + r;                                           // global token index of the row
             uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + h * HD + hf * 64);
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                uint32_t w[4];
+            for (int cc = 0; cc < 2; cc++) {
+                uint32_t t32[32];
+                tmem_ld32(tmem_o + lane_addr + cc * 32, t32);
+                tmem_ld_wait();
+                if (r < tile.q_len) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const __nv_bfloat162 b = __floats2bfloat162_rn(acc[ch * 8 + 2 * i] * inv, acc[ch * 8 + 2 * i + 1] * inv);
-                    w[i] = *reinterpret_cast<const uint32_t *>(&b);
+                    for (int ch = 0; ch < 4; ch++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const __nv_bfloat162 bb = __floats2bfloat162_rn(__uint_as_float(t32[ch * 8 + 2 * i]) * inv,
+                                                                            __uint_as_float(t32[ch * 8 + 2 * i + 1]) * inv);
+                            w[i] = *reinterpret_cast<const uint32_t *>(&bb);
+                        }
+                        dst[cc * 4 + ch] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
-                dst[ch] = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
@@ -341,21 +465,25 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
         // a wait ran out: give loads already in flight a bounded chance to land
-        for (int s = 0; s < 3; s++) {
+        for (int s = 0; s < 5; s++) {
             const int par = armed[s];
             if (par < 0) continue;
-            const uint32_t bar = s == 0 ? q_full : kv_full(s - 1);
+            const uint32_t bar = s == 0 ? q_full : s < 3 ? k_full(s - 1) : v_full(s - 3);
             const uint64_t t0 = globaltimer_ns();
             while (!mbar_try_wait(bar, (uint32_t)par) && globaltimer_ns() - t0 < 50000000ull) {}
         }
     }
     __syncthreads();
-    if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+    if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, AT_TMEM_COLS); }
 }
 
 }  // namespace
 
 extern "C" {
+
+#ifdef AT_DBG_CLOCK
+cudaError_t omni_attn_debug_read(unsigned long long *dst) { return cudaMemcpyFromSymbol(dst, at_dbg, sizeof(at_dbg)); }
+#endif
 
 cudaError_t omni_attn_configure(void) {
     return cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
