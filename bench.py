@@ -45,7 +45,7 @@ GATEUP_FLOP_PER_TOKEN = 2 * H * (2 * F) * TOP          # 50,331,648
 EXPERT_FLOP_PER_TOKEN = GATEUP_FLOP_PER_TOKEN + 2 * F * H * TOP   # 75,497,472
 WEIGHT_BYTES = (E * H + E * 2 * F * H + E * H * F) * 2
 KERNELS_PER_PASS = 7     # router (counts the sort segments), exact pass, scan, scatter, gate/up (gathers its rows), down, combine
-KERNELS_PER_PASS_EP = 9  # ... plus plan and one barrier; the expert kernels dispatch and return the rows themselves
+KERNELS_PER_PASS_EP = 10  # ... plus owner buckets, plan and one barrier; the expert kernels dispatch and return the rows themselves
 METRIC = "MoE-layer prefill tokens/sec at T=4096"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at T=4096, from the ncu
 # capture summarised in profiles/ncu_full_moe_layer_T4096.md

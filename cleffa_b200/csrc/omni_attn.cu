@@ -16,6 +16,7 @@
 // products read K-major operands; each record's columns start at a multiple of 64 tokens
 // (`vcol`), which keeps every TMA box 16-byte aligned.  Every wait is bounded.
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
@@ -125,32 +126,30 @@ __global__ void __launch_bounds__(256) v_transpose_kernel(const __nv_bfloat16 *_
 }
 
 // ------------------------------------------------------------------ attention
-// One CTA per (query head, tile of <= 128 query rows of one record).  Key blocks of 128 run from the
-// record's start to the tile's diagonal.  Per block j:
-//   S_j = Q K_j^T        tcgen05, FP32 in TMEM, two score buffers so that S_{j+1} is formed while
-//                        the softmax threads work on S_j
-//   P_j = exp2(c S_j - m)  256 threads, two per query row (64 keys each), BF16 into a swizzled
-//                        shared-memory tile
-//   O  += P_j V_j        tcgen05, accumulated in TMEM over all blocks
+// One CTA per (pair of query heads that share a key/value head, tile of <= 128 query rows of one
+// record).  Key blocks of 128 run from the record's start to the tile's diagonal.  For each head x
+// of the pair and block j:
+//   S_x(j) = Q_x K_j^T       tcgen05, FP32 in TMEM
+//   P_x(j) = exp2(c S - m)   128 threads, one per query row; BF16, written back over the first
+//                            64 columns of S_x in TMEM (two keys per column)
+//   O_x   += P_x(j) V_j      tcgen05 with the A operand read from TMEM, accumulated over all blocks
+// The two heads run half a block apart: while one head's threads are in their exponentials the
+// tensor pipe forms the other head's value product and next scores, so neither waits for long.
 // m is the row's reference maximum.  It follows the running maximum lazily: only when a block's
 // maximum exceeds it by more than 2^8 are O and the running sum rescaled (by the softmax threads,
-// in TMEM, between two value products); otherwise P simply holds values up to 256.  The result is
-// the same softmax; the accumulator never leaves TMEM until the tile is done.
+// in TMEM: the scores of a block being there means the previous value product is done);
+// otherwise P simply holds values up to 256.  The accumulators never leave TMEM until the end.
 struct AttnTile { int32_t rec_start, q0, q_len, vcol0; };          // vcol0: Vt column of the record's first token
 
-constexpr int AT_THREADS = 384;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..11 softmax (two threads per query row)
+constexpr int AT_THREADS = 384;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..7 softmax of head 0, 8..11 of head 1
 constexpr int AT_TILE_BYTES = 128 * 128 * 2;                       // 32 KiB: 128 rows x 128 BF16 as two 64-column halves
 constexpr int AT_KV_STAGES = 2;
-constexpr int AT_TMEM_COLS = 512;                                  // S0, S1, O of 128 columns each
-constexpr int AT_N_BARS = 14;
-constexpr int AT_XCH_BYTES = 2 * 2 * 128 * 4;                      // [block parity][row half][row]
-constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + AT_N_BARS * 8 + 16 + 64 + AT_XCH_BYTES;
-#ifndef AT_DBG_KSTEPS
-#define AT_DBG_KSTEPS 4
-#endif
+constexpr int AT_TMEM_COLS = 512;                                  // S_0, S_1, O_0, O_1 of 128 columns each
+constexpr int AT_N_BARS = 16;
+constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + AT_N_BARS * 8 + 64;
 constexpr float AT_LAZY = 8.f;                                     // log2 of how far a block may exceed the reference maximum
 
-__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t *r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -160,6 +159,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]
         "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
         "r"(r[31])
         : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] . B[smem]^T: A's rows are TMEM lanes, two BF16 of the K extent per column.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ float ex2_approx(float x) {          // 2^x, -inf -> 0; relative error ~2^-22, far below BF16's
     float y;
@@ -183,14 +191,7 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)));
     return *reinterpret_cast<float2 *>(&d);
 }
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-#ifdef AT_DBG_CLOCK
-__device__ unsigned long long at_dbg[16];
-#define AT_TICK(k) { const long long now_ = clock64(); tk[k] += now_ - tprev; tprev = now_; }
-#else
-#define AT_TICK(k)
-#endif
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_vt, const AttnTile *__restrict__ tiles, int T, float scale,
@@ -198,40 +199,37 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t q_smem = smem_base, p_smem = smem_base + AT_TILE_BYTES;
+    auto q_smem = [&](int x) { return smem_base + AT_TILE_BYTES * x; };
     auto k_smem = [&](int s) { return smem_base + AT_TILE_BYTES * (2 + s); };
     auto v_smem = [&](int s) { return smem_base + AT_TILE_BYTES * (2 + AT_KV_STAGES + s); };
     const uint32_t bar_base = smem_base + AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES);
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, pv_done
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done[2]
     const uint32_t q_full = bar_base;
     auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
     auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
-    auto s_full = [&](int b) { return bar_base + 8u * (9 + b); };
-    const uint32_t p_full = bar_base + 8u * 11, pv_done = bar_base + 8u * 12;
+    auto s_full = [&](int x) { return bar_base + 8u * (9 + x); };
+    auto p_full = [&](int x) { return bar_base + 8u * (11 + x); };
+    auto o_done = [&](int x) { return bar_base + 8u * (13 + x); };
     uint8_t *misc = smem_gen + AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + AT_N_BARS * 8;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
-    volatile int *quit = reinterpret_cast<volatile int *>(misc + 8);           // a softmax thread's wait ran out: all of them leave together
     volatile int *armed = reinterpret_cast<volatile int *>(misc + 16);         // [5]: q, k stages, v stages (parity of the load in flight, -1 none)
-    float *xch = reinterpret_cast<float *>(misc + 16 + 64);                    // what the two threads of a row tell each other
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const AttnTile tile = tiles[blockIdx.x];
-    const int h = blockIdx.y, kh = h / (NH / NKV);
+    const AttnTile tile = tiles[gridDim.x - 1 - blockIdx.x];                    // a record's longest tiles first
+    const int h0 = 2 * blockIdx.y, kh = h0 / (NH / NKV);
     const int q_last = tile.q0 + tile.q_len - 1;                                // last query row of the tile
     const int n_blocks = (q_last - tile.rec_start) / 128 + 1;                   // key blocks from the record's start to the diagonal
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < AT_KV_STAGES; s++) {
+        for (int s = 0; s < 2; s++) {
             mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
-            mbar_init(s_full(s), 1);
+            mbar_init(s_full(s), 1); mbar_init(p_full(s), 128); mbar_init(o_done(s), 1);
         }
-        mbar_init(p_full, 256); mbar_init(pv_done, 1);
         *abort_flag = 0;
-        *quit = 0;
         for (int i = 0; i < 5; i++) armed[i] = -1;
         fence_mbar_init();
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_vt);
@@ -243,14 +241,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256;
 
     if (warp == 0 && lane == 0) {
-        // ---------------------------------------------------------- loads: Q once, then K one block ahead of Vt
+        // ---------------------------------------------------------- loads: both Q tiles once, then K one block ahead of Vt
         armed[0] = 0;
-        mbar_expect_tx(q_full, AT_TILE_BYTES);
-        tma_load_2d(q_smem, &tm_q, 0, h * T + tile.q0, q_full);                        // d 0..63
-        tma_load_2d(q_smem + AT_TILE_BYTES / 2, &tm_q, 64, h * T + tile.q0, q_full);   // d 64..127
+        mbar_expect_tx(q_full, 2 * AT_TILE_BYTES);
+        for (int x = 0; x < 2; x++) {
+            tma_load_2d(q_smem(x), &tm_q, 0, (h0 + x) * T + tile.q0, q_full);                        // d 0..63
+            tma_load_2d(q_smem(x) + AT_TILE_BYTES / 2, &tm_q, 64, (h0 + x) * T + tile.q0, q_full);   // d 64..127
+        }
         PipeState pk, pv;
         auto load_k = [&](int j) {
             if (!mbar_wait(k_empty(pk.stage), pk.phase ^ 1u, abort_flag, status)) return false;
@@ -274,175 +273,151 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------- MMA issuer
-        // S_{j+1} goes to the tensor pipe before the wait for P_j, so that it is there when the softmax
-        // threads come back; O += P_j V_j follows as soon as P_j is written.
+        // Per head and block: the value product as soon as P is written, and behind it the head's next
+        // scores into the same TMEM columns (the tensor pipe runs them in the order issued, so the
+        // product has read P before the scores overwrite it).
         const uint32_t idesc = idesc_bf16(128, 128);
-        PipeState pk, pv;
-        auto scores = [&](int j) {       // S = Q K^T over the 128 head dimensions: two 64-wide halves, four K=16 steps each
-            if (!mbar_wait(k_full(pk.stage), pk.phase, abort_flag, status)) return false;
-            tc_fence_after();
+        auto scores = [&](int x, int stage) {     // S_x = Q_x K^T over the 128 head dimensions: two 64-wide halves, four K=16 steps each
 #pragma unroll
             for (int half = 0; half < 2; half++) {
-                const uint64_t da = smem_desc_sw128(q_smem + half * (AT_TILE_BYTES / 2));
-                const uint64_t db = smem_desc_sw128(k_smem(pk.stage) + half * (AT_TILE_BYTES / 2));
+                const uint64_t da = smem_desc_sw128(q_smem(x) + half * (AT_TILE_BYTES / 2));
+                const uint64_t db = smem_desc_sw128(k_smem(stage) + half * (AT_TILE_BYTES / 2));
 #pragma unroll
-                for (int k = 0; k < AT_DBG_KSTEPS; k++) umma_bf16(tmem_base + (j & 1) * 128, da + 2u * k, db + 2u * k, idesc, (half | k) ? 1u : 0u);
+                for (int k = 0; k < 4; k++) umma_bf16(tmem_base + x * 128, da + 2u * k, db + 2u * k, idesc, (half | k) ? 1u : 0u);
             }
-            umma_commit(k_empty(pk.stage));
-            umma_commit(s_full(j & 1));
-            pk.advance(AT_KV_STAGES);
-            return true;
+            umma_commit(s_full(x));
         };
-        bool ok = mbar_wait(q_full, 0, abort_flag, status) && scores(0);
-        for (int j = 0; j < n_blocks && ok; j++) {
-            // the score buffer of block j+1 held block j-1, which the softmax threads left before they wrote P_{j-1}
-            if (j + 1 < n_blocks) ok = scores(j + 1);
-            ok = ok && mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, status) && mbar_wait(v_full(pv.stage), pv.phase, abort_flag, status);
-            if (!ok) break;
+        PipeState pk, pv;
+        bool ok = mbar_wait(q_full, 0, abort_flag, status) && mbar_wait(k_full(0), 0, abort_flag, status);
+        if (ok) {
             tc_fence_after();
+            scores(0, 0); scores(1, 0);
+            umma_commit(k_empty(0));
+            pk.advance(AT_KV_STAGES);
+        }
+        for (int j = 0; j < n_blocks && ok; j++) {
+            for (int x = 0; x < 2 && ok; x++) {
+                ok = mbar_wait(p_full(x), (uint32_t)j & 1u, abort_flag, status);
+                if (ok && x == 0) ok = mbar_wait(v_full(pv.stage), pv.phase, abort_flag, status);
+                if (!ok) break;
+                tc_fence_after();
+                // O_x += P_x V: the 128 keys of the block are eight K=16 steps, 8 TMEM columns of P each
 #pragma unroll
-            for (int half = 0; half < 2; half++) {
-                const uint64_t da = smem_desc_sw128(p_smem + half * (AT_TILE_BYTES / 2));
-                const uint64_t db = smem_desc_sw128(v_smem(pv.stage) + half * (AT_TILE_BYTES / 2));
-#pragma unroll
-                for (int k = 0; k < AT_DBG_KSTEPS; k++) umma_bf16(tmem_o, da + 2u * k, db + 2u * k, idesc, (j | half | k) ? 1u : 0u);
+                for (int k = 0; k < 8; k++) {
+                    const uint64_t db = smem_desc_sw128(v_smem(pv.stage) + (k >> 2) * (AT_TILE_BYTES / 2));
+                    umma_bf16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + 8 * k, db + 2u * (k & 3), idesc, (j | k) ? 1u : 0u);
+                }
+                if (x == 1) umma_commit(v_empty(pv.stage));
+                if (j + 1 < n_blocks) {
+                    if (x == 0) { ok = mbar_wait(k_full(pk.stage), pk.phase, abort_flag, status); if (!ok) break; tc_fence_after(); }
+                    scores(x, pk.stage);
+                    if (x == 1) umma_commit(k_empty(pk.stage));
+                } else {
+                    umma_commit(o_done(x));
+                }
             }
-            umma_commit(v_empty(pv.stage));
-            umma_commit(pv_done);
             pv.advance(AT_KV_STAGES);
+            pk.advance(AT_KV_STAGES);
         }
     } else if (warp >= 4) {
-        // ---------------------------------------------------------- softmax: two threads per query row
-        // Thread (row r, half hf) owns keys hf*64.. of every score block and, at the end, head
-        // dimensions hf*64.. of the output.  The two threads of a row sit in different warps and
-        // exchange their partial row maxima through shared memory at a named barrier; a thread whose
-        // wait ran out marks `quit` and still joins that barrier, after which all of them leave.
-        const int q4 = warp & 3, hf = (warp - 4) >> 2;
+        // ---------------------------------------------------------- softmax of one head: one thread per query row
+        const int x = (warp - 4) >> 2, q4 = warp & 3;
         const int r = q4 * 32 + lane;                                             // row inside the tile = TMEM lane
-        const uint32_t lane_addr = ((uint32_t)(q4 * 32) << 16) + hf * 64;
+        const uint32_t tmem_s = tmem_base + x * 128 + ((uint32_t)(q4 * 32) << 16);
+        const uint32_t tmem_o = tmem_base + 256 + x * 128 + ((uint32_t)(q4 * 32) << 16);
         const float c = scale * 1.4426950408889634f;                              // scores to log2 units
         float m = 0.f, l = 0.f;
         bool alive = true;
-#ifdef AT_DBG_CLOCK
-        long long tk[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-#endif
         for (int j = 0; j < n_blocks; j++) {
-            const int b = j & 1;
-            AT_TICK(0)
-            if (alive) alive = mbar_wait(s_full(b), (uint32_t)(j >> 1) & 1u, abort_flag, status);
-            alive = __all_sync(0xffffffffu, alive);
-            AT_TICK(1)
-            uint32_t sa[32], sb[32];                                              // this thread's 64 scores of the block
-            float pmax = -CUDART_INF_F;
-            if (alive) {
-                tc_fence_after();
-                tmem_ld32(tmem_base + b * 128 + lane_addr, sa);
-                tmem_ld32(tmem_base + b * 128 + lane_addr + 32, sb);
-                tmem_ld_wait();
-                AT_TICK(2)
-                if (j == n_blocks - 1) {                                          // the only block with keys after some of the rows
+            alive = __all_sync(0xffffffffu, mbar_wait(s_full(x), (uint32_t)j & 1u, abort_flag, status));
+            if (!alive) break;
+            tc_fence_after();
+            // Two sweeps over the row's 128 scores, 32 at a time with the next 32 in flight: the maximum
+            // first, then the probabilities (reading TMEM twice costs less than holding 128 registers).
+            const bool diagonal = j == n_blocks - 1;                              // the only block with keys after some of the rows
+            uint32_t ta[32], tb[32];
+            float mx[4];
+            tmem_ld32(tmem_s, ta);
+            tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        if (hf * 64 + i > r) sa[i] = 0xff800000u;
-                        if (hf * 64 + 32 + i > r) sb[i] = 0xff800000u;
-                    }
-                }
-                float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            for (int q = 0; q < 4; q++) {
+                uint32_t *cur = (q & 1) ? tb : ta, *nxt = (q & 1) ? ta : tb;
+                if (q < 3) tmem_ld32(tmem_s + (q + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(nxt));
+                if (diagonal) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mx[0] = max3(mx[0], __uint_as_float(sa[i]), __uint_as_float(sa[i + 1]));
-                    mx[1] = max3(mx[1], __uint_as_float(sa[i + 2]), __uint_as_float(sa[i + 3]));
-                    mx[2] = max3(mx[2], __uint_as_float(sb[i]), __uint_as_float(sb[i + 1]));
-                    mx[3] = max3(mx[3], __uint_as_float(sb[i + 2]), __uint_as_float(sb[i + 3]));
+                    for (int i = 0; i < 32; i++)
+                        if (q * 32 + i > r) cur[i] = 0xff800000u;
                 }
-                pmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                xch[(b * 2 + hf) * 128 + r] = pmax;
-            } else {
-                *quit = 1;
+                mx[q] = fmaxf(__uint_as_float(cur[0]), __uint_as_float(cur[1]));
+#pragma unroll
+                for (int i = 2; i < 32; i += 2) mx[q] = max3(mx[q], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+                if (q < 3) tmem_ld_wait();
             }
-            AT_TICK(3)
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (*quit) break;
-            AT_TICK(4)
-            // every block holds at least one key the row may see (tiles and blocks are both cut from
-            // the record's start in steps of 128), so the block maximum is finite
-            const float bm = fmaxf(pmax, xch[(b * 2 + (hf ^ 1)) * 128 + r]) * c;
+            // key 0 of every block is visible to every row (tiles and blocks are both cut from the
+            // record's start in steps of 128), so the block maximum is finite
+            const float bm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;
             float corr = 1.f;
             if (j == 0) m = bm;
             else if (bm > m + AT_LAZY) { corr = ex2_approx(m - bm); m = bm; l *= corr; }
-            const bool rescale = __any_sync(0xffffffffu, corr != 1.f);
-            // P = exp2(c s - m) as BF16 (values up to 2^8 while m lags the running maximum)
-            uint32_t pk[32];
-            float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m, -m);
+            if (__any_sync(0xffffffffu, corr != 1.f)) {
+                // the scores of this block being complete means the previous value product is: O is at rest
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                const uint32_t *src = i < 16 ? sa : sb;
-                const float2 x = ffma2(make_float2(__uint_as_float(src[(2 * i) & 31]), __uint_as_float(src[(2 * i + 1) & 31])), c2, nm2);
-#ifdef AT_DBG_NOEXP
-                const float2 pp = make_float2(fminf(fmaxf(x.x, -1.f), 1.f) * 1e-3f + 2e-3f, fminf(fmaxf(x.y, -1.f), 1.f) * 1e-3f + 2e-3f);
-#else
-                const float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-#endif
-                acc[i & 1] = fadd2(acc[i & 1], pp);
-                const __nv_bfloat162 bb = __floats2bfloat162_rn(pp.x, pp.y);
-                pk[i] = *reinterpret_cast<const uint32_t *>(&bb);
-            }
-            const float sum = (acc[0].x + acc[1].x) + (acc[0].y + acc[1].y);
-            l += sum;
-            AT_TICK(5)
-            // the P tile and the accumulator are free once the previous value product is done
-            if (j > 0) alive = mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_flag, status);
-            alive = __all_sync(0xffffffffu, alive);
-            AT_TICK(6)
-            if (!alive) continue;
-            if (rescale) {
-                tc_fence_after();
-#pragma unroll
-                for (int cc = 0; cc < 4; cc++) {                  // this warp's 32 rows, all 128 columns in two passes of two threads' halves
-                    if ((cc >> 1) != hf) continue;                // each half of the row pair rescales its own 64 columns
+                for (int q = 0; q < 4; q++) {
                     uint32_t t32[32];
-                    tmem_ld32(tmem_o + ((uint32_t)(q4 * 32) << 16) + cc * 32, t32);
+                    tmem_ld32(tmem_o + q * 32, t32);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i++) t32[i] = __float_as_uint(__uint_as_float(t32[i]) * corr);
-                    tmem_st32(tmem_o + ((uint32_t)(q4 * 32) << 16) + cc * 32, t32);
+                    tmem_st32(tmem_o + q * 32, t32);
                 }
-                tmem_st_wait();
-                tc_fence_before();
             }
-            // swizzled K-major layout: this thread's 64 keys are one 128-byte row of its half tile,
-            // chunk c8 of 8 keys at c8 ^ (r & 7)
-            uint8_t *prow = smem_gen + AT_TILE_BYTES + hf * (AT_TILE_BYTES / 2) + r * 128;
+            // P = exp2(c s - m) as BF16 (values up to 2^8 while m lags the running maximum), two keys per column
+            uint32_t pk[64];
+            float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m, -m);
+            // second sweep (the diagonal block with its mask, the others without)
+            auto sweep = [&](auto diag) {
+                constexpr bool DIAG = decltype(diag)::value;
+                tmem_ld32(tmem_s, ta);
+                tmem_ld_wait();
 #pragma unroll
-            for (int c8 = 0; c8 < 8; c8++)
-                *reinterpret_cast<uint4 *>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[c8 * 4], pk[c8 * 4 + 1], pk[c8 * 4 + 2], pk[c8 * 4 + 3]);
+                for (int q = 0; q < 4; q++) {
+                    uint32_t *cur = (q & 1) ? tb : ta, *nxt = (q & 1) ? ta : tb;
+                    if (q < 3) tmem_ld32(tmem_s + (q + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(nxt));
+                    if (DIAG) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (q * 32 + i > r) cur[i] = 0xff800000u;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float2 e = ffma2(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])), c2, nm2);
+                        const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+                        acc[i & 1] = fadd2(acc[i & 1], pp);
+                        const __nv_bfloat162 bb = __floats2bfloat162_rn(pp.x, pp.y);
+                        pk[q * 16 + i] = *reinterpret_cast<const uint32_t *>(&bb);
+                    }
+                    if (q < 3) tmem_ld_wait();
+                }
+            };
+            if (diagonal) sweep(std::true_type{}); else sweep(std::false_type{});
+            l += (acc[0].x + acc[1].x) + (acc[0].y + acc[1].y);
+            tmem_st32(tmem_s, pk);
+            tmem_st32(tmem_s + 32, pk + 32);
+            tmem_st_wait();
             tc_fence_before();
-            fence_proxy_async_smem();
-            mbar_arrive(p_full);
-            AT_TICK(7)
+            mbar_arrive(p_full(x));
         }
-#ifdef AT_DBG_CLOCK
-        if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && threadIdx.x == 128) {
-            for (int k = 0; k < 8; k++) at_dbg[k] = (unsigned long long)tk[k];
-            at_dbg[8] = (unsigned long long)n_blocks;
-        }
-#endif
-        // the row's denominator is the sum of what its two threads added up (same reference maximum in both)
-        if (alive) alive = mbar_wait(pv_done, (uint32_t)(n_blocks - 1) & 1u, abort_flag, status);
-        if (!alive) *quit = 1;
-        xch[((n_blocks & 1) * 2 + hf) * 128 + r] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (!*quit) {
+        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(o_done(x), 0, abort_flag, status));
+        if (alive) {
             tc_fence_after();
-            const float lt = l + xch[((n_blocks & 1) * 2 + (hf ^ 1)) * 128 + r];
-            const float inv = lt > 0.f ? 1.f / lt : 0.f;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
             const int qg = tile.q0 + r;                                           // global token index of the row
-            uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + h * HD + hf * 64);
+            uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + (h0 + x) * HD);
 #pragma unroll
-            for (int cc = 0; cc < 2; cc++) {
+            for (int q = 0; q < 4; q++) {
                 uint32_t t32[32];
-                tmem_ld32(tmem_o + lane_addr + cc * 32, t32);
+                tmem_ld32(tmem_o + q * 32, t32);
                 tmem_ld_wait();
                 if (r < tile.q_len) {
 #pragma unroll
@@ -454,7 +429,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                                             __uint_as_float(t32[ch * 8 + 2 * i + 1]) * inv);
                             w[i] = *reinterpret_cast<const uint32_t *>(&bb);
                         }
-                        dst[cc * 4 + ch] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[q * 4 + ch] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
@@ -481,9 +456,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
 extern "C" {
 
-#ifdef AT_DBG_CLOCK
-cudaError_t omni_attn_debug_read(unsigned long long *dst) { return cudaMemcpyFromSymbol(dst, at_dbg, sizeof(at_dbg)); }
-#endif
 
 cudaError_t omni_attn_configure(void) {
     return cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
@@ -507,7 +479,7 @@ cudaError_t omni_launch_attn_prep(const void *qkv, const float *qw, const float 
 // tiles: [n_tiles] of {record start, first query row, rows (<= 128), Vt column of the record start}
 cudaError_t omni_launch_attention(const CUtensorMap *tm_q, const CUtensorMap *tm_k, const CUtensorMap *tm_vt, const void *tiles,
                                   int n_tiles, int T, void *out, uint32_t *status, cudaStream_t s) {
-    return omni_launch_chain(attention_kernel, dim3(n_tiles, OMNI_NH), dim3(AT_THREADS), AT_SMEM_BYTES, s, *tm_q, *tm_k, *tm_vt,
+    return omni_launch_chain(attention_kernel, dim3(n_tiles, OMNI_NH / 2), dim3(AT_THREADS), AT_SMEM_BYTES, s, *tm_q, *tm_k, *tm_vt,
                              (const AttnTile *)tiles, T, 1.0f / sqrtf((float)OMNI_HD), (__nv_bfloat16 *)out, status);
 }
 
