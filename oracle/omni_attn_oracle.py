@@ -89,6 +89,33 @@ def attention_half(x, positions, seq_bounds, attn_norm, w_qkv, q_norm, k_norm, w
     return dict(out=out, xn=xn, q=q, k=k, v=v, attn=values)
 
 
+def attention_half_rows(x, positions, rows, attn_norm, w_qkv, q_norm, k_norm, w_out, n_head, n_kv, head_dim=128,
+                        theta=THETA, sections=SECTIONS, eps=EPS):
+    """The rows `rows` (sorted indices) of attention_half's `out` for ONE record x [T][H], computed
+    without the full T x T products: keys and values for every token, queries and the output
+    projection for the chosen rows only.  Same arithmetic as attention_half, row by row."""
+    x = x.to(torch.float64)
+    T = x.shape[0]
+    rows = np.asarray(rows)
+    w_qkv, w_out = w_qkv.to(torch.float64), w_out.to(torch.float64)
+    xn = rms(x, attn_norm.to(torch.float64), eps)
+    nq, nk = n_head * head_dim, n_kv * head_dim
+    kv = xn @ w_qkv[nq:].T
+    k = rms(kv[:, :nk].reshape(T, n_kv, head_dim), k_norm.to(torch.float64), eps).transpose(0, 1)
+    v = kv[:, nk:].reshape(T, n_kv, head_dim).transpose(0, 1)
+    q = rms((xn[rows] @ w_qkv[:nq].T).reshape(len(rows), n_head, head_dim), q_norm.to(torch.float64), eps).transpose(0, 1)
+    cos, sin = rotary(positions, head_dim, theta, sections)
+    k = rotate(k, cos, sin)
+    q = rotate(q, cos[rows], sin[rows])
+    group = n_head // n_kv
+    values = torch.empty(len(rows), nq, dtype=torch.float64)
+    for i, r in enumerate(rows):
+        for h in range(n_head):
+            scores = (k[h // group, :r + 1] @ q[h, i]) * head_dim ** -0.5
+            values[i, h * head_dim:(h + 1) * head_dim] = scores.softmax(0) @ v[h // group, :r + 1]
+    return x[rows] + values @ w_out.T
+
+
 def make_attention_weights(seed, hidden=2048, n_head=32, n_kv=4, head_dim=128, std=0.02):
     """Random-init weights of the attention half in the converted layout: BF16 matrices N(0, std),
     FP32 norm weights around 1."""

@@ -60,6 +60,42 @@ def test_attention_half_matches_fp64_oracle(attn, bounds):
     assert torch.isfinite(got).all()
 
 
+def test_config2_T4096_eight_records(attn):
+    """The packed prefill of BASELINE configuration 2 (T=4096 as 8 records, seed 1), every row
+    against the FP64 oracle."""
+    from cleffa_b200 import workloads
+    b, w = attn
+    bounds = [int(v) for v in workloads.varlen_bounds(1, 4096)]
+    x = torch.randn(4096, 2048, generator=torch.Generator().manual_seed(41))
+    pos = ao.make_positions(41, bounds)
+    got = run(b, x, pos, bounds)
+    ref = ao.attention_half(x, pos, bounds, w["attn_norm"], w["w_qkv"], w["q_norm"], w["k_norm"], w["w_out"], 32, 4)
+    assert rel(bf16_rows(b, "attn_out", 4096, 4096), ref["attn"]) < GATE
+    assert rel(got - x, ref["out"] - x.double()) < GATE
+    for lo, hi in zip(bounds[:-1], bounds[1:]):                        # and record by record
+        assert rel(got[lo:hi] - x[lo:hi], ref["out"][lo:hi] - x[lo:hi].double()) < GATE
+
+
+def test_config3_T16384_one_record_sampled(attn):
+    """One record of 16,384 tokens (BASELINE configuration 3's batch): 128 key blocks per query
+    tile.  96 sampled rows -- the first and last rows, both sides of tile and block boundaries,
+    random ones -- against the FP64 oracle's rows."""
+    b, w = attn
+    T = 16384
+    x = torch.randn(T, 2048, generator=torch.Generator().manual_seed(42))
+    pos = ao.make_positions(42, [0, T])
+    got = run(b, x, pos, [0, T])
+    rng = np.random.default_rng(42)
+    rows = np.unique(np.concatenate([[0, 1, 127, 128, 129, 255, 256, 8191, 8192, T - 129, T - 128, T - 2, T - 1],
+                                     rng.integers(0, T, 83)]))
+    ref = ao.attention_half_rows(x, pos, rows, w["attn_norm"], w["w_qkv"], w["q_norm"], w["k_norm"], w["w_out"], 32, 4)
+    delta, want = got[rows] - x[rows], ref - x[rows].double()
+    assert rel(delta, want) < GATE
+    worst = max(rel(delta[i], want[i]) for i in range(len(rows)))
+    assert worst < 3 * GATE, worst
+    assert torch.isfinite(got).all()
+
+
 def test_records_do_not_depend_on_their_neighbours(attn):
     b, w = attn
     bounds = [0, 200, 333, 700]

@@ -207,3 +207,25 @@ def test_attention_oracle_reproduces_the_reference_fp64_functions():
     first = ao.attention_half(x[:20], g["positions"][:, :20], [0, 20], torch.from_numpy(g["attn_norm"]), w_qkv, torch.from_numpy(g["q_norm"]),
                               torch.from_numpy(g["k_norm"]), torch.from_numpy(g["w_o"]), nh, nkv, hd, float(g["theta"]), sections, float(g["eps"]))
     assert np.abs(both["out"][:20].numpy() - first["out"].numpy()).max() < 1e-13
+
+
+def test_attention_oracle_rows_agree_with_the_whole_record():
+    """attention_half_rows (what the T=16384 GPU test samples with) is attention_half restricted to
+    the chosen rows, on the golden problem's weights and on a longer seeded record."""
+    from pathlib import Path
+    from oracle import omni_attn_oracle as ao
+    g = np.load(Path(__file__).resolve().parent / "golden" / "attn_small.npz")
+    H, nh, nkv, hd, T, s0, s1, s2 = (int(v) for v in g["geometry"])
+    w_qkv = torch.from_numpy(np.concatenate([g["w_q"], g["w_k"], g["w_v"]]))
+    args = (torch.from_numpy(g["attn_norm"]), w_qkv, torch.from_numpy(g["q_norm"]), torch.from_numpy(g["k_norm"]), torch.from_numpy(g["w_o"]),
+            nh, nkv, hd, float(g["theta"]), (s0, s1, s2), float(g["eps"]))
+    rows = np.array([0, 1, T // 2, T - 1])
+    part = ao.attention_half_rows(torch.from_numpy(g["hidden"]), g["positions"], rows, *args)
+    assert np.abs(part.numpy() - g["out"][rows]).max() < 1e-12
+    w = ao.make_attention_weights(3)
+    x = torch.randn(200, 2048, generator=torch.Generator().manual_seed(3))
+    pos = ao.make_positions(3, [0, 200])
+    full = ao.attention_half(x, pos, [0, 200], w["attn_norm"], w["w_qkv"], w["q_norm"], w["k_norm"], w["w_out"], 32, 4)
+    rows = np.array([0, 127, 128, 199])
+    part = ao.attention_half_rows(x, pos, rows, w["attn_norm"], w["w_qkv"], w["q_norm"], w["k_norm"], w["w_out"], 32, 4)
+    assert (part - full["out"][rows]).abs().max() < 1e-12
