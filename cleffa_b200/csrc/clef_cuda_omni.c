@@ -1386,3 +1386,11 @@ bool clef_omni_encode_attention(clef_gpu *g, int layer, float *x, const int32_t 
     if (!ok) { set_err(err, errlen, "%s", g->fail_msg); return false; }
     return true;
 }
+
+/* clef_omni_encode_layer (clef_metal_omni.m:248-331): the attention half, then norm(ffn_norm) and
+ * the MoE section, both adding into the same residual stream. */
+bool clef_omni_encode_layer(clef_gpu *g, int layer, float *x, const int32_t *pos3, int T, int n_seq, const int32_t *seq_bounds,
+                            char *err, size_t errlen) {
+    if (!clef_omni_encode_attention(g, layer, x, pos3, T, n_seq, seq_bounds, err, errlen)) return false;
+    return clef_omni_encode_norm_moe(g, layer, x, T, n_seq, seq_bounds, err, errlen);
+}

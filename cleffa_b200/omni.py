@@ -38,7 +38,7 @@ EXPORTS = [
     "clef_omni_ep_export", "clef_omni_ep_connect", "clef_omni_ep_connect_local", "clef_omni_ep_disconnect",
     "clef_omni_assign_noalloc", "clef_omni_ep_sync",
     "clef_omni_bind_norm", "clef_omni_encode_norm_moe", "clef_omni_bind_gguf", "clef_omni_gguf_check",
-    "clef_omni_bind_attention", "clef_omni_encode_attention",
+    "clef_omni_bind_attention", "clef_omni_encode_attention", "clef_omni_encode_layer",
 ]
 NOALLOC_MAX_ROWS = 4096
 EP_HANDLES, EP_HANDLE_BYTES = 6, 64
@@ -84,6 +84,7 @@ def load_library(path: Path | None = None) -> C.CDLL:
         "clef_omni_bind_gguf": (C.c_bool, [vp, cc, ci, cc, cz]),
         "clef_omni_bind_attention": (C.c_bool, [vp, ci, vp, vp, vp, vp, vp, C.c_float, C.c_float, ci, cc, cz]),
         "clef_omni_encode_attention": (C.c_bool, [vp, ci, vp, vp, ci, ci, vp, cc, cz]),
+        "clef_omni_encode_layer": (C.c_bool, [vp, ci, vp, vp, ci, ci, vp, cc, cz]),
         "clef_omni_gguf_check": (C.c_bool, [cc, ci, ci, ci, ci, C.POINTER(C.c_float), cc, cz]),
     }
     for name, (res, args) in sig.items():
@@ -237,6 +238,19 @@ class OmniBackend:
         seq_bounds = np.ascontiguousarray(seq_bounds, dtype=np.int32)
         self._check(self.lib.clef_omni_encode_attention(self._g, layer, _ptr(x), _ptr(pos3), T, len(seq_bounds) - 1, _ptr(seq_bounds),
                                                         self._err, _ERRLEN))
+
+    def encode_layer(self, layer: int, x: torch.Tensor, pos3: torch.Tensor, seq_bounds=None):
+        """One decoder layer on x[T][2048] (float32, CUDA): attention half, then norm + MoE block."""
+        T = x.shape[0]
+        if x.dtype != torch.float32 or tuple(x.shape) != (T, H) or not x.is_cuda:
+            raise ValueError("x must be a CUDA float32 [T,2048] tensor")
+        if pos3.dtype != torch.int32 or tuple(pos3.shape) != (T, 3) or not pos3.is_cuda or not pos3.is_contiguous():
+            raise ValueError("pos3 must be a contiguous CUDA int32 [T,3] tensor")
+        if seq_bounds is None:
+            seq_bounds = np.array([0, T], dtype=np.int32)
+        seq_bounds = np.ascontiguousarray(seq_bounds, dtype=np.int32)
+        self._check(self.lib.clef_omni_encode_layer(self._g, layer, _ptr(x), _ptr(pos3), T, len(seq_bounds) - 1, _ptr(seq_bounds),
+                                                    self._err, _ERRLEN))
 
     def bind_gguf(self, path, n_layer: int):
         """Bind layers 0..n_layer-1 (experts, router, ffn_norm) from a converted checkpoint file."""

@@ -162,6 +162,12 @@ bool clef_omni_bind_attention(clef_gpu *g, int layer, const float *attn_norm, co
  * FP32 softmax and accumulation. */
 bool clef_omni_encode_attention(clef_gpu *g, int layer, float *x, const int32_t *pos3, int T, int n_seq,
                                 const int32_t *seq_bounds, char *err, size_t errlen);
+/* One decoder layer in one call, the drop-in for clef_omni_encode_layer (clef_metal_omni.m:248-331):
+ * clef_omni_encode_attention followed by clef_omni_encode_norm_moe on the same residual stream,
+ * with the same arguments, limits and error behaviour as those two (the layer needs its attention
+ * tensors, its ffn_norm and its expert tensors bound). */
+bool clef_omni_encode_layer(clef_gpu *g, int layer, float *x, const int32_t *pos3, int T, int n_seq, const int32_t *seq_bounds,
+                            char *err, size_t errlen);
 
 /* Binds layers 0..n_layer-1 from a converted checkpoint (GGUF v3 as tools/convert_omni.py:135-139
  * writes it): router, gate/up and down expert tensors and the ffn_norm weights, with the type,

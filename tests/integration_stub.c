@@ -32,10 +32,8 @@ bool cuda_backend_open(const clef_engine *e, char *err, size_t errlen) {
 bool cuda_backend_layers(const clef_engine *e, float *d_x, const int32_t *d_pos3, int T, int n_seq, const int32_t *seq_bounds,
                          char *err, size_t errlen) {
     clef_omni_begin(G);                                        /* once per pass (clef_metal.m:1150) */
-    for (int l = 0; l < e->cfg.n_layer; l++) {                 /* clef_omni_encode_layer, clef_metal_omni.m:248 */
-        if (!clef_omni_encode_attention(G, l, d_x, d_pos3, T, n_seq, seq_bounds, err, errlen)) return false;
-        if (!clef_omni_encode_norm_moe(G, l, d_x, T, n_seq, seq_bounds, err, errlen)) return false;
-    }
+    for (int l = 0; l < e->cfg.n_layer; l++)                   /* clef_metal_omni.m:248; or its two halves, */
+        if (!clef_omni_encode_layer(G, l, d_x, d_pos3, T, n_seq, seq_bounds, err, errlen)) return false;   /* clef_omni_encode_attention + clef_omni_encode_norm_moe */
     return clef_omni_complete(G, err, errlen);                 /* clef_metal.m:1597 */
 }
 

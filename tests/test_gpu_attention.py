@@ -154,3 +154,9 @@ def test_a_layer_is_attention_then_norm_and_moe(attn, weights0):
     ids = b.read("ids", T); wts = b.read("weights", T)
     moe = orc.experts(xn, ids.astype(np.int64), wts.astype(np.float64), weights0[1], weights0[2])
     assert rel(xd.cpu() - mid.cpu(), moe) < GATE
+    # the one-call form (clef_omni_encode_layer) is those two calls
+    one = x.clone().cuda()
+    b.begin()
+    b.encode_layer(2, one, pd, np.asarray(bounds, np.int32))
+    b.complete()
+    assert torch.equal(one, xd)
