@@ -156,7 +156,9 @@ bool clef_omni_bind_attention(clef_gpu *g, int layer, const float *attn_norm, co
 /* x (device FP32 [T][2048], the residual stream) += attention half of `layer`.  pos3: device int32
  * [T][3], each token's temporal, row and column rotary position (clef_record_positions; all three
  * equal to the index inside the record for text).  seq_bounds: host, n_seq + 1 ascending offsets
- * ending at T; a token attends to the earlier tokens of its own record.  T <= 16384 per call.
+ * ending at T; a token attends to the earlier tokens of its own record.  T <= 16384 per call, and
+ * the record lengths, each rounded up to a multiple of 64, must sum to at most 32768 (a batch of
+ * more than 256 records shorter than 64 tokens can exceed that and is refused with a message).
  * Asynchronous like clef_omni_encode_moe; nonfinite q/k/v set status bit 1 (value 2) as in the
  * reference (clef.metal:2120) and fail clef_omni_complete.  BF16 operands on the tensor cores,
  * FP32 softmax and accumulation. */

@@ -127,6 +127,13 @@ def test_invalid_attention_dispatch_is_refused(attn):
         b.encode_attention(3, x, pd)
     with pytest.raises(OmniError, match="sequence bounds"):
         b.encode_attention(0, x, pd, np.array([0, 9], np.int32))
+    # 600 one-token records: their value columns, 64 apart, do not fit one pass
+    x = torch.zeros(600, 2048, device="cuda"); pd = torch.zeros(600, 3, dtype=torch.int32, device="cuda")
+    with pytest.raises(OmniError, match="too many records"):
+        b.encode_attention(0, x, pd, np.arange(601, dtype=np.int32))
+    b.begin()
+    b.encode_attention(0, x, pd, np.arange(0, 601, 2, dtype=np.int32))     # 300 records of two tokens fit
+    b.complete()
 
 
 def test_a_layer_is_attention_then_norm_and_moe(attn, weights0):
