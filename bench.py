@@ -447,84 +447,160 @@ def ours(args):
 
 
 def attention_bench(args):
-    """The attention half in front of the block (and, with --layers N, whole decoder layers:
-    attention half + norm + MoE): one GPU, seeded random weights, text-like positions.  One JSON line
-    with the time per pass of the attention half alone and of the layer, and the attention half's
-    FLOP rate (projections 2 T (2048 x 5120 + 4096 x 2048), attention 4 x 128 x 32 x sum over records of L(L+1)/2)."""
+    """The attention half in front of the block and whole decoder layers (attention half + norm +
+    MoE; --layers N stacks them): seeded random weights, text-like positions.  One JSON line with the
+    time per pass of the attention half alone and of the layer, and the attention half's FLOP rate
+    (projections 2 T (2048 x 5120 + 4096 x 2048), attention 4 x 128 x 32 x sum over records of
+    L(L+1)/2).  On N GPUs (weak scaling, T tokens per GPU): the attention half works on the rank's own
+    records, the MoE block runs expert-parallel; rank 0 prints the line, every rank checks its bytes
+    against a single-GPU context."""
     import numpy as np
     import torch
+    import torch.distributed as dist
     from cleffa_b200 import OmniBackend, workloads
-    from oracle import omni_attn_oracle as ao     # weight and position generators only (not the timed path)
 
-    torch.cuda.set_device(0)
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if args.strong:
+        raise SystemExit("--attention scales by records (tokens stay with their rank): weak scaling only")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     T, n_layers = T_TOKENS, max(1, args.layers)
+    el = E // world
     single = n_layers > 1 or T > 4096
     bounds = np.array([0, T], np.int32) if single else workloads.varlen_bounds(SEED, T)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     peaks = measured_peaks()
-    with OmniBackend(0, stream=stream.cuda_stream) as b:
+    router, gate_up, down = workloads.make_weights(SEED)
+    aw = workloads.make_attention_weights(SEED)
+
+    def layer_weights(l):
+        """Layer 0: the seeded host weights; further layers from a device generator every rank seeds alike."""
+        if l == 0:
+            return (router, gate_up, down), (aw["attn_norm"], aw["w_qkv"], aw["w_out"], aw["q_norm"], aw["k_norm"])
+        g = torch.Generator(device="cuda").manual_seed(1000 * SEED + l)
+        moe = tuple((torch.randn(sh, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                    for sh in ((E, H), (E, 2 * F, H), (E, H, F)))
+        qkv, out = [(torch.randn(sh, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16) for sh in ((5120, H), (H, 4096))]
+        return moe, (torch.ones(H, device="cuda"), qkv, out, torch.ones(128, device="cuda"), torch.ones(128, device="cuda"))
+
+    def bind(backend, layers, lo, hi):
+        for l in range(layers):
+            (r_, gu_, dn_), attn = layer_weights(l)
+            backend.bind_layer(l, r_.cuda(), gu_[lo:hi].cuda().contiguous(), dn_[lo:hi].cuda().contiguous())
+            backend.bind_attention(l, *attn)
+            backend.bind_norm(l, torch.ones(H), 1e-6)
+
+    with OmniBackend(local, stream=stream.cuda_stream) as b:
         b.reserve(T, n_layer=n_layers)
-        g = torch.Generator(device="cuda").manual_seed(SEED)
-        router, gate_up, down = workloads.make_weights(SEED)
-        aw = ao.make_attention_weights(SEED)
-        for l in range(n_layers):
-            if l == 0:
-                b.bind_layer(0, router, gate_up, down)
-                b.bind_attention(0, aw["attn_norm"], aw["w_qkv"], aw["w_out"], aw["q_norm"], aw["k_norm"])
-            else:
-                b.bind_layer(l, *[(torch.randn(sh, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
-                                  for sh in ((E, H), (E, 2 * F, H), (E, H, F))])
-                qkv, out = [(torch.randn(sh, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16) for sh in ((5120, H), (H, 4096))]
-                b.bind_attention(l, torch.ones(H, device="cuda"), qkv, out, torch.ones(128, device="cuda"), torch.ones(128, device="cuda"))
-            b.bind_norm(l, torch.ones(H), 1e-6)
-        pos = torch.from_numpy(np.ascontiguousarray(ao.make_positions(SEED, bounds).T)).cuda()
-        x0 = workloads.make_activations(SEED, T).float().cuda()
+        for kv in args.option:
+            name, _, val = kv.partition("=")
+            b.set_option(name, int(val))
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, b.ep_export())
+            b.ep_connect(rank, world, b"".join(handles))
+        bind(b, n_layers, rank * el, (rank + 1) * el)
+        if world > 1:
+            dist.barrier()
+            b.ep_sync(30000)
+        pos = torch.from_numpy(np.ascontiguousarray(workloads.make_positions(SEED, bounds).T)).cuda()
+        x0 = workloads.make_activations(SEED + 1000 * rank, T).float().cuda()
         x = x0.clone()
+
+        def agree(v, op):
+            if world == 1:
+                return v
+            t = torch.tensor([v], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=op)
+            return float(t[0])
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
 
         def run(attention_only):
             x.copy_(x0)
             b.begin()
             for l in range(n_layers):
-                b.encode_attention(l, x, pos, bounds)
-                if not attention_only:
-                    b.encode_norm_moe(l, x, bounds)
+                if attention_only:
+                    b.encode_attention(l, x, pos, bounds)
+                else:
+                    b.encode_layer(l, x, pos, bounds)
 
         def timed(attention_only):
             for _ in range(max(3, args.warmup)):
                 run(attention_only)
             b.complete()
             regions = []
-            while not regions or (sum(regions) < args.min_time_ms and len(regions) < args.max_regions):
-                torch.cuda.synchronize()
+            while True:
+                barrier()
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record(stream)
                 for _ in range(args.steps):
                     run(attention_only)
                 stop.record(stream)
+                barrier()
                 b.complete()
-                regions.append(start.elapsed_time(stop))
+                regions.append(agree(start.elapsed_time(stop), dist.ReduceOp.MAX if world > 1 else None))
+                enough = sum(regions) >= args.min_time_ms or len(regions) >= args.max_regions
+                if agree(1.0 if enough else 0.0, dist.ReduceOp.MAX if world > 1 else None) > 0:
+                    break
             return statistics.median(regions) / args.steps, len(regions)
 
-        with ClockSampler(0) as sampler:
+        with ClockSampler(local) as sampler:
             attn_ms, n1 = timed(True)
             layer_ms, n2 = timed(False)
-        lens = np.diff(bounds).astype(np.float64)
-        flop = n_layers * (2.0 * T * (H * 5120 + 4096 * H) + 4.0 * 128 * 32 * float((lens * (lens + 1) / 2).sum()))
-        print(json.dumps({
-            "metric": f"decoder-layer prefill tokens/sec at T={T}" + (f" through {n_layers} layers" if n_layers > 1 else ""),
-            "value": T / (layer_ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": layer_ms, "regions": n2, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": f"Clef-Omni decoder layer(s): attention half (32/4 heads of 128, causal per record) + RMSNorm + MoE block, T={T}, "
-                                   f"{len(lens)} record(s), {n_layers} layer(s), bf16 weights N(0,0.02), seed {SEED}",
-                       "timing": f"CUDA events around exactly {args.steps} passes, median of the regions"},
-            "attention_half": {"ms_per_pass": attn_ms, "ms_per_layer": attn_ms / n_layers, "tflops": flop / (attn_ms * 1e-3) / 1e12,
-                               "frac_of_bf16_peak": flop / (attn_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "regions": n1,
-                               "flop": flop},
-            "moe_half_ms_per_layer": (layer_ms - attn_ms) / n_layers,
-            "clocks": sampler.summary(),
-        }), flush=True)
+
+        ep_equal = None
+        if world > 1:
+            # one untimed, checked pass of layer 0: the same tokens through a single-GPU context with all experts
+            out_ep = x0.clone()
+            b.begin(); b.encode_layer(0, out_ep, pos, bounds); b.complete()
+            solo_stream = torch.cuda.Stream()
+            with OmniBackend(local, stream=solo_stream.cuda_stream) as solo:
+                solo.reserve(T)
+                bind(solo, 1, 0, E)
+                out_1 = x0.clone()
+                torch.cuda.synchronize()
+                solo.begin(); solo.encode_layer(0, out_1, pos, bounds); solo.complete()
+            ep_equal = agree(1.0 if torch.equal(out_ep, out_1) else 0.0, dist.ReduceOp.MIN) > 0
+
+        if rank == 0:
+            lens = np.diff(bounds).astype(np.float64)
+            flop = n_layers * (2.0 * T * (H * 5120 + 4096 * H) + 4.0 * 128 * 32 * float((lens * (lens + 1) / 2).sum()))
+            line = {
+                "metric": f"decoder-layer prefill tokens/sec at T={T}" + (f" through {n_layers} layers" if n_layers > 1 else ""),
+                "value": T * world / (layer_ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+                "ms_per_step": layer_ms, "regions": n2, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": f"Clef-Omni decoder layer(s): attention half (32/4 heads of 128, causal per record) + RMSNorm + MoE block, T={T} per GPU, "
+                                       f"{len(lens)} record(s), {n_layers} layer(s), bf16 weights N(0,0.02), seed {SEED}",
+                           "parallelism": "single GPU" if world == 1 else f"records data-parallel, experts ep{world} (rows exchanged by peer stores from inside the expert kernels)",
+                           "timing": f"CUDA events around exactly {args.steps} passes, max over ranks, median of the regions"},
+                "attention_half": {"ms_per_pass": attn_ms, "ms_per_layer": attn_ms / n_layers, "tflops": flop / (attn_ms * 1e-3) / 1e12,
+                                   "frac_of_bf16_peak": flop / (attn_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "regions": n1,
+                                   "flop": flop},
+                "moe_half_ms_per_layer": (layer_ms - attn_ms) / n_layers,
+                "clocks": sampler.summary(),
+            }
+            if ep_equal is not None:
+                line["ep_bitwise_equal"] = bool(ep_equal)
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            b.ep_disconnect()
+            dist.barrier()
+    if world > 1:
+        dist.destroy_process_group()
+    if ep_equal is not None and not ep_equal:
+        raise SystemExit("expert-parallel layer output differs from the single-GPU output")
 
 
 def sweep(args):
@@ -584,7 +660,7 @@ def main():
     ap.add_argument("--seed", type=int, default=None, help="workload seed (default 1; 2 with --layers, 3 with --bias zipf)")
     ap.add_argument("--min-time-ms", type=float, default=1000.0, help="repeat the K-step timed region until this much device time was timed")
     ap.add_argument("--max-regions", type=int, default=400)
-    ap.add_argument("--attention", action="store_true", help="time the attention half and whole decoder layers (attention + norm + MoE), one GPU")
+    ap.add_argument("--attention", action="store_true", help="time the attention half and whole decoder layers (attention + norm + MoE); with --gpus N: records data-parallel, experts sharded (weak scaling)")
     ap.add_argument("--sweep", action="store_true", help="BASELINE configuration 5: latency table over small batch sizes, one GPU")
     ap.add_argument("--sweep-tokens", type=int, nargs="+", default=[1, 8, 32, 64, 128, 256])
     ap.add_argument("--norm", action="store_true", help="with --layers: each layer normalises the residual stream itself (RMSNorm, unit weights) instead of taking a BF16 copy")

@@ -39,12 +39,13 @@ __global__ void dense_tiles_kernel(int T, omni_ttile *ttiles, int32_t *n_ttiles,
 }
 
 // ------------------------------------------------------------------ q/k norm + rotary + layout
-// One block per token, four warps, nine heads each (32 query heads, then the 4 key heads): 128
-// values per head, four per lane (elements lane + 32 j).  Pair p of a head is (element p, element
-// p + 64); its angle is position[axis] * theta^(-p/64) with axis = p % 3 for p < 60 and the
-// temporal axis above (sections 24/20/20 interleaved; clef.metal:2051-2053).  The angle is formed
-// and reduced modulo 2 pi in FP64 -- FP32 loses ~pos * 6e-8 rad (clef.metal:2055-2060) -- and its
-// cosine and sine, the same for every head of the token, are computed once per warp.
+// One block per token, four warps, nine heads each (32 query heads, then the 4 key heads).  A lane
+// holds four consecutive elements of the 128 of a head (one 8-byte load and store); pair p of a
+// head is (element p, element p + 64), so a lane's partners sit in lane ^ 16.  The pair's angle is
+// position[axis] * theta^(-p/64) with axis = p % 3 for p < 60 and the temporal axis above (sections
+// 24/20/20 interleaved; clef.metal:2051-2053).  The angle is formed and reduced modulo 2 pi in
+// FP64 -- FP32 loses ~pos * 6e-8 rad (clef.metal:2055-2060) -- and its cosine and sine, the same
+// for every head of the token, are computed once per warp.
 __global__ void __launch_bounds__(128) attn_prep_kernel(const __nv_bfloat16 *__restrict__ qkv, const float *__restrict__ qw,
                                                         const float *__restrict__ kw, const int32_t *__restrict__ pos,
                                                         int head_stride, float eps, double theta,
@@ -54,39 +55,43 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const __nv_bfloat16 *__r
     dep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = blockIdx.x;
-    float cs[2], sn[2];
+    const bool upper = lane >= 16;                                               // elements 64..127: the second of each pair
+    float cs[4], sn[4];
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int pair = lane + 32 * j, axis = pair < 60 ? pair % 3 : 0;
+    for (int j = 0; j < 4; j++) {
+        const int pair = 4 * (lane & 15) + j, axis = pair < 60 ? pair % 3 : 0;
         const double angle = (double)__ldg(pos + 3 * t + axis) * exp2(-(double)pair * (1.0 / 64.0) * log2(theta));
         const double turns = rint(angle * 0.15915494309189535);
         const float r = (float)fma(-turns, 6.283185307179586, angle);           // |r| <= pi, accurate to FP32 rounding
         sincosf(r, &sn[j], &cs[j]);
+        if (!upper) sn[j] = -sn[j];                                              // lo' = lo cos - hi sin, hi' = hi cos + lo sin
     }
-    float wq[4], wk[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) { wq[j] = __ldg(qw + lane + 32 * j); wk[j] = __ldg(kw + lane + 32 * j); }
+    const float4 wq = __ldg(reinterpret_cast<const float4 *>(qw) + lane), wk = __ldg(reinterpret_cast<const float4 *>(kw) + lane);
     bool bad = false;
     for (int h = warp; h < NH + NKV; h += 4) {
         const bool query = h < NH;
-        const __nv_bfloat16 *src = qkv + t * OMNI_QKV + (long)h * HD;
-        float x[4], sum = 0.f;
+        const uint2 raw = *reinterpret_cast<const uint2 *>(qkv + t * OMNI_QKV + (long)h * HD + 4 * lane);
+        float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                      __uint_as_float(raw.y & 0xffff0000u)};
+        float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; j++) { x[j] = __bfloat162float(src[lane + 32 * j]); bad |= !(fabsf(x[j]) < CUDART_INF_F); sum += x[j] * x[j]; }
+        for (int j = 0; j < 4; j++) { bad |= !(fabsf(x[j]) < CUDART_INF_F); sum += x[j] * x[j]; }
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
         const float inv = rsqrtf(sum / (float)HD + eps);
+        const float4 w = query ? wq : wk;
+        x[0] = x[0] * inv * w.x; x[1] = x[1] * inv * w.y; x[2] = x[2] * inv * w.z; x[3] = x[3] * inv * w.w;
+        uint32_t o[2];
 #pragma unroll
-        for (int j = 0; j < 4; j++) x[j] = x[j] * inv * (query ? wq[j] : wk[j]);
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const float lo = x[j], hi = x[j + 2];
-            x[j] = lo * cs[j] - hi * sn[j];
-            x[j + 2] = hi * cs[j] + lo * sn[j];
+        for (int j = 0; j < 4; j += 2) {
+            const float p0 = __shfl_xor_sync(0xffffffffu, x[j], 16), p1 = __shfl_xor_sync(0xffffffffu, x[j + 1], 16);
+            const float y0 = x[j] * cs[j] + p0 * sn[j], y1 = x[j + 1] * cs[j + 1] + p1 * sn[j + 1];
+            bad |= !(fabsf(y0) < CUDART_INF_F) || !(fabsf(y1) < CUDART_INF_F);
+            const __nv_bfloat162 bb = __floats2bfloat162_rn(y0, y1);
+            o[j >> 1] = *reinterpret_cast<const uint32_t *>(&bb);
         }
         __nv_bfloat16 *dst = query ? Q + ((long)h * head_stride + t) * HD : K + ((long)(h - NH) * head_stride + t) * HD;
-#pragma unroll
-        for (int j = 0; j < 4; j++) { bad |= !(fabsf(x[j]) < CUDART_INF_F); dst[lane + 32 * j] = __float2bfloat16(x[j]); }
+        *reinterpret_cast<uint2 *>(dst + 4 * lane) = make_uint2(o[0], o[1]);
     }
     // reported at completion like the reference's status bit 2 (clef.metal:2120)
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, OMNI_ST_ATTN_NONFINITE);

@@ -116,29 +116,6 @@ def attention_half_rows(x, positions, rows, attn_norm, w_qkv, q_norm, k_norm, w_
     return x[rows] + values @ w_out.T
 
 
-def make_attention_weights(seed, hidden=2048, n_head=32, n_kv=4, head_dim=128, std=0.02):
-    """Random-init weights of the attention half in the converted layout: BF16 matrices N(0, std),
-    FP32 norm weights around 1."""
-    g = torch.Generator(device="cpu").manual_seed(7000003 * seed + 29)
-    w_qkv = (torch.randn((n_head + 2 * n_kv) * head_dim, hidden, generator=g) * std).to(torch.bfloat16)
-    w_out = (torch.randn(hidden, n_head * head_dim, generator=g) * std).to(torch.bfloat16)
-    attn_norm = 1.0 + 0.1 * torch.randn(hidden, generator=g)
-    q_norm = 1.0 + 0.1 * torch.randn(head_dim, generator=g)
-    k_norm = 1.0 + 0.1 * torch.randn(head_dim, generator=g)
-    return dict(w_qkv=w_qkv, w_out=w_out, attn_norm=attn_norm.float(), q_norm=q_norm.float(), k_norm=k_norm.float())
-
-
-def make_positions(seed, seq_bounds):
-    """Text-like 3-axis positions: all three axes equal to the index inside the record, except a
-    seeded stretch per record whose row/column axes differ (as image tokens' do)."""
-    rng = np.random.default_rng(seed)
-    b = np.asarray(seq_bounds)
-    pos = np.zeros((3, b[-1]), np.int32)
-    for lo, hi in zip(b[:-1], b[1:]):
-        n = hi - lo
-        pos[:, lo:hi] = np.arange(n)
-        if n > 8:
-            a = int(rng.integers(1, n // 2)); m = int(rng.integers(2, n - a))
-            pos[1, lo + a:lo + a + m] = a + rng.integers(0, 16, m)
-            pos[2, lo + a:lo + a + m] = a + rng.integers(0, 16, m)
-    return pos
+# The seeded generators live with the other synthetic workloads so that bench.py can build the same
+# bytes without importing this package.
+from cleffa_b200.workloads import make_attention_weights, make_positions  # noqa: E402,F401

@@ -152,7 +152,9 @@ def test_a_layer_is_attention_then_norm_and_moe(attn, weights0):
     pd = torch.from_numpy(np.ascontiguousarray(pos.T)).cuda()
     b.begin()
     b.encode_attention(2, xd, pd, np.asarray(bounds, np.int32))
+    b.complete()                                                       # the library runs on its own stream: finish before reading
     mid = xd.clone()
+    b.begin()
     b.encode_norm_moe(2, xd, np.asarray(bounds, np.int32))
     b.complete()
     ref = ao.attention_half(x, pos, bounds, w["attn_norm"], w["w_qkv"], w["q_norm"], w["k_norm"], w["w_out"], 32, 4)
