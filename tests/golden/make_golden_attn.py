@@ -32,7 +32,7 @@ def load_reference_fp64(ref_root: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     ref = load_reference_fp64(Path(args.reference))
     g = torch.Generator().manual_seed(11)

@@ -1,5 +1,5 @@
 /* The binding a maintainer of the reference engine adds to drive the CUDA Omni MoE backend:
- * the same text as the stub in INTEGRATION.md.  tests/test_abi.py compiles it against the
+ * the same text as the stub in the integration guide.  tests/test_abi.py compiles it against the
  * reference's own clef_engine.h (clef_config, clef_layer_w, gguf_tensor) and links it with the
  * library, so the boundary is checked against the reference's real types. */
 #include "clef_engine.h"        /* clef_config, clef_layer_w, gguf_tensor: the reference's header */

@@ -68,7 +68,7 @@ def test_open_without_a_gpu_fails_loudly():
 
 def reference_dir():
     import os
-    for cand in (os.environ.get("CLEF_REFERENCE_DIR"), "/root/reference"):
+    for cand in (os.environ.get("CLEF_REFERENCE_DIR"), ROOT.parent / "reference"):     # or a checkout beside this repository
         if cand and (Path(cand) / "clef_engine.h").exists():
             return Path(cand)
     return None
@@ -76,7 +76,7 @@ def reference_dir():
 
 @pytest.mark.skipif(reference_dir() is None, reason="no checkout of the reference engine (set CLEF_REFERENCE_DIR)")
 def test_integration_stub_builds_against_the_reference_headers(tmp_path, lib):
-    """tests/integration_stub.c is the binding INTEGRATION.md shows.  It is compiled with the
+    """tests/integration_stub.c is the binding the integration guide shows.  It is compiled with the
     reference's own clef_engine.h in front of this repository's header, so clef_config,
     clef_layer_w and gguf_tensor (clef_engine.h:18-40, clef_gguf.h:31-39) are the real types,
     and linked against the library so every call resolves."""
@@ -84,7 +84,7 @@ def test_integration_stub_builds_against_the_reference_headers(tmp_path, lib):
     stub = ROOT / "tests" / "integration_stub.c"
     md = (ROOT / "INTEGRATION.md").read_text()
     body = stub.read_text().split("*/", 1)[1].strip()
-    assert body in md, "INTEGRATION.md must show the stub that is compiled here"
+    assert body in md, "the integration guide must show the stub that is compiled here"
     main = tmp_path / "main.c"
     main.write_text('#include <stdbool.h>\n#include <stddef.h>\nvoid cuda_backend_close(void);\n'
                     'int main(int argc, char **argv) { (void)argv; if (argc > 99) cuda_backend_close(); return 0; }\n')
