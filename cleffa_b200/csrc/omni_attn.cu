@@ -135,8 +135,9 @@ __global__ void __launch_bounds__(256) v_transpose_kernel(const __nv_bfloat16 *_
 // record).  Key blocks of 128 run from the record's start to the tile's diagonal.  For each head x
 // of the pair and block j:
 //   S_x(j) = Q_x K_j^T       tcgen05, FP32 in TMEM
-//   P_x(j) = exp2(c S - m)   128 threads, one per query row; BF16, written back over the first
-//                            64 columns of S_x in TMEM (two keys per column)
+//   P_x(j) = exp2(c S - m)   256 threads, two per query row (64 keys each); BF16, two keys per
+//                            column, written back over score columns the writing thread alone has
+//                            read (keys 0..63 over columns 0..31, keys 64..127 over 96..127)
 //   O_x   += P_x(j) V_j      tcgen05 with the A operand read from TMEM, accumulated over all blocks
 // The two heads run half a block apart: while one head's threads are in their exponentials the
 // tensor pipe forms the other head's value product and next scores, so neither waits for long.
@@ -146,12 +147,13 @@ __global__ void __launch_bounds__(256) v_transpose_kernel(const __nv_bfloat16 *_
 // otherwise P simply holds values up to 256.  The accumulators never leave TMEM until the end.
 struct AttnTile { int32_t rec_start, q0, q_len, vcol0; };          // vcol0: Vt column of the record's first token
 
-constexpr int AT_THREADS = 384;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..7 softmax of head 0, 8..11 of head 1
+constexpr int AT_THREADS = 640;                                    // warp 0 loads, 1 MMA, 2 TMEM, 3 spare, 4..11 softmax of head 0, 12..19 of head 1
 constexpr int AT_TILE_BYTES = 128 * 128 * 2;                       // 32 KiB: 128 rows x 128 BF16 as two 64-column halves
 constexpr int AT_KV_STAGES = 2;
 constexpr int AT_TMEM_COLS = 512;                                  // S_0, S_1, O_0, O_1 of 128 columns each
 constexpr int AT_N_BARS = 16;
-constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + AT_N_BARS * 8 + 64;
+constexpr int AT_XCH_BYTES = 2 * 2 * 2 * 128 * 4;                  // [head][block parity][row half][row]
+constexpr int AT_SMEM_BYTES = AT_TILE_BYTES * (2 + 2 * AT_KV_STAGES) + 1024 + AT_N_BARS * 8 + 64 + AT_XCH_BYTES;
 constexpr float AT_LAZY = 8.f;                                     // log2 of how far a block may exceed the reference maximum
 
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t *r) {
@@ -221,6 +223,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(misc + 4);
     volatile int *armed = reinterpret_cast<volatile int *>(misc + 16);         // [5]: q, k stages, v stages (parity of the load in flight, -1 none)
+    volatile int *quit = reinterpret_cast<volatile int *>(misc + 40);          // [2] per head: a softmax thread's wait ran out, all of them leave together
+    float *xch = reinterpret_cast<float *>(misc + 64);                         // what the two threads of a row tell each other
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const AttnTile tile = tiles[gridDim.x - 1 - blockIdx.x];                    // a record's longest tiles first
@@ -232,9 +236,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; s++) {
             mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
-            mbar_init(s_full(s), 1); mbar_init(p_full(s), 128); mbar_init(o_done(s), 1);
+            mbar_init(s_full(s), 1); mbar_init(p_full(s), 256); mbar_init(o_done(s), 1);
         }
         *abort_flag = 0;
+        quit[0] = quit[1] = 0;
         for (int i = 0; i < 5; i++) armed[i] = -1;
         fence_mbar_init();
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_vt);
@@ -307,10 +312,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (!ok) break;
                 tc_fence_after();
                 // O_x += P_x V: the 128 keys of the block are eight K=16 steps, 8 TMEM columns of P each
+                // (keys 0..63 in columns 0..31 of the score buffer, keys 64..127 in columns 96..127)
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
                     const uint64_t db = smem_desc_sw128(v_smem(pv.stage) + (k >> 2) * (AT_TILE_BYTES / 2));
-                    umma_bf16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + 8 * k, db + 2u * (k & 3), idesc, (j | k) ? 1u : 0u);
+                    umma_bf16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + 8 * k + (k >> 2) * 64, db + 2u * (k & 3), idesc, (j | k) ? 1u : 0u);
                 }
                 if (x == 1) umma_commit(v_empty(pv.stage));
                 if (j + 1 < n_blocks) {
@@ -325,49 +331,61 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             pk.advance(AT_KV_STAGES);
         }
     } else if (warp >= 4) {
-        // ---------------------------------------------------------- softmax of one head: one thread per query row
-        const int x = (warp - 4) >> 2, q4 = warp & 3;
+        // ---------------------------------------------------------- softmax of one head: two threads per query row
+        // Thread (row r, half hf) owns keys hf*64.. of every score block, the P columns that hold
+        // them, and head dimensions hf*64.. of the accumulator.  The two threads of a row sit in
+        // different warps and exchange their partial maxima through shared memory at the head's
+        // named barrier; a thread whose wait ran out marks `quit` and still joins that barrier,
+        // after which all threads of the head leave together.
+        const int x = (warp - 4) >> 3, q4 = warp & 3, hf = ((warp - 4) >> 2) & 1;
         const int r = q4 * 32 + lane;                                             // row inside the tile = TMEM lane
         const uint32_t tmem_s = tmem_base + x * 128 + ((uint32_t)(q4 * 32) << 16);
-        const uint32_t tmem_o = tmem_base + 256 + x * 128 + ((uint32_t)(q4 * 32) << 16);
+        const uint32_t tmem_o = tmem_base + 256 + x * 128 + ((uint32_t)(q4 * 32) << 16) + hf * 64;
+        float *xc = xch + x * 512;                                                // [parity][half][row]
         const float c = scale * 1.4426950408889634f;                              // scores to log2 units
         float m = 0.f, l = 0.f;
         bool alive = true;
         for (int j = 0; j < n_blocks; j++) {
-            alive = __all_sync(0xffffffffu, mbar_wait(s_full(x), (uint32_t)j & 1u, abort_flag, status));
-            if (!alive) break;
-            tc_fence_after();
-            // Two sweeps over the row's 128 scores, 32 at a time with the next 32 in flight: the maximum
-            // first, then the probabilities (reading TMEM twice costs less than holding 128 registers).
+            const int par = j & 1;
+            if (alive) alive = mbar_wait(s_full(x), (uint32_t)par, abort_flag, status);
+            alive = __all_sync(0xffffffffu, alive);
             const bool diagonal = j == n_blocks - 1;                              // the only block with keys after some of the rows
-            uint32_t ta[32], tb[32];
-            float mx[4];
-            tmem_ld32(tmem_s, ta);
-            tmem_ld_wait();
+            uint32_t ta[32];
+            float pmax = -CUDART_INF_F;
+            if (alive) {
+                tc_fence_after();
+                // two sweeps over the thread's 64 scores, 32 at a time: the maximum first, then the
+                // probabilities (reading TMEM twice costs less than holding the scores in registers)
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                uint32_t *cur = (q & 1) ? tb : ta, *nxt = (q & 1) ? ta : tb;
-                if (q < 3) tmem_ld32(tmem_s + (q + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(nxt));
-                if (diagonal) {
+                for (int q = 0; q < 2; q++) {
+                    tmem_ld32(tmem_s + hf * 64 + q * 32, ta);
+                    tmem_ld_wait();
+                    if (diagonal) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (q * 32 + i > r) cur[i] = 0xff800000u;
+                        for (int i = 0; i < 32; i++)
+                            if (hf * 64 + q * 32 + i > r) ta[i] = 0xff800000u;
+                    }
+                    float mq = fmaxf(__uint_as_float(ta[0]), __uint_as_float(ta[1]));
+#pragma unroll
+                    for (int i = 2; i < 32; i += 2) mq = max3(mq, __uint_as_float(ta[i]), __uint_as_float(ta[i + 1]));
+                    pmax = fmaxf(pmax, mq);
                 }
-                mx[q] = fmaxf(__uint_as_float(cur[0]), __uint_as_float(cur[1]));
-#pragma unroll
-                for (int i = 2; i < 32; i += 2) mx[q] = max3(mx[q], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
-                if (q < 3) tmem_ld_wait();
+                xc[(par * 2 + hf) * 128 + r] = pmax;
+            } else {
+                quit[x] = 1;
             }
+            asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
+            if (quit[x]) { alive = false; break; }
             // key 0 of every block is visible to every row (tiles and blocks are both cut from the
             // record's start in steps of 128), so the block maximum is finite
-            const float bm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;
+            const float bm = fmaxf(pmax, xc[(par * 2 + (hf ^ 1)) * 128 + r]) * c;
             float corr = 1.f;
             if (j == 0) m = bm;
             else if (bm > m + AT_LAZY) { corr = ex2_approx(m - bm); m = bm; l *= corr; }
             if (__any_sync(0xffffffffu, corr != 1.f)) {
                 // the scores of this block being complete means the previous value product is: O is at rest
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
+                for (int q = 0; q < 2; q++) {
                     uint32_t t32[32];
                     tmem_ld32(tmem_o + q * 32, t32);
                     tmem_ld_wait();
@@ -377,50 +395,49 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 }
             }
             // P = exp2(c s - m) as BF16 (values up to 2^8 while m lags the running maximum), two keys per column
-            uint32_t pk[64];
+            uint32_t pk[32];
             float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             const float2 c2 = make_float2(c, c), nm2 = make_float2(-m, -m);
-            // second sweep (the diagonal block with its mask, the others without)
-            auto sweep = [&](auto diag) {
-                constexpr bool DIAG = decltype(diag)::value;
-                tmem_ld32(tmem_s, ta);
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                tmem_ld32(tmem_s + hf * 64 + q * 32, ta);
                 tmem_ld_wait();
+                if (diagonal) {
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    uint32_t *cur = (q & 1) ? tb : ta, *nxt = (q & 1) ? ta : tb;
-                    if (q < 3) tmem_ld32(tmem_s + (q + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(nxt));
-                    if (DIAG) {
-#pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            if (q * 32 + i > r) cur[i] = 0xff800000u;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const float2 e = ffma2(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])), c2, nm2);
-                        const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-                        acc[i & 1] = fadd2(acc[i & 1], pp);
-                        const __nv_bfloat162 bb = __floats2bfloat162_rn(pp.x, pp.y);
-                        pk[q * 16 + i] = *reinterpret_cast<const uint32_t *>(&bb);
-                    }
-                    if (q < 3) tmem_ld_wait();
+                    for (int i = 0; i < 32; i++)
+                        if (hf * 64 + q * 32 + i > r) ta[i] = 0xff800000u;
                 }
-            };
-            if (diagonal) sweep(std::true_type{}); else sweep(std::false_type{});
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float2 e = ffma2(make_float2(__uint_as_float(ta[2 * i]), __uint_as_float(ta[2 * i + 1])), c2, nm2);
+                    const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+                    acc[i & 1] = fadd2(acc[i & 1], pp);
+                    const __nv_bfloat162 bb = __floats2bfloat162_rn(pp.x, pp.y);
+                    pk[q * 16 + i] = *reinterpret_cast<const uint32_t *>(&bb);
+                }
+            }
             l += (acc[0].x + acc[1].x) + (acc[0].y + acc[1].y);
-            tmem_st32(tmem_s, pk);
-            tmem_st32(tmem_s + 32, pk + 32);
+            // P goes over columns whose scores this thread alone read: keys 0..63 into columns 0..31,
+            // keys 64..127 into columns 96..127
+            tmem_st32(tmem_s + hf * 96, pk);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(p_full(x));
         }
-        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(o_done(x), 0, abort_flag, status));
-        if (alive) {
+        // the row's denominator is the sum of what its two threads added up (same reference maximum in both)
+        if (alive) alive = mbar_wait(o_done(x), 0, abort_flag, status);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) quit[x] = 1;
+        xc[((n_blocks & 1) * 2 + hf) * 128 + r] = l;
+        asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
+        if (!quit[x]) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float lt = l + xc[((n_blocks & 1) * 2 + (hf ^ 1)) * 128 + r];
+            const float inv = lt > 0.f ? 1.f / lt : 0.f;
             const int qg = tile.q0 + r;                                           // global token index of the row
-            uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + (h0 + x) * HD);
+            uint4 *dst = reinterpret_cast<uint4 *>(out + (long)qg * (NH * HD) + (h0 + x) * HD + hf * 64);
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
+            for (int q = 0; q < 2; q++) {
                 uint32_t t32[32];
                 tmem_ld32(tmem_o + q * 32, t32);
                 tmem_ld_wait();
