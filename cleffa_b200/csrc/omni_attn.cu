@@ -56,19 +56,29 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const __nv_bfloat16 *__r
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = blockIdx.x;
     const bool upper = lane >= 16;                                               // elements 64..127: the second of each pair
+    // the four pairs of a lane are those of lane ^ 16 too: each computes two and they swap
     float cs[4], sn[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const int pair = 4 * (lane & 15) + j, axis = pair < 60 ? pair % 3 : 0;
+    for (int j = 0; j < 2; j++) {
+        const int own = (upper ? 2 : 0) + j, pair = 4 * (lane & 15) + own, axis = pair < 60 ? pair % 3 : 0;
         const double angle = (double)__ldg(pos + 3 * t + axis) * exp2(-(double)pair * (1.0 / 64.0) * log2(theta));
         const double turns = rint(angle * 0.15915494309189535);
         const float r = (float)fma(-turns, 6.283185307179586, angle);           // |r| <= pi, accurate to FP32 rounding
-        sincosf(r, &sn[j], &cs[j]);
-        if (!upper) sn[j] = -sn[j];                                              // lo' = lo cos - hi sin, hi' = hi cos + lo sin
+        float sj, cj;
+        sincosf(r, &sj, &cj);
+        const float so = __shfl_xor_sync(0xffffffffu, sj, 16), co = __shfl_xor_sync(0xffffffffu, cj, 16);
+        cs[own] = cj; sn[own] = sj;
+        cs[own ^ 2] = co; sn[own ^ 2] = so;
     }
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        if (!upper) sn[j] = -sn[j];                                              // lo' = lo cos - hi sin, hi' = hi cos + lo sin
     const float4 wq = __ldg(reinterpret_cast<const float4 *>(qw) + lane), wk = __ldg(reinterpret_cast<const float4 *>(kw) + lane);
     bool bad = false;
-    for (int h = warp; h < NH + NKV; h += 4) {
+    static_assert((NH + NKV) % 4 == 0, "heads are dealt to four warps");
+#pragma unroll
+    for (int i = 0; i < (NH + NKV) / 4; i++) {            // unrolled: the loads of all nine heads are in flight together
+        const int h = warp + 4 * i;
         const bool query = h < NH;
         const uint2 raw = *reinterpret_cast<const uint2 *>(qkv + t * OMNI_QKV + (long)h * HD + 4 * lane);
         float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
