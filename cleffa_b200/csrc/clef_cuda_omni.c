@@ -81,6 +81,7 @@ struct clef_gpu {
     int ep_fused;                       /* expert parallelism: the expert kernels move the rows themselves (default 1) */
     float router_eps;
     int gemm_impl, router_impl;         /* 0 = tcgen05, 1 = CUDA-core check kernels */
+    int expert_chain;                   /* 1: on one GPU the down kernel is chained behind gate/up per expert (default 0: worth ~1 % only while the GPU is cool) */
     int expert_kernel;                  /* tcgen05 expert products: 2 = pairs of CTAs (cta_group::2), 1 = the same kernel on
                                            single CTAs, 0 = the earlier single-CTA kernels (two accumulators for gate/up) */
     int reserve_sms;                    /* SMs the persistent expert kernels leave to other streams */
@@ -199,6 +200,7 @@ bool clef_cuda_omni_open(clef_gpu **out, int device, void *stream, char *err, si
     g->fused_gather = 1;
     g->fused_router = 1;
     g->ep_fused = 1;
+    g->expert_chain = 0;
     void *fn = NULL;
     enum cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -308,7 +310,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         {(void **)&s->ids, (size_t)OMNI_CHUNK * OMNI_TOP * 4},
         {(void **)&s->weights, (size_t)OMNI_CHUNK * OMNI_TOP * 4},
         {(void **)&s->flag_rows, (size_t)OMNI_CHUNK * 4},
-        {(void **)&s->n_flag, 256},
+        {(void **)&s->n_flag, 2048},       /* [0..1] flagged-row counts; from word 64: done[128], done_need[128] */
         {(void **)&s->status, 256},
         {(void **)&s->sink, 256},
         {(void **)&s->stamps, (size_t)(OMNI_CHUNK / 32) * 8 * 8},
@@ -332,12 +334,14 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
     }
     s->sort.status = s->status;
     s->sort.n_flag = s->n_flag;
+    s->sort.done = ok ? s->n_flag + 64 : NULL;
+    s->sort.done_need = ok ? s->n_flag + 192 : NULL;
     for (int i = 0; i < 4 && ok; i++)
         ok = make_map(g, &s->tm_xg[i], s->xg, OMNI_ROWS, OMNI_H, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) &&
              make_map(g, &s->tm_h[i], s->h, OMNI_ROWS, OMNI_F, 32u << i, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (ok) ok = cudaMemsetAsync(s->status, 0, 256, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(s->sink, 0, 256, g->stream) == cudaSuccess &&
-                 cudaMemsetAsync(s->n_flag, 0, 256, g->stream) == cudaSuccess &&
+                 cudaMemsetAsync(s->n_flag, 0, 2048, g->stream) == cudaSuccess &&
                  cudaMemsetAsync(s->sort.n_ttiles, 0, 256, g->stream) == cudaSuccess &&
                  cudaStreamSynchronize(g->stream) == cudaSuccess;
     if (!ok) {
@@ -629,10 +633,16 @@ static bool run_experts(clef_gpu *g, const omni_layer *L, const void *xn, const 
         if (!launched(g, "down experts", omni_launch_down_pair(ctas, &L->tm_down, s->tm_h, s->sort, s->d, NULL, NULL, g->reserve_sms == 0,
                                                                g->n_sm - g->reserve_sms, g->stream))) return false;
     } else if (g->gemm_impl == 0) {
+        /* the down kernel starts on the SMs the first gate/up blocks leave and takes an expert's rows as
+         * soon as they are complete: only when this stream's kernels are chained by dependent launch
+         * and the gate/up grid invites its successor */
+        const int chain = g->expert_chain && g->reserve_sms == 0;
         if (!launched(g, "gate/up experts", omni_launch_gateup_sm100(&L->tm_gate_up, s->tm_xg, s->sort, s->h, NULL, NULL, 1, fused ? xn : NULL,
-                                                                     fused ? s->sort.rowmap : NULL, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
+                                                                     fused ? s->sort.rowmap : NULL, g->reserve_sms == 0, chain,
+                                                                     g->n_sm - g->reserve_sms, g->stream))) return false;
         stage_mark(g, 3);
-        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, g->reserve_sms == 0, g->n_sm - g->reserve_sms, g->stream))) return false;
+        if (!launched(g, "down experts", omni_launch_down_sm100(&L->tm_down, s->tm_h, s->sort, s->d, NULL, 0, g->reserve_sms == 0, chain,
+                                                                g->n_sm - g->reserve_sms, g->stream))) return false;
     } else {
         if (!launched(g, "gate/up experts (check kernel)", omni_launch_gateup_simple(s->xg, L->gate_up, s->sort.offsets, rows8, s->h, g->stream))) return false;
         stage_mark(g, 3);
@@ -987,6 +997,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "gemm")) { if (value < 0 || value > 1) return false; g->gemm_impl = (int)value; }
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "expert_kernel")) { if (value < 0 || value > 2) return false; g->expert_kernel = (int)value; }
+    else if (!strcmp(name, "expert_chain")) g->expert_chain = value != 0;
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "ep_fused")) g->ep_fused = value != 0;

@@ -60,6 +60,8 @@ typedef struct {
     int32_t *sched;        /* [8] work counters: [0] gate/up, [1..] down (one per launch group), zeroed by the scan */
     uint32_t *status;      /* [1]                                     */
     int32_t *n_flag;       /* [2] rows flagged for the exact pass: the scan moves [0] to [1] and clears [0] for the next pass */
+    int32_t *done;         /* [128] epilogue warps of the gate/up kernel that have stored their part of an expert's rows; zeroed by the scan (may be NULL) */
+    int32_t *done_need;    /* [128] what done[e] reaches when expert e's rows are complete: 8 warps x 6 weight tiles x token tiles */
 } omni_sort_state;
 
 /* Expert parallelism: every rank's view of every rank's exchange buffers (index = rank). */
@@ -151,14 +153,18 @@ cudaError_t omni_launch_router_sm100(const CUtensorMap *tm_x, int nt, const CUte
  * row gather_rows[i] of gather_src ([rows][2048] BF16) itself and tm_x4 is not used */
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, const uint32_t *ready, const int32_t *need, int group_size,
-                                     const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
-                                     cudaStream_t s);
+                                     const void *gather_src, const int32_t *gather_rows, int early_dependents, int announce,
+                                     int n_sm, cudaStream_t s);
 /* tile_bounds (may be NULL) + group: restrict the launch to tiles [tile_bounds[group], tile_bounds[group+1]).
  * early_dependents (both launchers): let blocks of the next kernel in the stream become resident
  * while this one runs; pass 0 when the grid leaves SMs free for kernels of another stream */
+/* announce (gate/up) + chained (down): the gate/up kernel counts, per expert, the epilogue warps
+ * that have stored their rows (st.done); the down kernel launched behind it then does not wait for
+ * the whole gate/up grid but, per expert, for st.done[e] to reach st.done_need[e], so its blocks
+ * start on the SMs the first gate/up blocks leave while the last ones are still working. */
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                   void *d, const int32_t *tile_bounds, int group, int early_dependents, int n_sm,
-                                   cudaStream_t s);
+                                   void *d, const int32_t *tile_bounds, int group, int early_dependents, int chained,
+                                   int n_sm, cudaStream_t s);
 
 /* ---- expert products on pairs of SMs (omni_expert.cu) ---- */
 cudaError_t omni_expert_configure(void);  /* opt-in shared-memory sizes; call once per device */

@@ -229,6 +229,9 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         for (int j = 0; j < nt; j++)
             st.ttiles[first + j] = omni_ttile{e, off + j * base + min(j, extra), base + (j < extra), first | (nt << 16)};
         if (e < 8) st.sched[e] = 0;
+        // per expert: how many epilogue warps of the gate/up kernel will report (8 per work item, 6 weight
+        // tiles per token tile), and the count they report into
+        if (st.done) { st.done[e] = 0; st.done_need[e] = 8 * (OMNI_F / 128) * nt; }
         if (e == OMNI_E - 1) *st.n_ttiles = tiles_incl;
         // the router and the exact pass of this chunk are done with the flagged-row count: keep it
         // for introspection and clear it for the next router launch (no memset between passes)
@@ -610,6 +613,7 @@ cudaError_t omni_noalloc_assign(const int32_t *ids, int rows, int32_t *counts, i
     st.segcount = sc->segcount; st.ttiles = sc->ttiles; st.n_ttiles = &sc->n_ttiles; st.sched = sc->sched;
     st.status = status;
     st.n_flag = sc->n_flag;
+    st.done = nullptr; st.done_need = nullptr;
     return omni_launch_assign(ids, rows, st, 0, s);
 }
 

@@ -85,7 +85,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    const uint32_t *__restrict__ ready, const int32_t *__restrict__ need, int group_size,
                    const int32_t *__restrict__ tile_bounds, int tile_group,
                    const __nv_bfloat16 *__restrict__ gather_src, const int32_t *__restrict__ gather_rows,
-                   int early_dependents) {
+                   int early_dependents, int32_t *__restrict__ done, int chained) {
     using C = GemmCfg<MODE>;
     constexpr int KSTAGES = C::KTOT / BK;
     constexpr int WS = C::W_STAGES, TS = C::T_STAGES;
@@ -129,7 +129,11 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int i = 0; i < 4; i++) prefetch_tmap(&tm_tok.m[i]);
     }
     if (warp == 2) { tmem_alloc(smem_u32((const void *)tmem_slot), 512); tmem_relinquish(); }
-    dep_wait();                 // everything above overlaps the tail of the previous kernel
+    // Chained behind the gate/up kernel, the down kernel does not wait for that whole grid: what it
+    // reads of it (rows of h) it takes expert by expert once `ready` says they are complete.  The
+    // kernels before gate/up had completed before gate/up let this grid start; their results (the
+    // tile list) are read past L1 below.
+    if (!chained) dep_wait();   // everything above overlaps the tail of the previous kernel
     // Blocks of the next kernel that become resident early sit on whatever SM is free.  When
     // this grid leaves SMs free on purpose (for copy kernels of another stream), it must not
     // invite them.
@@ -140,7 +144,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     // the launch covers work items [work_lo, n_work): everything, or one group of experts
     const int work_lo = tile_bounds ? tile_bounds[tile_group] * C::MTILES : 0;
-    const int n_work = tile_bounds ? min(tile_bounds[tile_group + 1], *n_ttiles) * C::MTILES : *n_ttiles * C::MTILES;
+    const int n_tt = __ldcg(n_ttiles);
+    const int n_work = tile_bounds ? min(tile_bounds[tile_group + 1], n_tt) * C::MTILES : n_tt * C::MTILES;
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- scheduler + weight producer
@@ -149,8 +154,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // item i+1 is decoded (its claim came back one iteration ago) and item i+2 is claimed.
         PipeState p, wr;
         const uint64_t pol_w1 = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+        auto tile_at = [&](int i) {                           // past L1: a chained launch starts before its predecessor ends
+            const int4 v = __ldcg(reinterpret_cast<const int4 *>(ttiles) + i);
+            return omni_ttile{v.x, v.y, v.z, v.w};
+        };
         auto lookup = [&](int w, int &m, int &cnt) {          // item -> (weight tile m, tile-list index)
-            const omni_ttile t0 = ttiles[w / C::MTILES];
+            const omni_ttile t0 = tile_at(w / C::MTILES);
             const int first = t0.group & 0xffff;
             cnt = t0.group >> 16;
             const int local = w - first * C::MTILES;
@@ -161,7 +170,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         omni_ttile cur = omni_ttile{0, 0, -1, 0};
         int w0 = work_lo + atomicAdd(work_counter, 1);
         int w1 = work_lo + atomicAdd(work_counter, 1);        // index of the item after the current one
-        if (w0 < n_work) cur = ttiles[lookup(w0, cur_m, cur_cnt)];
+        if (w0 < n_work) cur = tile_at(lookup(w0, cur_m, cur_cnt));
         for (;;) {
             if (!mbar_wait(iempty_bar(wr.stage), wr.phase ^ 1u, abort_flag, status)) break;
             if (cur.len < 0) {
@@ -176,7 +185,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const int w2 = work_lo + atomicAdd(work_counter, 1);   // consumed two iterations from now
             const bool has_next = w1 < n_work;
             omni_ttile head = omni_ttile{0, 0, 0, 0};
-            if (has_next) head = ttiles[w1 / C::MTILES];      // first dependent load: in flight during the loop below
+            if (has_next) head = tile_at(w1 / C::MTILES);      // first dependent load: in flight during the loop below
             int nxt_m = 0, nxt_cnt = 1;
             const int wrow = cur.expert * C::W_ROWS_PER_EXPERT + cur_m * 128;
             // a weight tile is read once per token tile of its expert: keep it in L2 while
@@ -190,7 +199,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     nxt_cnt = head.group >> 16;
                     const int local = w1 - first * C::MTILES;
                     nxt_m = local / nxt_cnt;
-                    nxt = ttiles[first + local % nxt_cnt];
+                    nxt = tile_at(first + local % nxt_cnt);
                 }
                 ok = mbar_wait(wempty_bar(p.stage), p.phase ^ 1u, abort_flag, status);
                 if (!ok) break;
@@ -290,7 +299,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 // expert parallelism: this expert's rows are being written by other GPUs while the
                 // kernel runs; wait (bounded, polling gently) until its whole group has arrived
                 const int grp = expert / group_size;
-                const uint32_t want = (uint32_t)need[grp];
+                const uint32_t want = (uint32_t)__ldcg(need + grp);      // past L1, like the tile list
                 const uint64_t t0 = globaltimer_ns();
                 while (ld_acquire_sys_u32(ready + grp) != want) {
                     __nanosleep(500);
@@ -374,7 +383,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int it = 0; ok; it++) {
             ok = mbar_wait(ifull_bar(wr.stage), wr.phase, abort_flag, status);
             if (!ok) break;
-            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, m = ring[wr.stage].m;
+            const int row0 = ring[wr.stage].row0, len = ring[wr.stage].len, m = ring[wr.stage].m, expert = ring[wr.stage].expert;
             __syncwarp();
             if (lane == 0) mbar_arrive(iempty_bar(wr.stage));
             wr.advance(RING);
@@ -424,6 +433,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                             if (col + 1 < len) o16[(long)(col + 1) * C::OUT_COLS] = (unsigned short)(hp[ci][j] >> 16);
                         }
                     }
+                }
+                if (done) {
+                    // this warp's part of the expert's rows is out: tell the down kernel chained behind
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(done + expert, 1);
                 }
             } else {
                 for (int c = half; c < nchunk; c += 2) {
@@ -477,25 +492,27 @@ cudaError_t omni_sm100_configure(void) {
 
 cudaError_t omni_launch_gateup_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_x4, const omni_sort_state st,
                                      void *h, const uint32_t *ready, const int32_t *need, int group_size,
-                                     const void *gather_src, const int32_t *gather_rows, int early_dependents, int n_sm,
-                                     cudaStream_t s) {
+                                     const void *gather_src, const int32_t *gather_rows, int early_dependents, int announce,
+                                     int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_x4[i];
     return omni_launch_chain(expert_gemm_kernel<MODE_GATEUP>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_GATEUP>::TOTAL_BYTES, s,
                              *tm_w, tok, st.ttiles, st.n_ttiles, st.sched, (__nv_bfloat16 *)h, st.status, ready, need,
                              group_size > 0 ? group_size : 1, nullptr, 0, (const __nv_bfloat16 *)gather_src, gather_rows,
-                             early_dependents);
+                             early_dependents, announce ? st.done : (int32_t *)nullptr, 0);
 }
 
 cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *tm_h4, const omni_sort_state st,
-                                   void *d, const int32_t *tile_bounds, int group, int early_dependents, int n_sm,
-                                   cudaStream_t s) {
+                                   void *d, const int32_t *tile_bounds, int group, int early_dependents, int chained,
+                                   int n_sm, cudaStream_t s) {
     TokMaps tok;
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
+    chained = chained && st.done && st.done_need;
     return omni_launch_chain(expert_gemm_kernel<MODE_DOWN>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_DOWN>::TOTAL_BYTES, s,
                              *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d,
-                             st.status, nullptr, nullptr, 1, tile_bounds, group, (const __nv_bfloat16 *)nullptr,
-                             (const int32_t *)nullptr, early_dependents);
+                             st.status, chained ? (const uint32_t *)st.done : (const uint32_t *)nullptr,
+                             chained ? st.done_need : (const int32_t *)nullptr, 1, tile_bounds, group, (const __nv_bfloat16 *)nullptr,
+                             (const int32_t *)nullptr, early_dependents, (int32_t *)nullptr, chained);
 }
 
 }  // extern "C"
