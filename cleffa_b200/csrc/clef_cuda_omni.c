@@ -1349,6 +1349,20 @@ static bool attn_plan(clef_gpu *g, int T, int n_seq, const int32_t *seq_bounds, 
         for (int t = lo; t < hi; t++) g->at.h_vcol[t] = col + (t - lo);
         col = (col + (hi - lo) + 63) & ~63;
     }
+    /* longest first (most key blocks = largest distance from the record's start): the blocks of the
+     * grid are dealt in this order, so the short tiles fill the end of the launch.  Insertion sort
+     * by distance, descending, stable. */
+    for (int i = 1; i < n_tiles; i++) {
+        int32_t t[4];
+        memcpy(t, g->at.h_tiles + 4 * i, 16);
+        const int key = t[1] - t[0];
+        int j = i;
+        while (j > 0 && g->at.h_tiles[4 * (j - 1) + 1] - g->at.h_tiles[4 * (j - 1)] < key) {
+            memcpy(g->at.h_tiles + 4 * j, g->at.h_tiles + 4 * (j - 1), 16);
+            j--;
+        }
+        memcpy(g->at.h_tiles + 4 * j, t, 16);
+    }
     if (cudaMemcpyAsync(g->at.tiles, g->at.h_tiles, (size_t)n_tiles * 16, cudaMemcpyHostToDevice, g->stream) != cudaSuccess ||
         cudaMemcpyAsync(g->at.vcol, g->at.h_vcol, (size_t)T * 4, cudaMemcpyHostToDevice, g->stream) != cudaSuccess) {
         cudaGetLastError();

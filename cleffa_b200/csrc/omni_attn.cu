@@ -237,8 +237,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     float *xch = reinterpret_cast<float *>(misc + 64);                         // what the two threads of a row tell each other
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const AttnTile tile = tiles[gridDim.x - 1 - blockIdx.x];                    // a record's longest tiles first
-    const int h0 = 2 * blockIdx.y, kh = h0 / (NH / NKV);
+    const AttnTile tile = tiles[blockIdx.y];                                    // the host lists the tiles with the most key blocks first
+    const int h0 = 2 * blockIdx.x, kh = h0 / (NH / NKV);
     const int q_last = tile.q0 + tile.q_len - 1;                                // last query row of the tile
     const int n_blocks = (q_last - tile.rec_start) / 128 + 1;                   // key blocks from the record's start to the diagonal
 
@@ -511,7 +511,7 @@ cudaError_t omni_launch_attn_prep(const void *qkv, const float *qw, const float 
 // tiles: [n_tiles] of {record start, first query row, rows (<= 128), Vt column of the record start}
 cudaError_t omni_launch_attention(const CUtensorMap *tm_q, const CUtensorMap *tm_k, const CUtensorMap *tm_vt, const void *tiles,
                                   int n_tiles, int T, void *out, uint32_t *status, cudaStream_t s) {
-    return omni_launch_chain(attention_kernel, dim3(n_tiles, OMNI_NH / 2), dim3(AT_THREADS), AT_SMEM_BYTES, s, *tm_q, *tm_k, *tm_vt,
+    return omni_launch_chain(attention_kernel, dim3(OMNI_NH / 2, n_tiles), dim3(AT_THREADS), AT_SMEM_BYTES, s, *tm_q, *tm_k, *tm_vt,
                              (const AttnTile *)tiles, T, 1.0f / sqrtf((float)OMNI_HD), (__nv_bfloat16 *)out, status);
 }
 
