@@ -169,6 +169,7 @@ __global__ void __launch_bounds__(256) assign_hist_kernel(const int32_t *__restr
 __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_state st) {
     __shared__ int part[8][OMNI_E];
     __shared__ int warp_rows[4], warp_tiles[4];
+    __shared__ int tile_key[OMNI_E], tile_cnt[OMNI_E];       // per expert: rows per token tile, token tiles
     dep_wait();
     dep_launch();
     const int e = threadIdx.x & (OMNI_E - 1), grp = threadIdx.x >> 7, lane = threadIdx.x & 31;
@@ -211,6 +212,8 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
             if (lane >= d) { rows_incl += a; tiles_incl += b; }
         }
         if (lane == 31) { warp_rows[e >> 5] = rows_incl; warp_tiles[e >> 5] = tiles_incl; }
+        tile_cnt[e] = (total + OMNI_TILE_N - 1) / OMNI_TILE_N;
+        tile_key[e] = tile_cnt[e] ? total / tile_cnt[e] : 0;
     }
     __syncthreads();
     if (grp == 0) {
@@ -220,9 +223,17 @@ __global__ void __launch_bounds__(1024) assign_scan_kernel(int nseg, omni_sort_s
         st.counts[e] = n;
         st.offsets[e] = off;
         if (e == OMNI_E - 1) st.offsets[OMNI_E] = rows_incl;
-        // expert-major tile list
+        // Expert-major tile list, the experts in order of falling tile length (ties by id): the work
+        // items of the persistent expert kernels are claimed in list order, so the longest come first
+        // and the short ones fill the end of the launch.  Rows and offsets stay in expert order.
         const int nt = (n + OMNI_TILE_N - 1) / OMNI_TILE_N;
-        const int first = tiles_incl - nt;
+        const int key = tile_key[e];
+        int first = 0;
+#pragma unroll 8
+        for (int o = 0; o < OMNI_E; o++) {
+            const int okey = tile_key[o];
+            if (okey > key || (okey == key && o < e)) first += tile_cnt[o];
+        }
         // an expert's rows are split into nt tiles of near-equal length: tiles that share a
         // weight tile then advance at the same pace and meet in L2
         const int base = nt ? n / nt : 0, extra = nt ? n % nt : 0;
