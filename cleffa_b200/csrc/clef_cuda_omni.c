@@ -319,7 +319,7 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
         {(void **)&s->sort.rowmap, (size_t)OMNI_ROWS * 4},
         {(void **)&s->sort.slots, (size_t)OMNI_ROWS * 4},
         {(void **)&s->sort.segcount, (size_t)OMNI_MAX_SEGS * OMNI_E * 4},
-        {(void **)&s->sort.ttiles, (size_t)OMNI_MAX_TTILES * sizeof(omni_ttile)},
+        {(void **)&s->sort.ttiles, (size_t)2 * OMNI_MAX_TTILES * sizeof(omni_ttile)},      /* the list, and the same tiles in expert order */
         {(void **)&s->sort.n_ttiles, 256},
         {(void **)&s->sort.sched, 256},
         {&s->xg, (size_t)OMNI_ROWS * OMNI_H * 2},
@@ -334,6 +334,8 @@ bool clef_omni_reserve(clef_gpu *g, const clef_omni_config *c, int T, char *err,
     }
     s->sort.status = s->status;
     s->sort.n_flag = s->n_flag;
+    s->sort.longest_first = 1;
+    s->sort.ttiles_down = ok ? s->sort.ttiles + OMNI_MAX_TTILES : NULL;
     s->sort.done = ok ? s->n_flag + 64 : NULL;
     s->sort.done_need = ok ? s->n_flag + 192 : NULL;
     for (int i = 0; i < 4 && ok; i++)
@@ -998,6 +1000,7 @@ bool clef_omni_set_option(clef_gpu *g, const char *name, long value) {
     else if (!strcmp(name, "router")) { if (value < 0 || value > 1) return false; g->router_impl = (int)value; }
     else if (!strcmp(name, "expert_kernel")) { if (value < 0 || value > 2) return false; g->expert_kernel = (int)value; }
     else if (!strcmp(name, "expert_chain")) g->expert_chain = value != 0;
+    else if (!strcmp(name, "longest_first")) { if (!g->omni) return false; g->omni->sort.longest_first = value != 0; }
     else if (!strcmp(name, "profile")) { g->profile = value != 0; g->prof_passes = 0; }
     else if (!strcmp(name, "debug_stamps")) g->debug_stamps = value != 0;
     else if (!strcmp(name, "ep_fused")) g->ep_fused = value != 0;

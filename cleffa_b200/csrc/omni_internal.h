@@ -62,6 +62,8 @@ typedef struct {
     int32_t *n_flag;       /* [2] rows flagged for the exact pass: the scan moves [0] to [1] and clears [0] for the next pass */
     int32_t *done;         /* [128] epilogue warps of the gate/up kernel that have stored their part of an expert's rows; zeroed by the scan (may be NULL) */
     int32_t *done_need;    /* [128] what done[e] reaches when expert e's rows are complete: 8 warps x 6 weight tiles x token tiles */
+    int32_t longest_first; /* tile list in order of falling tile length (else in expert order) */
+    omni_ttile *ttiles_down; /* the same tiles in expert order, for the down kernel (may be NULL: it then reads ttiles) */
 } omni_sort_state;
 
 /* Expert parallelism: every rank's view of every rank's exchange buffers (index = rank). */

@@ -509,7 +509,8 @@ cudaError_t omni_launch_down_sm100(const CUtensorMap *tm_w, const CUtensorMap *t
     for (int i = 0; i < 4; i++) tok.m[i] = tm_h4[i];
     chained = chained && st.done && st.done_need;
     return omni_launch_chain(expert_gemm_kernel<MODE_DOWN>, dim3(n_sm), dim3(GEMM_THREADS), GemmSmem<MODE_DOWN>::TOTAL_BYTES, s,
-                             *tm_w, tok, st.ttiles, st.n_ttiles, st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d,
+                             *tm_w, tok, st.ttiles_down && !tile_bounds ? st.ttiles_down : st.ttiles, st.n_ttiles,
+                             st.sched + 1 + (tile_bounds ? group : 0), (__nv_bfloat16 *)d,
                              st.status, chained ? (const uint32_t *)st.done : (const uint32_t *)nullptr,
                              chained ? st.done_need : (const int32_t *)nullptr, 1, tile_bounds, group, (const __nv_bfloat16 *)nullptr,
                              (const int32_t *)nullptr, early_dependents, (int32_t *)nullptr, chained);

@@ -279,6 +279,8 @@ bool clef_omni_read(clef_gpu *g, const char *what, void *dst, size_t bytes, char
  * gate/up kernel; same results; must be the same on every rank, as it changes the number of barriers per pass),
  * "expert_kernel" 0/1/2 (2: expert products on pairs of CTAs, tcgen05.mma.cta_group::2; 1: the same
  * kernel on single CTAs; 0: the earlier single-CTA kernels; same results),
+ * "longest_first" 0/1 (default 1: the gate/up kernel claims its work items in order of falling tile length, the
+ * short ones filling the end of the launch; 0: in expert order; same results; set after clef_omni_reserve),
  * "expert_chain" 0/1 (default 0; one GPU, single-CTA kernels: the down kernel does not wait for the
  * whole gate/up grid but starts on the SMs its first blocks leave and takes each expert's rows once
  * a per-expert counter says they are complete; same results; about 1 % faster while the GPU is
