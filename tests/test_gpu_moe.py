@@ -86,12 +86,14 @@ def test_launch_variants_give_the_same_bits(bound0, T):
     b = bound0
     x = orc.make_activations(17, T)
     base = run_block(b, 0, x)
-    opts = ("fused_router", "fused_gather", "dependent_launch", "expert_chain")
+    opts = ("fused_router", "fused_gather", "dependent_launch", "expert_chain", "longest_first")
     try:
         # expert_chain (off by default): the down kernel starts while gate/up's last blocks still
         # run and takes each expert's rows once they are complete; twice, so that the second pass
         # meets the counters and the tile list of another batch at the same addresses
-        for combo in ((0, 1, 1, 0), (1, 0, 1, 0), (1, 1, 0, 0), (0, 0, 0, 0), (1, 1, 1, 1), (1, 0, 1, 1), (1, 1, 0, 1)):
+        # longest_first (on by default): the order in which the gate/up kernel claims its work items
+        for combo in ((0, 1, 1, 0, 1), (1, 0, 1, 0, 1), (1, 1, 0, 0, 1), (0, 0, 0, 0, 0), (1, 1, 1, 1, 1), (1, 0, 1, 1, 0), (1, 1, 0, 1, 1),
+                      (1, 1, 1, 0, 0)):
             for name, v in zip(opts, combo):
                 b.set_option(name, v)
             if combo[3]:
@@ -100,7 +102,7 @@ def test_launch_variants_give_the_same_bits(bound0, T):
             for key in ("ids", "slots", "counts", "rechecked", "out"):
                 assert np.array_equal(base[key], other[key]), (key, combo)
     finally:
-        for name in opts[:3]:
+        for name in opts[:3] + opts[4:]:
             b.set_option(name, 1)
         b.set_option("expert_chain", 0)
 
